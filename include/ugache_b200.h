@@ -1,0 +1,246 @@
+/*
+ * ugache_b200 -- C ABI of the B200-native embedding-extraction path.
+ *
+ * Plain C: pointers, sizes and integer status codes only; no exception crosses this
+ * boundary and no function aborts the process.  Every call returns UGC_OK (0) or an
+ * error code; ugc_last_error() gives the message of the calling thread's last failure.
+ *
+ * Each entry point cites the interface of the reference (SJTU-IPADS/ugache, paths
+ * relative to its project root) that it replaces.
+ *
+ * Vocabulary (the reference's): a *replica* is one GPU worker; a *location* is a source
+ * of rows -- replicas 0..G-1 are the GPUs' cache slices, location G is the host table;
+ * the *placement* is the host-side input (4 arrays) saying which GPUs store which rows
+ * and where each reader fetches each row from.
+ */
+#ifndef UGACHE_B200_H_
+#define UGACHE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define UGC_MAX_DEVICE 8 /* placement bitmask is one byte: optimal_solver_class.cc:1381 */
+
+typedef enum {
+  UGC_OK = 0,
+  UGC_ERR_INVALID = 1,     /* bad argument or configuration                         */
+  UGC_ERR_CUDA = 2,        /* a CUDA runtime call failed (message has the details)  */
+  UGC_ERR_NOMEM = 3,       /* allocator returned NULL                               */
+  UGC_ERR_CAPACITY = 4,    /* placement needs more cache rows than the slice holds  */
+  UGC_ERR_STATE = 5,       /* call out of order (e.g. lookup before build)          */
+  UGC_ERR_KEY_RANGE = 6,   /* a key outside [0, num_total_item) was seen            */
+  UGC_ERR_TIMEOUT = 7,     /* a bounded host-side wait ran out                      */
+  UGC_ERR_UNSUPPORTED = 8, /* row size / key space outside what the kernels handle  */
+  UGC_ERR_TABLE = 9        /* table inconsistency found on the device (dup / miss)  */
+} ugc_status;
+
+/* Placement heuristics of the reference that need no MILP licence
+ * (python/collcache/common/__init__.py:46-64 numbering). */
+typedef enum {
+  UGC_POLICY_INTUITIVE = 9, /* coll_intuitive: replicate hottest, partition next      */
+  UGC_POLICY_REP = 12,      /* rep: replicate hottest on every GPU                    */
+  UGC_POLICY_CLIQUE_PART = 14 /* clique_part: partition hottest round-robin           */
+} ugc_policy;
+
+typedef enum { UGC_TABLE_AUTO = 0, UGC_TABLE_FLAT = 1, UGC_TABLE_HASHED = 2 } ugc_table_kind;
+
+/* Device-memory allocator supplied by the caller, the C form of the reference's
+ * std::function<MemHandle(size_t)> gpu_mem_allocator (coll_cache_lib/facade.h:57-60,
+ * coll_cache_lib/common.h:140-149).  Called with the replica's device current.
+ * NULL callbacks select cudaMalloc / cudaFree. */
+typedef void* (*ugc_alloc_fn)(size_t nbytes, void* user);
+typedef void (*ugc_free_fn)(void* ptr, void* user);
+
+/* Replaces the static RunConfig + config map of the reference
+ * (coll_cache_lib/run_config.h:30-111, python/collcache/common/operation.cc:68-104). */
+typedef struct {
+  uint32_t struct_size;     /* sizeof(ugc_config), for forward compatibility          */
+  int32_t num_device;       /* G: replicas in the job, 1..8                            */
+  uint64_t num_total_item;  /* N: rows of the table, < 2^31-1                          */
+  uint32_t row_bytes;       /* bytes per row (dim * element size), multiple of 4       */
+  double cache_percentage;  /* per-GPU cache size as a FRACTION of N, 0..1             */
+  int32_t empty_feat;       /* k>0: host rows wrap to key mod 2^k (SAMGRAPH_EMPTY_FEAT,
+                               coll_cache_lib/cache_context.h:346-352); 0 = off        */
+  int32_t table_kind;       /* ugc_table_kind; AUTO follows cache_context.cu:2489-2497 */
+  uint32_t max_batch;       /* largest key batch one lookup may carry (scratch size)   */
+  int32_t register_host;    /* 1: cudaHostRegister the host table if it is not already
+                               GPU-visible (coll_cache_lib/facade.cc:476)              */
+  /* Link model used to size the per-source CTA groups of the gather (the B200
+   * counterpart of coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289).  0 = default. */
+  double bw_local_gbs, bw_remote_gbs, bw_host_gbs;
+  int32_t gather_ctas_per_sm; /* CTAs of the gather kernel per SM; 0 = default          */
+  int32_t host_ctas;          /* CTA budget of the host-row group; 0 = default          */
+  int32_t remote_ctas;        /* CTA budget of the peer-row group; 0 = default          */
+  ugc_alloc_fn alloc;
+  ugc_free_fn free;
+  void* alloc_user;
+} ugc_config;
+
+typedef struct ugc_ctx ugc_ctx; /* one per process; holds the replicas built in it */
+
+/* What one replica publishes so that peers can read its slice and its table, and the C
+ * form of DevicePointerExchanger's page of pointers / IPC handles
+ * (coll_cache_lib/cache_context.cu:2648-2680). */
+typedef struct {
+  int32_t replica_id;
+  int32_t device_id;
+  int64_t pid;
+  uint64_t slice_ptr;        /* device address in the owner's process                  */
+  uint64_t table_ptr;
+  uint64_t table_lines;      /* hashed: number of 32-byte lines; flat: N               */
+  int32_t table_kind;
+  int32_t has_ipc;
+  unsigned char slice_ipc[64]; /* cudaIpcMemHandle_t                                   */
+  unsigned char table_ipc[64];
+} ugc_peer_handle;
+
+typedef struct {
+  uint64_t num_local_rows;     /* rows this replica stores                             */
+  uint64_t num_remote_keys;    /* keys it reads from peers                             */
+  uint64_t num_host_keys;      /* keys it reads from the host table                    */
+  uint64_t capacity_rows;
+  uint64_t free_rows;
+  int32_t table_kind;
+  uint64_t table_bytes;
+  uint64_t slice_bytes;
+  /* last completed lookup (valid after the stream it ran on is synchronised) */
+  uint64_t last_keys;
+  uint64_t last_local, last_remote, last_host;
+  /* sticky device-side error counters */
+  uint64_t err_key_range;
+  uint64_t err_table;
+  uint64_t lookups;            /* lookups issued on this replica                       */
+} ugc_stats_t;
+
+const char* ugc_version(void);
+const char* ugc_last_error(void);
+const char* ugc_status_string(int status);
+
+/* Fills *cfg with defaults (struct_size set, everything else zero / default). */
+int ugc_config_default(ugc_config* cfg);
+
+/* -- context ------------------------------------------------------------------------ */
+/* CollCache constructor + coll_cache_config (coll_cache_lib/facade.h:39,
+ * python/collcache/common/operation.cc:160-173). */
+int ugc_create(const ugc_config* cfg, ugc_ctx** out);
+int ugc_destroy(ugc_ctx* ctx);
+
+/* -- placement (host side; no GPU needed) -------------------------------------------- */
+/* The reference's non-MILP solvers: IntuitiveSolver / RepSolver / CliquePartSolver
+ * (coll_cache_lib/coll_cache/optimal_solver_class.cc:1251-1404, :1869-1924, :1926-2058).
+ * cache_percent is in PERCENT (0..100) as the solvers take it.  Output arrays are caller
+ * allocated: nid_to_block[N], block_placement[G+2], block_access_from[G*(G+2)],
+ * block_density[G+2]; *num_block receives the number of blocks actually used (row stride
+ * of block_access_from). */
+int ugc_solve_placement(int policy, int num_device, uint64_t num_total_item,
+                        const uint32_t* rank_ids, const uint32_t* rank_freqs,
+                        double cache_percent, double t_local, double t_remote, double t_cpu,
+                        uint32_t* nid_to_block, uint8_t* block_placement,
+                        uint8_t* block_access_from, double* block_density, int* num_block);
+
+/* Default B200 time-per-byte ratios (local : remote : host) for the solvers, the
+ * counterpart of coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289. */
+int ugc_link_model(int num_device, double* t_local, double* t_remote, double* t_cpu);
+
+/* Hands the placement to the context (arrays are copied).  Corresponds to the four shm
+ * tensors the reference publishes (coll_cache_lib/facade.cc:238-261). */
+int ugc_set_placement(ugc_ctx* ctx, const uint32_t* nid_to_block, const uint8_t* block_placement,
+                      const uint8_t* block_access_from, const double* block_density,
+                      int num_block);
+
+/* Host-side key classification for one reader: which source serves each key.
+ * Replaces CacheEntryManager::DetectKeysForAllSource
+ * (coll_cache_lib/cuda/cache_hashtable.cuh:741-835); lists come out in ascending key
+ * order.  counts[G+1] receives the per-location key counts (index G = host).  If
+ * keys_out is non-NULL it must hold N entries and receives the GPU-served keys grouped by
+ * source (source s starts at the sum of counts[0..s)).  Needs ugc_set_placement. */
+int ugc_classify_keys(ugc_ctx* ctx, int replica_id, uint64_t* counts, uint32_t* keys_out);
+
+/* -- build ---------------------------------------------------------------------------- */
+/* Per-replica cache build: allocate the slice, fill it from the host table, build the
+ * table for the rows stored here.  Replaces CollCache::build_v2 -> CacheContext::build
+ * (coll_cache_lib/facade.cc:430-511, coll_cache_lib/cache_context.cu:2414-2520).
+ * host_table: N rows (or 2^empty_feat rows) of row_bytes, caller owned, must stay valid.
+ * stream: a cudaStream_t (NULL = default stream).  Returns after the stream is idle. */
+int ugc_build(ugc_ctx* ctx, int replica_id, int device_id, const void* host_table,
+              void* stream);
+
+/* Publishes / receives peer pointers (DevicePointerExchanger signin / extract,
+ * coll_cache_lib/cache_context.cu:2519-2526, :2658-2680).  ugc_connect_local wires every
+ * replica built in THIS process to every other one (peer access is enabled when they sit
+ * on different devices); ugc_import_peer takes a handle from another process. */
+int ugc_export(ugc_ctx* ctx, int replica_id, ugc_peer_handle* out);
+int ugc_import_peer(ugc_ctx* ctx, int replica_id, const ugc_peer_handle* peer);
+int ugc_connect_local(ugc_ctx* ctx);
+
+/* Resolves the slice offsets of the keys this replica reads from peers by probing the
+ * peers' tables over P2P, and inserts them into its own table.  Replaces the per-peer
+ * loop of coll_cache_lib/cache_context.cu:2531-2570.  Every peer named by the placement
+ * must have been imported and must have finished ugc_build. */
+int ugc_attach_peers(ugc_ctx* ctx, int replica_id, void* stream);
+
+/* -- lookup (the hot path) ------------------------------------------------------------ */
+/* out[i, :] = row of keys[i], for i in [0, n).  keys and out are DEVICE pointers on the
+ * replica's GPU; out holds n * row_bytes bytes.  Work is enqueued on `stream` and the
+ * call returns without synchronising (the reference's call returns after its internal
+ * streams are idle; its shim adds the synchronise).  Replaces CollCache::lookup ->
+ * ExtractSession::ExtractFeat (coll_cache_lib/facade.cc:74-88,
+ * coll_cache_lib/cache_context.cu:1199) and coll_cache_lookup
+ * (python/collcache/common/operation.cc:232-236), whose keys are 32-bit. */
+int ugc_lookup_u32(ugc_ctx* ctx, int replica_id, const uint32_t* keys, size_t n, void* out,
+                   void* stream);
+/* Same with 64-bit ids (results identical for ids below 2^31-1). */
+int ugc_lookup_i64(ugc_ctx* ctx, int replica_id, const int64_t* keys, size_t n, void* out,
+                   void* stream);
+
+/* Host-buffer form: keys and out are HOST pointers (pinned memory gives full speed).
+ * Copies the keys to the GPU, runs the lookup, copies the rows back and returns after
+ * they have landed.  key_bytes is 4 or 8. */
+int ugc_lookup_host(ugc_ctx* ctx, int replica_id, const void* keys, int key_bytes, size_t n,
+                    void* out, void* stream);
+
+/* -- refresh --------------------------------------------------------------------------- */
+/* Moves a replica from the current placement to a new one while lookups keep running.
+ * Replaces CollCache::refresh -> RefreshSession::refresh_after_solve_new
+ * (coll_cache_lib/facade.cc:513-557, coll_cache_lib/cache_context.cu:3944-4107) in three
+ * phases; the caller puts a barrier over all replicas between them, as the reference
+ * does (cache_context.cu:4047, :4077, :4099):
+ *   ugc_refresh_set_placement  once per process: the new placement (old one is kept)
+ *   ugc_refresh_evict          steps 1-4: classify, evict local and re-pointed remote keys
+ *   ugc_refresh_fill           step 6: scatter new rows into freed slots, insert them
+ *   ugc_refresh_attach         step 7: resolve and insert the new remote keys
+ *   ugc_refresh_commit         once per process: new placement becomes current
+ */
+int ugc_refresh_set_placement(ugc_ctx* ctx, const uint32_t* nid_to_block,
+                              const uint8_t* block_placement, const uint8_t* block_access_from,
+                              const double* block_density, int num_block);
+int ugc_refresh_evict(ugc_ctx* ctx, int replica_id, void* stream);
+int ugc_refresh_fill(ugc_ctx* ctx, int replica_id, void* stream);
+int ugc_refresh_attach(ugc_ctx* ctx, int replica_id, void* stream);
+int ugc_refresh_commit(ugc_ctx* ctx);
+
+/* -- introspection --------------------------------------------------------------------- */
+int ugc_stats(ugc_ctx* ctx, int replica_id, ugc_stats_t* out);
+
+/* Debug / test aid: the packed (location << 28 | offset) word the replica's table holds
+ * for each of n keys (0xffffffff = not in the table, i.e. served by the host).  keys and
+ * words are DEVICE pointers.  The word format is the reference's EmbCacheOff
+ * (coll_cache_lib/cuda/cache_hashtable.h:20-28). */
+int ugc_table_words(ugc_ctx* ctx, int replica_id, const uint32_t* keys, size_t n,
+                    uint32_t* words, void* stream);
+
+/* Synthetic-input helper for benchmarks: writes rows [row_begin, row_begin+n_rows) of the
+ * seeded uniform[-1,1) table into dst (device memory, or GPU-visible pinned host memory).
+ * elem_bytes 4 = fp32, 2 = fp16.  No counterpart in the reference (its tables are loaded
+ * from datasets, python/collcache/torch/adapter.cc:239-270). */
+int ugc_gen_table(void* dst, uint64_t seed, uint64_t row_begin, uint64_t n_rows, uint64_t dim,
+                  int elem_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UGACHE_B200_H_ */

@@ -1,0 +1,263 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle, bit for bit.
+
+Replicas are spread over the visible GPUs round-robin; on a one-GPU box all of them sit on
+device 0, where a "peer" slice is simply another allocation on the same device: the
+multi-replica logic (placement, tables, peer resolve, grouped gather) is exercised in
+full, only the NVLink hop is missing.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests.conftest import oracle_solver
+from tests.helpers import case_workload, digest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def pinned_table(np_table):
+    t = torch.from_numpy(np_table.view(np.uint8).reshape(np_table.shape[0], -1).copy()).pin_memory()
+    return t
+
+
+def make_cache(w, table_kind=0, max_batch=1 << 16, **kw):
+    from ugache_b200 import runtime as rt
+    ndev = torch.cuda.device_count()
+    cache = rt.Cache(w.G, w.N, w.row_bytes, w.pct, max_batch=max_batch, table_kind=table_kind, **kw)
+    cache.set_placement(w.placement)
+    host = pinned_table(w.table)
+    for r in range(w.G):
+        cache.build(r, r % ndev, host.data_ptr())
+    cache.connect_local()
+    for r in range(w.G):
+        cache.attach_peers(r)
+    cache._host_keepalive = host
+    return cache
+
+
+def lookup_np(cache, r, keys_np, dtype=torch.int64):
+    ndev = torch.cuda.device_count()
+    dev = torch.device("cuda", r % ndev)
+    with torch.cuda.device(dev):
+        k = torch.from_numpy(np.ascontiguousarray(keys_np)).to(dev)
+        if dtype != torch.int64:
+            k = k.to(dtype)
+        out = torch.full((len(keys_np), cache.cfg.row_bytes), 0xCD, dtype=torch.uint8, device=dev)
+        cache.lookup(r, k, out=out)
+        torch.cuda.synchronize(dev)
+        return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("table_kind", [0, 1, 2])
+def test_golden_cases_bit_exact(built_lib, golden_cases, table_kind):
+    for case in golden_cases:
+        w = case_workload(case)
+        cache = make_cache(w, table_kind=table_kind)
+        for r in range(w.G):
+            keys = w.keys(rank=r)
+            want = orc.gather(w.table, keys)
+            got = lookup_np(cache, r, keys)
+            assert got.tobytes() == want.tobytes(), (case["name"], r)
+            assert digest(got) == case["ranks"][str(r)]["out"]
+            st = cache.stats(r)
+            assert st["err_key_range"] == 0 and st["err_table"] == 0
+            # per-source split of the batch against the oracle's model
+            words, _, _ = orc.model_build(w.placement, r, w.capacity)
+            kw = words[keys]
+            n_host = int((kw == 0xFFFFFFFF).sum())
+            n_local = int(((kw != 0xFFFFFFFF) & ((kw >> 28) == r)).sum())
+            assert (st["last_local"], st["last_remote"], st["last_host"]) == \
+                (n_local, len(keys) - n_local - n_host, n_host)
+            assert st["last_keys"] == len(keys)
+        cache.close()
+
+
+def test_table_words_match_oracle_model(built_lib, golden_cases):
+    for case in golden_cases:
+        w = case_workload(case)
+        for kind in (1, 2):
+            cache = make_cache(w, table_kind=kind)
+            allk = torch.arange(w.N, dtype=torch.int32)
+            for r in range(w.G):
+                dev = torch.device("cuda", r % torch.cuda.device_count())
+                got = cache.table_words(r, allk.to(dev))
+                torch.cuda.synchronize(dev)
+                words, _, _ = orc.model_build(w.placement, r, w.capacity)
+                assert np.array_equal(got.cpu().numpy().view(np.uint32), words), (case["name"], r, kind)
+                assert digest(got.cpu().numpy().view(np.uint32)) == case["ranks"][str(r)]["words"]
+            cache.close()
+
+
+def test_u32_keys_and_int64_agree(built_lib, golden_cases):
+    case = golden_cases[2]
+    w = case_workload(case)
+    cache = make_cache(w)
+    keys = w.keys(rank=1)
+    a = lookup_np(cache, 1, keys)
+    b = lookup_np(cache, 1, keys, dtype=torch.int32)
+    assert a.tobytes() == b.tobytes() == orc.gather(w.table, keys).tobytes()
+    cache.close()
+
+
+@pytest.mark.parametrize("n", [0, 1, 2, 31, 32, 33, 255, 256, 257, 1023, 1024, 1025, 4097])
+def test_ragged_batch_sizes(built_lib, golden_cases, n):
+    case = golden_cases[4]   # 8 replicas
+    w = case_workload(case)
+    cache = make_cache(w)
+    keys = w.keys(rank=3)[:n]
+    got = lookup_np(cache, 3, keys)
+    assert got.tobytes() == orc.gather(w.table, keys).tobytes()
+    cache.close()
+
+
+def test_duplicates_and_single_source_batches(built_lib, golden_cases):
+    case = golden_cases[2]
+    w = case_workload(case)
+    cache = make_cache(w)
+    words, _, _ = orc.model_build(w.placement, 0, w.capacity)
+    local = np.nonzero((words != 0xFFFFFFFF) & ((words >> 28) == 0))[0]
+    remote = np.nonzero((words != 0xFFFFFFFF) & ((words >> 28) == 1))[0]
+    host = np.nonzero(words == 0xFFFFFFFF)[0]
+    rng = np.random.default_rng(0)
+    for name, pool in (("local", local), ("remote", remote), ("host", host)):
+        keys = rng.choice(pool, size=3000).astype(np.int64)      # with duplicates
+        got = lookup_np(cache, 0, keys)
+        assert got.tobytes() == orc.gather(w.table, keys).tobytes(), name
+    same = np.full(2000, int(local[0]), dtype=np.int64)          # one key repeated
+    assert lookup_np(cache, 0, same).tobytes() == orc.gather(w.table, same).tobytes()
+    cache.close()
+
+
+def test_out_of_range_keys_are_counted_and_skipped(built_lib, golden_cases):
+    case = golden_cases[1]
+    w = case_workload(case)
+    cache = make_cache(w)
+    keys = w.keys(rank=0)[:1000].copy()
+    keys[10] = w.N           # first id past the table
+    keys[20] = -1
+    keys[30] = 1 << 40
+    got = lookup_np(cache, 0, keys)
+    want = orc.gather(w.table, np.where((keys >= 0) & (keys < w.N), keys, 0))
+    good = np.ones(1000, dtype=bool)
+    good[[10, 20, 30]] = False
+    assert got[good].tobytes() == want.view(np.uint8).reshape(1000, -1)[good].tobytes()
+    assert (got[~good] == 0xCD).all()          # rows of bad keys are left untouched
+    st = cache.stats(0)
+    assert st["err_key_range"] == 3
+    assert st["last_local"] + st["last_remote"] + st["last_host"] == 997
+    cache.close()
+
+
+def test_host_buffer_lookup(built_lib, golden_cases):
+    case = golden_cases[2]
+    w = case_workload(case)
+    cache = make_cache(w)
+    keys = w.keys(rank=0)
+    out = np.zeros((len(keys), w.row_bytes), dtype=np.uint8)
+    cache.lookup_host(0, keys, out)
+    assert out.tobytes() == orc.gather(w.table, keys).tobytes()
+    k32 = keys.astype(np.uint32)
+    out2 = np.zeros_like(out)
+    cache.lookup_host(0, k32, out2)
+    assert out2.tobytes() == out.tobytes()
+    cache.close()
+
+
+def test_mock_host_table(built_lib):
+    """empty_feat: host rows wrap to key mod 2^k, cached rows are filled from the wrapped row
+    too (the reference's SAMGRAPH_EMPTY_FEAT)."""
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim, k = 30000, 32, 10
+    small = wl.table(9, 1 << k, dim)
+    ids, freqs = wl.analytic_hotness(N, 1.2)
+    p = rt.solve_placement("rep", 1, ids, freqs, 10.0)
+    cache = rt.Cache(1, N, dim * 4, 0.10, max_batch=1 << 14, empty_feat=k)
+    cache.set_placement(p)
+    host = pinned_table(small)
+    cache.build(0, 0, host.data_ptr())
+    keys = wl.zipf_keys(5, 5000, N, 1.2)
+    got = lookup_np(cache, 0, keys)
+    assert got.tobytes() == orc.gather(small, keys, empty_feat=k).tobytes()
+    cache.close()
+
+
+def test_gen_table_matches_oracle(built_lib):
+    from ugache_b200 import runtime as rt
+    for dt, eb in ((np.float32, 4), (np.float16, 2)):
+        n_rows, dim, row0 = 1000, 64, 12345
+        buf = torch.empty(n_rows * dim * eb, dtype=torch.uint8, device="cuda")
+        rt.gen_table(buf.data_ptr(), 77, row0, n_rows, dim, eb, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert buf.cpu().numpy().tobytes() == orc.gen_rows(77, row0, n_rows, dim, dt).tobytes()
+    # straight into pinned host memory (how the benchmark fills its table)
+    host = torch.empty(256 * 128 * 4, dtype=torch.uint8).pin_memory()
+    rt.gen_table(host.data_ptr(), 3, 0, 256, 128, 4, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert host.numpy().tobytes() == orc.gen_rows(3, 0, 256, 128).tobytes()
+
+
+def test_refresh_keeps_results_identical(built_lib):
+    """Lookups before, between the phases of, and after a refresh all return the table's
+    rows; the per-replica stored set follows the new placement."""
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim, G = 40000, 32, 4
+    table = wl.table(31, N, dim)
+    ids, freqs = wl.analytic_hotness(N, 1.2)
+    p_old = rt.solve_placement("intuitive", G, ids, freqs, 8.0)
+    shifted = np.roll(ids, 1500)              # hotness drifts: a different hot set
+    p_new = rt.solve_placement("intuitive", G, shifted, freqs, 8.0)
+    for kind in (1, 2):
+        cache = rt.Cache(G, N, dim * 4, 0.08, max_batch=1 << 14, table_kind=kind)
+        cache.set_placement(p_old)
+        host = pinned_table(table)
+        ndev = torch.cuda.device_count()
+        for r in range(G):
+            cache.build(r, r % ndev, host.data_ptr())
+        cache.connect_local()
+        for r in range(G):
+            cache.attach_peers(r)
+        keys = [wl.zipf_keys(100 + r, 6000, N, 1.2) for r in range(G)]
+        want = [orc.gather(table, k).tobytes() for k in keys]
+
+        def check(tag):
+            for r in range(G):
+                assert lookup_np(cache, r, keys[r]).tobytes() == want[r], (tag, r, kind)
+
+        check("before")
+        cache.refresh_set_placement(p_new)
+        for r in range(G):
+            cache.refresh_evict(r)
+        check("after evict")                  # evicted keys fall back to the host
+        for r in range(G):
+            cache.refresh_fill(r)
+        check("after fill")
+        for r in range(G):
+            cache.refresh_attach(r)
+        cache.refresh_commit()
+        check("after refresh")
+        o_new = orc.Placement(p_new.nid_to_block, p_new.block_placement, p_new.block_access_from,
+                              p_new.block_density)
+        allk = torch.arange(N, dtype=torch.int32)
+        for r in range(G):
+            dev = torch.device("cuda", r % ndev)
+            got = cache.table_words(r, allk.to(dev)).cpu().numpy().view(np.uint32)
+            words, cnt, _ = orc.model_build(o_new, r, int(N * 0.081))
+            # same source per key as the model; slots differ after a refresh by design
+            assert np.array_equal(got == 0xFFFFFFFF, words == 0xFFFFFFFF)
+            live = got != 0xFFFFFFFF
+            assert np.array_equal(got[live] >> 28, words[live] >> 28)
+            st = cache.stats(r)
+            assert st["err_table"] == 0
+            assert st["num_local_rows"] == int(cnt[r])
+            assert st["free_rows"] == st["capacity_rows"] - st["num_local_rows"]
+            # every stored row sits in its own slot
+            mine = got[live & ((got >> 28) == r)] & 0x0FFFFFFF
+            assert len(np.unique(mine)) == len(mine)
+        # a second refresh back to the old placement
+        cache.refresh_all_local(p_old, list(range(G)))
+        check("after second refresh")
+        cache.close()

@@ -1,0 +1,150 @@
+"""CPU-only checks of the shipped library: it loads without a GPU, exports every symbol
+the headers declare, its host-side logic (placement heuristics, key classification,
+validation) agrees with the oracle, and device entry points fail with a status (never a
+crash, never a silent CPU fallback) when no GPU is present."""
+import ctypes as C
+import glob
+import os
+import re
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests.conftest import ROOT, oracle_solver
+from tests.helpers import case_workload, digest
+
+
+def declared_symbols():
+    names = set()
+    for h in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        text = open(h).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        text = re.sub(r"//[^\n]*", "", text)
+        names |= set(re.findall(r"\b((?:ugc|coll_cache)_[a-z0-9_]+)\s*\(", text))
+    return sorted(n for n in names if not n.endswith("_fn"))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    lib = C.CDLL(built_lib)
+    syms = declared_symbols()
+    assert len(syms) >= 20
+    missing = [s for s in syms if not hasattr(lib, s)]
+    assert not missing, missing
+
+
+def test_binding_covers_header(built_lib):
+    from ugache_b200 import _lib
+    ugc = [s for s in declared_symbols() if s.startswith("ugc_")]
+    assert sorted(_lib.SIGNATURES) == ugc
+
+
+def test_placement_solvers_match_oracle(built_lib, golden_cases):
+    from ugache_b200 import runtime as rt
+    for case in golden_cases:
+        w_prod = case_workload(case)                 # product solver (C++ in the library)
+        w_orc = case_workload(case, oracle_solver)   # oracle solver
+        for f in ("nid_to_block", "block_placement", "block_access_from", "block_density"):
+            assert np.array_equal(getattr(w_prod.placement, f), getattr(w_orc.placement, f)), \
+                (case["name"], f)
+        assert digest(w_prod.placement.nid_to_block) + digest(w_prod.placement.block_access_from) \
+            == case["placement"]
+    # a few more shapes, all three policies, G = 1..8
+    rng = np.random.default_rng(0)
+    for G in (1, 2, 3, 5, 8):
+        N = 3000 + 17 * G
+        ids = rng.permutation(N).astype(np.uint32)
+        freqs = np.sort(rng.zipf(1.3, N).astype(np.uint32))[::-1].copy()
+        for pol in ("intuitive", "rep", "clique_part"):
+            for pct in (0.0, 1.0, 7.5, 40.0, 100.0):
+                a = rt.solve_placement(pol, G, ids, freqs, pct)
+                b = oracle_solver(pol, G, ids, freqs, pct)
+                assert np.array_equal(a.nid_to_block, b.nid_to_block), (G, pol, pct)
+                assert np.array_equal(a.block_access_from, b.block_access_from)
+                assert np.array_equal(a.block_placement, b.block_placement)
+                assert np.allclose(a.block_density, b.block_density)
+
+
+def test_classification_matches_oracle(built_lib, golden_cases):
+    from ugache_b200 import runtime as rt
+    for case in golden_cases:
+        w = case_workload(case)
+        cache = rt.Cache(case["G"], case["N"], w.row_bytes, case["pct"], max_batch=1 << 14)
+        cache.set_placement(w.placement)
+        for r in range(case["G"]):
+            counts, lists = cache.classify_keys(r, want_keys=True)
+            words, cnt, slot_of = orc.model_build(w.placement, r, w.capacity)
+            assert [int(x) for x in counts] == case["ranks"][str(r)]["per_src"]
+            for s in range(case["G"]):
+                want = np.nonzero((words != 0xFFFFFFFF) & ((words >> 28) == s))[0]
+                assert np.array_equal(lists[s], want.astype(np.uint32))
+                if s == r:  # slot = position in the ascending list
+                    assert np.array_equal(slot_of[r][lists[s]], np.arange(len(lists[s])))
+        cache.close()
+
+
+def test_config_and_placement_validation(built_lib):
+    from ugache_b200 import _lib, runtime as rt
+    with pytest.raises(_lib.UgcError):
+        rt.Cache(9, 1000, 512, 0.1)
+    with pytest.raises(_lib.UgcError):
+        rt.Cache(1, 1000, 510, 0.1)           # row size not a multiple of 4
+    with pytest.raises(_lib.UgcError):
+        rt.Cache(1, 1000, 512, 1.5)           # fraction, not percent
+    with pytest.raises(_lib.UgcError):
+        rt.Cache(1, 1 << 31, 512, 0.1)        # key space too large for 31-bit table keys
+    cache = rt.Cache(2, 1000, 512, 0.1)
+    ids = np.arange(1000, dtype=np.uint32)
+    good = rt.solve_placement("rep", 2, ids, None, 10.0)
+    cache.set_placement(good)
+    bad = rt.PlacementArrays(good.nid_to_block, good.block_placement,
+                             good.block_access_from.copy(), good.block_density)
+    bad.block_access_from[0, 0] = 1           # GPU 0 stores block 0 but reads it from GPU 1
+    with pytest.raises(_lib.UgcError):
+        cache.set_placement(bad)
+    bad2 = rt.PlacementArrays(good.nid_to_block.copy(), good.block_placement,
+                              good.block_access_from, good.block_density)
+    bad2.nid_to_block[5] = 99                 # block id out of range
+    with pytest.raises(_lib.UgcError):
+        cache.set_placement(bad2)
+    with pytest.raises(_lib.UgcError):        # lookup before build
+        cache.lookup_ptr(0, 1, 8, 1, 1)
+    cache.close()
+
+
+def test_device_entry_points_fail_loudly_without_gpu(built_lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from ugache_b200 import _lib, runtime as rt
+    cache = rt.Cache(1, 1000, 512, 0.1)
+    cache.set_placement(rt.solve_placement("rep", 1, np.arange(1000, dtype=np.uint32), None, 10.0))
+    table = np.zeros((1000, 128), dtype=np.float32)
+    with pytest.raises(_lib.UgcError) as e:
+        cache.build(0, 0, table.ctypes.data)
+    assert e.value.status == 2               # UGC_ERR_CUDA: no silent fallback
+    cache.close()
+
+
+def test_missing_library_is_an_import_error(monkeypatch, tmp_path):
+    from ugache_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError):
+        _lib.lib()
+
+
+def test_workload_generators_match_oracle():
+    from ugache_b200 import workload as wl
+    for dt in (np.float32, np.float16):
+        a = wl.table(21, 300, 24, dt, row_begin=5)
+        b = orc.gen_rows(21, 5, 300, 24, dt)
+        assert a.tobytes() == b.tobytes()
+    u = np.random.default_rng(4).random(50000)
+    for N, alpha in ((10 ** 8, 1.2), (4 * 10 ** 8, 1.05), (10 ** 6, 1.0), (10 ** 6, 0.8), (10 ** 6, 1.4)):
+        r = wl.zipf_ranks(u, N, alpha)
+        assert np.array_equal(r, orc.zipf_ranks(u, N, alpha))
+        A, B = wl.bijection(N)
+        assert np.array_equal(wl.rank_to_id(r, N), orc.rank_to_id(r, N, A, B))
+        ids = wl.rank_to_id(np.arange(1000), N)
+        assert len(np.unique(ids)) == 1000

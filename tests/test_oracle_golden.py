@@ -1,0 +1,130 @@
+"""The CPU oracle against (a) known answers printed by the reference's own code and
+(b) the committed digests of its answers on the small seeded cases."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests.conftest import oracle_solver
+from tests.helpers import case_workload, digest
+
+
+def test_murmur3_matches_reference(ref_pin):
+    for key, want in ref_pin["murmur3_32"]:
+        assert orc.murmur3_32(key) == want
+
+
+def test_packed_word_matches_reference(ref_pin):
+    for loc, off, data, rloc, roff in ref_pin["emb_cache_off"]:
+        w = orc.pack_loc_off(loc, off)
+        assert w == data
+        assert orc.lib().orc_word_loc(w) == rloc
+        assert orc.lib().orc_word_off(w) == roff
+
+
+def test_table_size_matches_reference(ref_pin):
+    for num, want in ref_pin["table_size"]:
+        assert orc.table_size(num) == want
+
+
+def test_constants_match_reference(ref_pin):
+    assert ref_pin["constants"]["kEmptyKey"] == 0xFFFFFFFF
+    assert ref_pin["constants"]["kEmptyPos"] == 0xFFFFFFFF
+
+
+def test_table_choice_rule():
+    # sizes worked out from the reference rule: flat iff TableSize(entries) > N/2
+    N = 100_000_000
+    assert orc.use_flat_table(80_000_000, N)       # 8 GPUs x 10 %
+    assert orc.use_flat_table(40_000_000, N)       # 8 GPUs x 5 %
+    assert not orc.use_flat_table(10_000_000, N)   # 1 GPU x 10 %
+    assert orc.cache_capacity(N, 0.10) == 10_100_000
+
+
+def test_probing_table_semantics():
+    rng = np.random.default_rng(1)
+    keys = rng.choice(1 << 20, size=5000, replace=False).astype(np.uint32)
+    t = orc.SimpleTable(len(keys))
+    ref = {}
+    for i, k in enumerate(keys):
+        t.insert(int(k), orc.pack_loc_off(i % 8, i))
+        ref[int(k)] = orc.pack_loc_off(i % 8, i)
+    for k in keys[:500]:
+        pos = t.search(int(k))
+        assert pos != 0xFFFFFFFF and t.buckets[pos]["val"] == ref[int(k)]
+    absent = np.setdiff1d(np.arange(1 << 20, dtype=np.uint32), keys)[:500]
+    for k in absent:
+        assert t.search(int(k)) == 0xFFFFFFFF
+    # evict then re-insert elsewhere in the chain: searches walk past tombstones
+    for k in keys[:1000]:
+        t.evict(int(k))
+    for k in keys[:1000]:
+        assert t.search(int(k)) == 0xFFFFFFFF
+    for k in keys[1000:1500]:
+        assert t.search(int(k)) != 0xFFFFFFFF
+    for k in keys[:200]:
+        t.insert(int(k), 7)
+        assert t.buckets[t.search(int(k))]["val"] == 7
+    rec = t.lookup(np.concatenate([keys[:10], absent[:10]]).astype(np.int64), fallback_loc=8)
+    assert (rec["loc"][10:] == 8).all() and (rec["off"][10:] == absent[:10]).all()
+
+
+def test_records_gather_equals_plain_gather():
+    case = dict(N=5000, dim=16, dtype="float32", G=4, pct=0.1, alpha=1.2, n_keys=3000,
+                policy="intuitive", seed=5, dedup=False)
+    w = case_workload(case, oracle_solver)
+    for r in range(4):
+        words, cnt, slot_of = orc.model_build(w.placement, r, w.capacity)
+        # per-GPU slices as the model places them
+        slices = []
+        for g in range(4):
+            sl = np.zeros((w.capacity, w.dim), dtype=np.float32)
+            own = np.nonzero(slot_of[g] != 0xFFFFFFFF)[0]
+            sl[slot_of[g][own]] = w.table[own]
+            slices.append(sl)
+        keys = w.keys(rank=r)
+        rec = orc.lookup_flat(words, keys, fallback_loc=4)
+        out = orc.extract_records(rec, slices + [w.table], w.row_bytes)
+        assert (out.view(np.float32) == orc.gather(w.table, keys)).all()
+
+
+def test_golden_cases(golden_cases):
+    for case in golden_cases:
+        w = case_workload(case, oracle_solver)
+        assert digest(w.table) == case["table"], case["name"]
+        assert digest(orc.gen_rows(case["seed"], 0, 64, case["dim"], np.dtype(case["dtype"]))) \
+            == case["table_head"]
+        assert digest(w.placement.nid_to_block) + digest(w.placement.block_access_from) \
+            == case["placement"]
+        for r, want in case["ranks"].items():
+            keys = w.keys(rank=int(r))
+            assert digest(keys) == want["keys"]
+            words, cnt, _ = orc.model_build(w.placement, int(r), w.capacity)
+            assert digest(words) == want["words"]
+            assert [int(x) for x in cnt] == want["per_src"]
+            assert digest(orc.gather(w.table, keys)) == want["out"]
+
+
+def test_refresh_slot_model():
+    N, G = 4000, 2
+    ids = np.arange(N, dtype=np.uint32)
+    old = orc.solve_rep(G, ids, 10.0)
+    new = orc.solve_rep(G, np.roll(ids, 100), 10.0)
+    cap = orc.cache_capacity(N, 0.10)
+    _, _, slot_of = orc.model_build(old, 0, cap)
+    slots = slot_of[0].copy()
+    free = np.arange(int((slots != 0xFFFFFFFF).sum()), cap, dtype=np.uint32)
+    free2, ev, ins = orc.model_refresh_slots(0, old, new, slots, free)
+    assert ev == 100 and ins == 100
+    stored = np.nonzero(new.block_placement[new.nid_to_block] & 1)[0]
+    assert (slots[stored] != 0xFFFFFFFF).all()
+    assert len(np.unique(slots[stored])) == len(stored)
+    assert len(free2) == len(free)
+
+
+def test_empty_and_ragged_gather():
+    t = orc.gen_rows(3, 0, 100, 8)
+    assert orc.gather(t, np.zeros(0, dtype=np.int64)).shape == (0, 8)
+    for n in (1, 7, 33):
+        k = np.arange(n, dtype=np.int64) * 3 % 100
+        assert (orc.gather(t, k) == t[k]).all()
+    assert (orc.gather(t, np.array([5, 69]), empty_feat=6) == t[[5, 5]]).all()

@@ -1,0 +1,137 @@
+"""ctypes binding of ``libugache_b200.so`` (the C ABI declared in include/ugache_b200.h).
+
+Loading fails loudly when the shared library is missing: there is no CPU fallback.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libugache_b200.so")
+
+UGC_MAX_DEVICE = 8
+UGC_OK = 0
+POLICY_INTUITIVE, POLICY_REP, POLICY_CLIQUE_PART = 9, 12, 14
+TABLE_AUTO, TABLE_FLAT, TABLE_HASHED = 0, 1, 2
+
+ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_size_t, C.c_void_p)
+FREE_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)
+
+
+class Config(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("num_device", C.c_int32),
+        ("num_total_item", C.c_uint64),
+        ("row_bytes", C.c_uint32),
+        ("cache_percentage", C.c_double),
+        ("empty_feat", C.c_int32),
+        ("table_kind", C.c_int32),
+        ("max_batch", C.c_uint32),
+        ("register_host", C.c_int32),
+        ("bw_local_gbs", C.c_double),
+        ("bw_remote_gbs", C.c_double),
+        ("bw_host_gbs", C.c_double),
+        ("gather_ctas_per_sm", C.c_int32),
+        ("host_ctas", C.c_int32),
+        ("remote_ctas", C.c_int32),
+        ("alloc", ALLOC_FN),
+        ("free", FREE_FN),
+        ("alloc_user", C.c_void_p),
+    ]
+
+
+class PeerHandle(C.Structure):
+    _fields_ = [
+        ("replica_id", C.c_int32),
+        ("device_id", C.c_int32),
+        ("pid", C.c_int64),
+        ("slice_ptr", C.c_uint64),
+        ("table_ptr", C.c_uint64),
+        ("table_lines", C.c_uint64),
+        ("table_kind", C.c_int32),
+        ("has_ipc", C.c_int32),
+        ("slice_ipc", C.c_ubyte * 64),
+        ("table_ipc", C.c_ubyte * 64),
+    ]
+
+
+class Stats(C.Structure):
+    _fields_ = [
+        ("num_local_rows", C.c_uint64),
+        ("num_remote_keys", C.c_uint64),
+        ("num_host_keys", C.c_uint64),
+        ("capacity_rows", C.c_uint64),
+        ("free_rows", C.c_uint64),
+        ("table_kind", C.c_int32),
+        ("table_bytes", C.c_uint64),
+        ("slice_bytes", C.c_uint64),
+        ("last_keys", C.c_uint64),
+        ("last_local", C.c_uint64),
+        ("last_remote", C.c_uint64),
+        ("last_host", C.c_uint64),
+        ("err_key_range", C.c_uint64),
+        ("err_table", C.c_uint64),
+        ("lookups", C.c_uint64),
+    ]
+
+
+class UgcError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__("ugache_b200 status %d: %s" % (status, message))
+        self.status = status
+
+
+_lib = None
+
+# name -> (restype, argtypes); every symbol include/ugache_b200.h declares
+_P, _I, _U64, _SZ, _D = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t, C.c_double
+SIGNATURES = {
+    "ugc_version": (C.c_char_p, []),
+    "ugc_last_error": (C.c_char_p, []),
+    "ugc_status_string": (C.c_char_p, [_I]),
+    "ugc_config_default": (_I, [C.POINTER(Config)]),
+    "ugc_create": (_I, [C.POINTER(Config), C.POINTER(_P)]),
+    "ugc_destroy": (_I, [_P]),
+    "ugc_solve_placement": (_I, [_I, _I, _U64, _P, _P, _D, _D, _D, _D, _P, _P, _P, _P,
+                                 C.POINTER(_I)]),
+    "ugc_link_model": (_I, [_I, C.POINTER(_D), C.POINTER(_D), C.POINTER(_D)]),
+    "ugc_set_placement": (_I, [_P, _P, _P, _P, _P, _I]),
+    "ugc_classify_keys": (_I, [_P, _I, _P, _P]),
+    "ugc_build": (_I, [_P, _I, _I, _P, _P]),
+    "ugc_export": (_I, [_P, _I, C.POINTER(PeerHandle)]),
+    "ugc_import_peer": (_I, [_P, _I, C.POINTER(PeerHandle)]),
+    "ugc_connect_local": (_I, [_P]),
+    "ugc_attach_peers": (_I, [_P, _I, _P]),
+    "ugc_lookup_u32": (_I, [_P, _I, _P, _SZ, _P, _P]),
+    "ugc_lookup_i64": (_I, [_P, _I, _P, _SZ, _P, _P]),
+    "ugc_lookup_host": (_I, [_P, _I, _P, _I, _SZ, _P, _P]),
+    "ugc_refresh_set_placement": (_I, [_P, _P, _P, _P, _P, _I]),
+    "ugc_refresh_evict": (_I, [_P, _I, _P]),
+    "ugc_refresh_fill": (_I, [_P, _I, _P]),
+    "ugc_refresh_attach": (_I, [_P, _I, _P]),
+    "ugc_refresh_commit": (_I, [_P]),
+    "ugc_stats": (_I, [_P, _I, C.POINTER(Stats)]),
+    "ugc_table_words": (_I, [_P, _I, _P, _SZ, _P, _P]),
+    "ugc_gen_table": (_I, [_P, _U64, _U64, _U64, _U64, _I, _P]),
+}
+
+
+def lib():
+    """The loaded shared library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                "libugache_b200.so is missing (%s): build it with "
+                "`python -m ugache_b200.build`; there is no CPU fallback" % LIB_PATH)
+        _lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(_lib, name)
+            fn.restype = res
+            fn.argtypes = args
+    return _lib
+
+
+def check(status):
+    if status != UGC_OK:
+        raise UgcError(status, lib().ugc_last_error().decode())

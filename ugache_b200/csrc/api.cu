@@ -1,0 +1,878 @@
+// C ABI of the extraction path: context, build, peer exchange, lookup, refresh, stats.
+// Host runtime in C++; device work in kernels.cu.  Nothing here throws across the ABI or
+// aborts: every entry point returns a ugc_status and records a per-thread message.
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <deque>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/ugache_b200.h"
+#include "device_types.h"
+#include "kernels.cuh"
+#include "placement.h"
+
+using namespace ugc;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+#define UGC_CUDA(expr)                                                                        \
+  do {                                                                                        \
+    cudaError_t e__ = (expr);                                                                 \
+    if (e__ != cudaSuccess)                                                                   \
+      return fail(UGC_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__),     \
+                  __FILE__, __LINE__);                                                        \
+  } while (0)
+
+#define UGC_TRY(expr)              \
+  do {                             \
+    int rc__ = (expr);             \
+    if (rc__ != UGC_OK) return rc__; \
+  } while (0)
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+uint64_t pow2_ceil(uint64_t v) {
+  uint64_t p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+// A device buffer that grows on demand through the context's allocator.
+struct DevBuf {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+struct Replica {
+  bool built = false;
+  bool attached = false;
+  int id = -1;
+  int device = -1;
+  int sm_count = 148;
+  // cache slice
+  void* slice = nullptr;
+  uint64_t capacity = 0;
+  size_t slice_bytes = 0;
+  // table
+  TableView table{};
+  void* table_mem = nullptr;
+  size_t table_bytes = 0;
+  uint64_t table_entry_cap = 0;  // hashed: entries the table is sized for
+  // sources, as seen from this replica's device
+  const void* src_base[kMaxLocation] = {nullptr};
+  TableView peer_table[kMaxDevice] = {};
+  bool peer_known[kMaxDevice] = {false};
+  void* ipc_opened[2 * kMaxDevice] = {nullptr};
+  int n_ipc_opened = 0;
+  // lookup scratch
+  uint64_t* list[kNumGroup] = {nullptr, nullptr, nullptr};
+  Counters* counters = nullptr;
+  uint32_t max_batch = 0;
+  // host-buffer lookups
+  DevBuf stage_keys, stage_out;
+  // build / refresh staging
+  DevBuf stage_a, stage_b;
+  // bookkeeping mirrored from the reference's CacheEntryManager
+  // (coll_cache_lib/cuda/cache_hashtable.cuh:548-557): keys per source, free slots
+  std::vector<uint32_t> keys_by_src[kMaxDevice];
+  std::deque<uint32_t> free_slots;
+  // refresh in flight
+  std::vector<uint32_t> next_keys_by_src[kMaxDevice];
+  std::vector<uint32_t> pending_insert;
+  bool refresh_open = false;
+  uint64_t counts[kMaxLocation] = {0};
+  uint64_t lookups = 0;
+  int gather_grid = 0;
+  int host_ctas = 0, remote_ctas = 0;
+};
+
+}  // namespace
+
+struct ugc_ctx {
+  ugc_config cfg;
+  Placement cur, next;
+  std::vector<Replica> reps;
+  const void* host_table = nullptr;
+  const void* host_dev = nullptr;
+  bool host_registered_here = false;
+  std::mutex mu;
+};
+
+namespace {
+
+void* ctx_alloc(ugc_ctx* c, size_t bytes) {
+  bytes = round_up(std::max<size_t>(bytes, 256), 256);
+  if (c->cfg.alloc) return c->cfg.alloc(bytes, c->cfg.alloc_user);
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+void ctx_free(ugc_ctx* c, void* p) {
+  if (!p) return;
+  if (c->cfg.free) {
+    c->cfg.free(p, c->cfg.alloc_user);
+  } else if (!c->cfg.alloc) {
+    cudaFree(p);
+  }
+}
+
+int ensure(ugc_ctx* c, DevBuf& b, size_t bytes) {
+  if (b.bytes >= bytes) return UGC_OK;
+  ctx_free(c, b.ptr);
+  b.ptr = ctx_alloc(c, bytes);
+  b.bytes = b.ptr ? round_up(std::max<size_t>(bytes, 256), 256) : 0;
+  if (!b.ptr) return fail(UGC_ERR_NOMEM, "device allocation of %zu bytes failed", bytes);
+  return UGC_OK;
+}
+
+int get_replica(ugc_ctx* c, int id, bool need_built, Replica** out) {
+  if (!c) return fail(UGC_ERR_INVALID, "null context");
+  if (id < 0 || id >= c->cfg.num_device)
+    return fail(UGC_ERR_INVALID, "replica_id %d outside [0, %d)", id, c->cfg.num_device);
+  Replica* r = &c->reps[id];
+  if (need_built && !r->built) return fail(UGC_ERR_STATE, "replica %d has not been built", id);
+  *out = r;
+  return UGC_OK;
+}
+
+// Device-visible address of the caller's host table.
+int map_host_table(ugc_ctx* c, const void* host_table) {
+  if (c->host_table == host_table && c->host_dev) return UGC_OK;
+  const uint64_t rows = c->cfg.empty_feat > 0 ? ((uint64_t)1 << c->cfg.empty_feat)
+                                               : c->cfg.num_total_item;
+  const size_t bytes = (size_t)rows * c->cfg.row_bytes;
+  void* dptr = nullptr;
+  cudaError_t e = cudaHostGetDevicePointer(&dptr, const_cast<void*>(host_table), 0);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (!c->cfg.register_host)
+      return fail(UGC_ERR_INVALID,
+                  "host table is not GPU-visible (pin it, or set register_host): %s",
+                  cudaGetErrorString(e));
+    // The reference registers the table read-only (coll_cache_lib/facade.cc:476); not every
+    // platform takes that flag, so fall back to a plain mapped registration.
+    e = cudaHostRegister(const_cast<void*>(host_table), bytes,
+                         cudaHostRegisterPortable | cudaHostRegisterMapped |
+                             cudaHostRegisterReadOnly);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      e = cudaHostRegister(const_cast<void*>(host_table), bytes,
+                           cudaHostRegisterPortable | cudaHostRegisterMapped);
+    }
+    if (e != cudaSuccess)
+      return fail(UGC_ERR_CUDA, "cudaHostRegister of %zu bytes failed: %s", bytes,
+                  cudaGetErrorString(e));
+    c->host_registered_here = true;
+    UGC_CUDA(cudaHostGetDevicePointer(&dptr, const_cast<void*>(host_table), 0));
+  }
+  c->host_table = host_table;
+  c->host_dev = dptr;
+  return UGC_OK;
+}
+
+int read_counters(Replica* r, Counters* out) {
+  UGC_CUDA(cudaMemcpy(out, r->counters, sizeof(Counters), cudaMemcpyDeviceToHost));
+  return UGC_OK;
+}
+
+// Synchronises the stream and turns device-side table errors into a status.
+int check_table_errors(Replica* r, cudaStream_t s, const char* what) {
+  UGC_CUDA(cudaStreamSynchronize(s));
+  Counters h;
+  UGC_TRY(read_counters(r, &h));
+  if (h.err_table)
+    return fail(UGC_ERR_TABLE, "%s: %llu table operations failed on replica %d", what,
+                (unsigned long long)h.err_table, r->id);
+  return UGC_OK;
+}
+
+int upload_u32(ugc_ctx* c, DevBuf& buf, const uint32_t* src, size_t n, cudaStream_t s) {
+  UGC_TRY(ensure(c, buf, n * sizeof(uint32_t)));
+  if (n) UGC_CUDA(cudaMemcpyAsync(buf.ptr, src, n * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+  return UGC_OK;
+}
+
+int alloc_table(ugc_ctx* c, Replica* r, uint64_t entries, cudaStream_t s) {
+  const uint64_t N = c->cfg.num_total_item;
+  int kind = c->cfg.table_kind;
+  if (kind == UGC_TABLE_AUTO)
+    kind = reference_prefers_flat_table(std::max<uint64_t>(entries, 2), N) ? UGC_TABLE_FLAT
+                                                                           : UGC_TABLE_HASHED;
+  r->table = TableView{};
+  r->table.num_keys = N;
+  if (kind == UGC_TABLE_FLAT) {
+    r->table.kind = kTableFlat;
+    r->table_bytes = round_up((size_t)N * 4, 256);
+    r->table_entry_cap = N;
+  } else {
+    // 4-slot lines; slots = 2 * pow2_ceil(entries): load factor 25..50 %.
+    uint64_t lines = std::max<uint64_t>(pow2_ceil(std::max<uint64_t>(entries, 1)) / 2, 64);
+    if (lines > (1ull << 31)) return fail(UGC_ERR_UNSUPPORTED, "hashed table too large");
+    r->table.kind = kTableHashed;
+    r->table.line_mask = (uint32_t)(lines - 1);
+    r->table_bytes = (size_t)lines * kSlotsPerLine * sizeof(uint2);
+    r->table_entry_cap = lines * 2;
+  }
+  r->table_mem = ctx_alloc(c, r->table_bytes);
+  if (!r->table_mem) return fail(UGC_ERR_NOMEM, "table allocation of %zu bytes failed", r->table_bytes);
+  if (r->table.kind == kTableFlat) {
+    r->table.flat = static_cast<uint32_t*>(r->table_mem);
+  } else {
+    r->table.slots = static_cast<uint2*>(r->table_mem);
+  }
+  UGC_CUDA(launch_table_clear(r->table, s));
+  return UGC_OK;
+}
+
+void release_replica(ugc_ctx* c, Replica* r) {
+  if (r->device >= 0) cudaSetDevice(r->device);
+  for (int i = 0; i < r->n_ipc_opened; i++) cudaIpcCloseMemHandle(r->ipc_opened[i]);
+  ctx_free(c, r->slice);
+  ctx_free(c, r->table_mem);
+  for (auto& l : r->list) ctx_free(c, l);
+  ctx_free(c, r->counters);
+  ctx_free(c, r->stage_keys.ptr);
+  ctx_free(c, r->stage_out.ptr);
+  ctx_free(c, r->stage_a.ptr);
+  ctx_free(c, r->stage_b.ptr);
+  *r = Replica{};
+}
+
+GatherParams gather_params(ugc_ctx* c, Replica* r, void* out, uint32_t n) {
+  GatherParams p{};
+  for (int i = 0; i < kMaxLocation; i++) p.src_base[i] = r->src_base[i];
+  p.out = out;
+  for (int g = 0; g < kNumGroup; g++) p.list[g] = r->list[g];
+  p.counters = r->counters;
+  p.row_bytes = c->cfg.row_bytes;
+  p.n_keys = n;
+  p.remote_cta_cap = r->remote_ctas;
+  p.host_cta_cap = r->host_ctas;
+  p.rows_per_cta_min = 32;
+  return p;
+}
+
+int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n, void* out,
+              cudaStream_t s) {
+  if (n == 0) return UGC_OK;
+  if (!keys || !out) return fail(UGC_ERR_INVALID, "keys and out must be non-null");
+  if (n > r->max_batch)
+    return fail(UGC_ERR_INVALID, "batch of %zu keys exceeds max_batch %u", n, r->max_batch);
+  if (c->cfg.num_device > 1 && !r->attached) {
+    for (int s2 = 0; s2 < c->cfg.num_device; s2++)
+      if (s2 != r->id && !r->keys_by_src[s2].empty())
+        return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
+  }
+  UGC_CUDA(launch_lookup_group(keys, key_bytes, (uint32_t)n, r->table, (uint32_t)r->id,
+                               (uint32_t)c->cfg.num_device, c->cfg.empty_feat, r->list[kGroupLocal],
+                               r->list[kGroupRemote], r->list[kGroupHost], r->counters, s));
+  GatherParams p = gather_params(c, r, out, (uint32_t)n);
+  UGC_CUDA(launch_gather_roles(p, r->gather_grid, 16, s));
+  r->lookups++;
+  return UGC_OK;
+}
+
+}  // namespace
+
+// --------------------------------------------------------------------------------------
+extern "C" {
+
+const char* ugc_version(void) { return "ugache_b200 0.1 (sm_100a)"; }
+const char* ugc_last_error(void) { return g_last_error.c_str(); }
+
+const char* ugc_status_string(int s) {
+  switch (s) {
+    case UGC_OK: return "ok";
+    case UGC_ERR_INVALID: return "invalid argument";
+    case UGC_ERR_CUDA: return "CUDA error";
+    case UGC_ERR_NOMEM: return "out of device memory";
+    case UGC_ERR_CAPACITY: return "cache capacity exceeded";
+    case UGC_ERR_STATE: return "call out of order";
+    case UGC_ERR_KEY_RANGE: return "key out of range";
+    case UGC_ERR_TIMEOUT: return "timed out";
+    case UGC_ERR_UNSUPPORTED: return "unsupported configuration";
+    case UGC_ERR_TABLE: return "table inconsistency";
+    default: return "unknown status";
+  }
+}
+
+int ugc_config_default(ugc_config* cfg) {
+  if (!cfg) return fail(UGC_ERR_INVALID, "null config");
+  memset(cfg, 0, sizeof(*cfg));
+  cfg->struct_size = sizeof(*cfg);
+  cfg->num_device = 1;
+  cfg->max_batch = 1u << 20;
+  cfg->register_host = 1;
+  return UGC_OK;
+}
+
+int ugc_create(const ugc_config* cfg, ugc_ctx** out) {
+  if (!cfg || !out) return fail(UGC_ERR_INVALID, "null argument");
+  if (cfg->struct_size != sizeof(ugc_config))
+    return fail(UGC_ERR_INVALID, "ugc_config.struct_size %u != %zu", cfg->struct_size, sizeof(ugc_config));
+  if (cfg->num_device < 1 || cfg->num_device > UGC_MAX_DEVICE)
+    return fail(UGC_ERR_INVALID, "num_device must be 1..%d", UGC_MAX_DEVICE);
+  if (cfg->num_total_item == 0 || cfg->num_total_item >= 0x7fffffffull)
+    return fail(UGC_ERR_UNSUPPORTED, "num_total_item must be in [1, 2^31-1)");
+  if (cfg->row_bytes == 0 || cfg->row_bytes % 4 != 0)
+    return fail(UGC_ERR_UNSUPPORTED, "row_bytes must be a positive multiple of 4");
+  if (cfg->cache_percentage < 0 || cfg->cache_percentage > 1)
+    return fail(UGC_ERR_INVALID, "cache_percentage is a fraction in [0, 1]");
+  if (cfg->empty_feat < 0 || cfg->empty_feat > 31)
+    return fail(UGC_ERR_INVALID, "empty_feat must be in [0, 31]");
+  if (cfg->max_batch == 0 || cfg->max_batch > kMaxBatch)
+    return fail(UGC_ERR_INVALID, "max_batch must be in [1, 2^28]");
+  if ((cfg->alloc == nullptr) != (cfg->free == nullptr) && cfg->free != nullptr)
+    return fail(UGC_ERR_INVALID, "a free callback needs an alloc callback");
+  if (cache_capacity_rows(cfg->num_total_item, cfg->cache_percentage) > (uint64_t)kOffMask)
+    return fail(UGC_ERR_UNSUPPORTED, "a cache slice holds at most 2^28-1 rows");
+  ugc_ctx* c = new (std::nothrow) ugc_ctx();
+  if (!c) return fail(UGC_ERR_NOMEM, "out of host memory");
+  c->cfg = *cfg;
+  c->reps.resize(cfg->num_device);
+  *out = c;
+  return UGC_OK;
+}
+
+int ugc_destroy(ugc_ctx* c) {
+  if (!c) return UGC_OK;
+  for (auto& r : c->reps)
+    if (r.built) release_replica(c, &r);
+  if (c->host_registered_here && c->host_table) cudaHostUnregister(const_cast<void*>(c->host_table));
+  delete c;
+  return UGC_OK;
+}
+
+int ugc_solve_placement(int policy, int num_device, uint64_t N, const uint32_t* rank_ids,
+                        const uint32_t* rank_freqs, double cache_percent, double t_local,
+                        double t_remote, double t_cpu, uint32_t* nid_to_block,
+                        uint8_t* block_placement, uint8_t* block_access_from, double* block_density,
+                        int* num_block) {
+  if (!nid_to_block || !block_placement || !block_access_from || !block_density || !num_block)
+    return fail(UGC_ERR_INVALID, "null output array");
+  Placement p;
+  std::string err = solve_placement(policy, num_device, N, rank_ids, rank_freqs, cache_percent,
+                                    t_local, t_remote, t_cpu, &p);
+  if (!err.empty()) return fail(UGC_ERR_INVALID, "%s", err.c_str());
+  memcpy(nid_to_block, p.nid_to_block.data(), N * sizeof(uint32_t));
+  memcpy(block_placement, p.block_placement.data(), p.num_block);
+  memcpy(block_access_from, p.block_access_from.data(), (size_t)num_device * p.num_block);
+  memcpy(block_density, p.block_density.data(), p.num_block * sizeof(double));
+  *num_block = p.num_block;
+  return UGC_OK;
+}
+
+int ugc_link_model(int num_device, double* t_local, double* t_remote, double* t_cpu) {
+  if (!t_local || !t_remote || !t_cpu) return fail(UGC_ERR_INVALID, "null output");
+  b200_link_model(num_device, t_local, t_remote, t_cpu);
+  return UGC_OK;
+}
+
+static int load_placement(ugc_ctx* c, Placement* dst, const uint32_t* n2b, const uint8_t* bp,
+                          const uint8_t* ba, const double* bd, int B) {
+  if (!c) return fail(UGC_ERR_INVALID, "null context");
+  if (!n2b || !bp || !ba || B <= 0) return fail(UGC_ERR_INVALID, "null placement array");
+  const int G = c->cfg.num_device;
+  const uint64_t N = c->cfg.num_total_item;
+  Placement p;
+  p.num_block = B;
+  p.num_device = G;
+  p.nid_to_block.assign(n2b, n2b + N);
+  p.block_placement.assign(bp, bp + B);
+  p.block_access_from.assign(ba, ba + (size_t)G * B);
+  if (bd) p.block_density.assign(bd, bd + B);
+  std::string err = validate_placement(p, G, N);
+  if (!err.empty()) return fail(UGC_ERR_INVALID, "placement rejected: %s", err.c_str());
+  p.valid = true;
+  *dst = std::move(p);
+  return UGC_OK;
+}
+
+int ugc_set_placement(ugc_ctx* c, const uint32_t* n2b, const uint8_t* bp, const uint8_t* ba,
+                      const double* bd, int B) {
+  if (c)
+    for (auto& r : c->reps)
+      if (r.built) return fail(UGC_ERR_STATE, "replicas are built: use the refresh calls");
+  return load_placement(c, c ? &c->cur : nullptr, n2b, bp, ba, bd, B);
+}
+
+int ugc_classify_keys(ugc_ctx* c, int replica_id, uint64_t* counts, uint32_t* keys_out) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, false, &r));
+  if (!c->cur.valid) return fail(UGC_ERR_STATE, "no placement set");
+  if (!counts) return fail(UGC_ERR_INVALID, "null counts");
+  std::vector<uint32_t> lists[kMaxDevice];
+  classify_keys(c->cur, replica_id, c->cfg.num_total_item, lists, counts);
+  if (keys_out) {
+    size_t pos = 0;
+    for (int s = 0; s < c->cfg.num_device; s++) {
+      memcpy(keys_out + pos, lists[s].data(), lists[s].size() * sizeof(uint32_t));
+      pos += lists[s].size();
+    }
+  }
+  return UGC_OK;
+}
+
+int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, false, &r));
+  if (r->built) return fail(UGC_ERR_STATE, "replica %d is already built", replica_id);
+  if (!c->cur.valid) return fail(UGC_ERR_STATE, "no placement set");
+  if (!host_table) return fail(UGC_ERR_INVALID, "null host table");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int G = c->cfg.num_device;
+  const uint64_t N = c->cfg.num_total_item;
+  UGC_CUDA(cudaSetDevice(device_id));
+  {
+    std::lock_guard<std::mutex> lock(c->mu);
+    UGC_TRY(map_host_table(c, host_table));
+  }
+  r->id = replica_id;
+  r->device = device_id;
+  cudaDeviceProp prop;
+  UGC_CUDA(cudaGetDeviceProperties(&prop, device_id));
+  r->sm_count = prop.multiProcessorCount;
+  const int per_sm = c->cfg.gather_ctas_per_sm > 0 ? c->cfg.gather_ctas_per_sm : 4;
+  r->gather_grid = r->sm_count * per_sm;
+  r->host_ctas = c->cfg.host_ctas > 0 ? c->cfg.host_ctas : std::max(2, r->sm_count / 8);
+  r->remote_ctas = c->cfg.remote_ctas > 0 ? c->cfg.remote_ctas : std::max(2, r->sm_count * per_sm / 4);
+
+  // 1. which source serves each key (ascending key lists per GPU source)
+  classify_keys(c->cur, replica_id, N, r->keys_by_src, r->counts);
+  const uint64_t n_local = r->keys_by_src[replica_id].size();
+  uint64_t n_remote = 0;
+  for (int s2 = 0; s2 < G; s2++)
+    if (s2 != replica_id) n_remote += r->keys_by_src[s2].size();
+
+  // 2. the slice
+  r->capacity = cache_capacity_rows(N, c->cfg.cache_percentage);
+  if (n_local > r->capacity) {
+    int rc = fail(UGC_ERR_CAPACITY, "placement stores %llu rows on replica %d, slice holds %llu",
+                  (unsigned long long)n_local, replica_id, (unsigned long long)r->capacity);
+    release_replica(c, r);
+    return rc;
+  }
+  r->slice_bytes = std::max<size_t>((size_t)r->capacity * c->cfg.row_bytes, 256);
+  r->slice = ctx_alloc(c, r->slice_bytes);
+  if (!r->slice) {
+    int rc = fail(UGC_ERR_NOMEM, "slice allocation of %zu bytes failed", r->slice_bytes);
+    release_replica(c, r);
+    return rc;
+  }
+  auto bail = [&](int rc) {
+    std::string keep = g_last_error;
+    release_replica(c, r);
+    g_last_error = keep;
+    return rc;
+  };
+  int rc;
+  // 3. lookup scratch and counters
+  r->max_batch = c->cfg.max_batch;
+  for (int g = 0; g < kNumGroup; g++) {
+    r->list[g] = static_cast<uint64_t*>(ctx_alloc(c, (size_t)r->max_batch * sizeof(uint64_t)));
+    if (!r->list[g]) return bail(fail(UGC_ERR_NOMEM, "scratch allocation failed"));
+  }
+  r->counters = static_cast<Counters*>(ctx_alloc(c, sizeof(Counters)));
+  if (!r->counters) return bail(fail(UGC_ERR_NOMEM, "counter allocation failed"));
+  if (cudaMemsetAsync(r->counters, 0, sizeof(Counters), s) != cudaSuccess)
+    return bail(fail(UGC_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(cudaGetLastError())));
+
+  // 4. fill: slice[j] = host[local_keys[j]]
+  if ((rc = upload_u32(c, r->stage_a, r->keys_by_src[replica_id].data(), n_local, s)) != UGC_OK)
+    return bail(rc);
+  if (launch_fill_scatter(c->host_dev, r->slice, static_cast<uint32_t*>(r->stage_a.ptr), nullptr, 0,
+                          (uint32_t)n_local, c->cfg.row_bytes, c->cfg.empty_feat, r->sm_count * 2,
+                          s) != cudaSuccess)
+    return bail(fail(UGC_ERR_CUDA, "fill launch failed: %s", cudaGetErrorString(cudaGetLastError())));
+
+  // 5. table with the local entries (slot = position in the list)
+  if ((rc = alloc_table(c, r, n_local + n_remote, s)) != UGC_OK) return bail(rc);
+  if (launch_table_insert(r->table, static_cast<uint32_t*>(r->stage_a.ptr), nullptr, 0,
+                          (uint32_t)replica_id, (uint32_t)n_local, r->counters, s) != cudaSuccess)
+    return bail(fail(UGC_ERR_CUDA, "insert launch failed: %s", cudaGetErrorString(cudaGetLastError())));
+  if ((rc = check_table_errors(r, s, "build insert")) != UGC_OK) return bail(rc);
+
+  // 6. free slots: [n_local, capacity)  (coll_cache_lib/cache_context.cu:2577-2585)
+  r->free_slots.clear();
+  for (uint64_t o = n_local; o < r->capacity; o++) r->free_slots.push_back((uint32_t)o);
+
+  r->src_base[replica_id] = r->slice;
+  r->src_base[G] = c->host_dev;
+  r->attached = (n_remote == 0);
+  r->built = true;
+  return UGC_OK;
+}
+
+int ugc_export(ugc_ctx* c, int replica_id, ugc_peer_handle* out) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (!out) return fail(UGC_ERR_INVALID, "null handle");
+  memset(out, 0, sizeof(*out));
+  out->replica_id = r->id;
+  out->device_id = r->device;
+  out->pid = (int64_t)getpid();
+  out->slice_ptr = (uint64_t)(uintptr_t)r->slice;
+  out->table_ptr = (uint64_t)(uintptr_t)r->table_mem;
+  out->table_kind = r->table.kind;
+  out->table_lines = r->table.kind == kTableFlat ? r->table.num_keys : (uint64_t)r->table.line_mask + 1;
+  // IPC handles only describe whole cudaMalloc allocations; with a caller-supplied allocator
+  // the pointers may sit inside a larger block, so cross-process export needs the built-in
+  // allocator.
+  if (!c->cfg.alloc) {
+    UGC_CUDA(cudaSetDevice(r->device));
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    UGC_CUDA(cudaIpcGetMemHandle(&h, r->slice));
+    memcpy(out->slice_ipc, &h, 64);
+    UGC_CUDA(cudaIpcGetMemHandle(&h, r->table_mem));
+    memcpy(out->table_ipc, &h, 64);
+    out->has_ipc = 1;
+  }
+  return UGC_OK;
+}
+
+static TableView view_from_handle(const ugc_peer_handle* h, void* table_ptr, uint64_t N) {
+  TableView t{};
+  t.kind = h->table_kind;
+  t.num_keys = N;
+  if (t.kind == kTableFlat) {
+    t.flat = static_cast<uint32_t*>(table_ptr);
+  } else {
+    t.slots = static_cast<uint2*>(table_ptr);
+    t.line_mask = (uint32_t)(h->table_lines - 1);
+  }
+  return t;
+}
+
+static int enable_peer(int from_dev, int to_dev) {
+  if (from_dev == to_dev) return UGC_OK;
+  UGC_CUDA(cudaSetDevice(from_dev));
+  int can = 0;
+  UGC_CUDA(cudaDeviceCanAccessPeer(&can, from_dev, to_dev));
+  if (!can) return fail(UGC_ERR_UNSUPPORTED, "device %d cannot access device %d", from_dev, to_dev);
+  cudaError_t e = cudaDeviceEnablePeerAccess(to_dev, 0);
+  if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+    return fail(UGC_ERR_CUDA, "cudaDeviceEnablePeerAccess(%d) failed: %s", to_dev, cudaGetErrorString(e));
+  cudaGetLastError();
+  return UGC_OK;
+}
+
+int ugc_import_peer(ugc_ctx* c, int replica_id, const ugc_peer_handle* peer) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (!peer) return fail(UGC_ERR_INVALID, "null handle");
+  const int p = peer->replica_id;
+  if (p < 0 || p >= c->cfg.num_device || p == replica_id)
+    return fail(UGC_ERR_INVALID, "bad peer replica id %d", p);
+  void* slice = nullptr;
+  void* table = nullptr;
+  if (peer->pid == (int64_t)getpid()) {
+    UGC_TRY(enable_peer(r->device, peer->device_id));
+    slice = (void*)(uintptr_t)peer->slice_ptr;
+    table = (void*)(uintptr_t)peer->table_ptr;
+  } else {
+    if (!peer->has_ipc) return fail(UGC_ERR_INVALID, "peer handle from another process carries no IPC handles");
+    UGC_CUDA(cudaSetDevice(r->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, peer->slice_ipc, 64);
+    UGC_CUDA(cudaIpcOpenMemHandle(&slice, h, cudaIpcMemLazyEnablePeerAccess));
+    r->ipc_opened[r->n_ipc_opened++] = slice;
+    memcpy(&h, peer->table_ipc, 64);
+    UGC_CUDA(cudaIpcOpenMemHandle(&table, h, cudaIpcMemLazyEnablePeerAccess));
+    r->ipc_opened[r->n_ipc_opened++] = table;
+  }
+  r->src_base[p] = slice;
+  r->peer_table[p] = view_from_handle(peer, table, c->cfg.num_total_item);
+  r->peer_known[p] = true;
+  return UGC_OK;
+}
+
+int ugc_connect_local(ugc_ctx* c) {
+  if (!c) return fail(UGC_ERR_INVALID, "null context");
+  for (auto& a : c->reps) {
+    if (!a.built) continue;
+    for (auto& b : c->reps) {
+      if (!b.built || a.id == b.id) continue;
+      ugc_peer_handle h;
+      memset(&h, 0, sizeof(h));
+      h.replica_id = b.id;
+      h.device_id = b.device;
+      h.pid = (int64_t)getpid();
+      h.slice_ptr = (uint64_t)(uintptr_t)b.slice;
+      h.table_ptr = (uint64_t)(uintptr_t)b.table_mem;
+      h.table_kind = b.table.kind;
+      h.table_lines = b.table.kind == kTableFlat ? b.table.num_keys : (uint64_t)b.table.line_mask + 1;
+      UGC_TRY(ugc_import_peer(c, a.id, &h));
+    }
+  }
+  return UGC_OK;
+}
+
+// Resolve the slots of `keys` (all served by `src`) from src's table and insert them.
+static int attach_keys(ugc_ctx* c, Replica* r, int src, const std::vector<uint32_t>& keys,
+                       cudaStream_t s) {
+  if (keys.empty()) return UGC_OK;
+  if (!r->peer_known[src] || !r->src_base[src])
+    return fail(UGC_ERR_STATE, "replica %d reads from replica %d, which has not been imported", r->id, src);
+  UGC_TRY(upload_u32(c, r->stage_a, keys.data(), keys.size(), s));
+  UGC_TRY(ensure(c, r->stage_b, keys.size() * sizeof(uint32_t)));
+  UGC_CUDA(launch_table_resolve(r->peer_table[src], static_cast<uint32_t*>(r->stage_a.ptr),
+                                (uint32_t)keys.size(), (uint32_t)src,
+                                static_cast<uint32_t*>(r->stage_b.ptr), r->counters, s));
+  UGC_CUDA(launch_table_insert(r->table, static_cast<uint32_t*>(r->stage_a.ptr),
+                               static_cast<uint32_t*>(r->stage_b.ptr), 0, (uint32_t)src,
+                               (uint32_t)keys.size(), r->counters, s));
+  // the staging buffers are reused by the next source
+  return check_table_errors(r, s, "peer attach");
+}
+
+int ugc_attach_peers(ugc_ctx* c, int replica_id, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  UGC_CUDA(cudaSetDevice(r->device));
+  for (int src = 0; src < c->cfg.num_device; src++) {
+    if (src == replica_id) continue;
+    UGC_TRY(attach_keys(c, r, src, r->keys_by_src[src], s));
+  }
+  r->attached = true;
+  return UGC_OK;
+}
+
+int ugc_lookup_u32(ugc_ctx* c, int replica_id, const uint32_t* keys, size_t n, void* out, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  UGC_CUDA(cudaSetDevice(r->device));
+  return do_lookup(c, r, keys, 4, n, out, static_cast<cudaStream_t>(stream));
+}
+
+int ugc_lookup_i64(ugc_ctx* c, int replica_id, const int64_t* keys, size_t n, void* out, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  UGC_CUDA(cudaSetDevice(r->device));
+  return do_lookup(c, r, keys, 8, n, out, static_cast<cudaStream_t>(stream));
+}
+
+int ugc_lookup_host(ugc_ctx* c, int replica_id, const void* keys, int key_bytes, size_t n, void* out,
+                    void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (key_bytes != 4 && key_bytes != 8) return fail(UGC_ERR_INVALID, "key_bytes must be 4 or 8");
+  if (n == 0) return UGC_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  UGC_CUDA(cudaSetDevice(r->device));
+  UGC_TRY(ensure(c, r->stage_keys, n * (size_t)key_bytes));
+  UGC_TRY(ensure(c, r->stage_out, n * (size_t)c->cfg.row_bytes));
+  UGC_CUDA(cudaMemcpyAsync(r->stage_keys.ptr, keys, n * (size_t)key_bytes, cudaMemcpyHostToDevice, s));
+  UGC_TRY(do_lookup(c, r, r->stage_keys.ptr, key_bytes, n, r->stage_out.ptr, s));
+  UGC_CUDA(cudaMemcpyAsync(out, r->stage_out.ptr, n * (size_t)c->cfg.row_bytes, cudaMemcpyDeviceToHost, s));
+  UGC_CUDA(cudaStreamSynchronize(s));
+  return UGC_OK;
+}
+
+// --------------------------------------------------------------------------------------
+// refresh
+// --------------------------------------------------------------------------------------
+int ugc_refresh_set_placement(ugc_ctx* c, const uint32_t* n2b, const uint8_t* bp, const uint8_t* ba,
+                              const double* bd, int B) {
+  if (c && !c->cur.valid) return fail(UGC_ERR_STATE, "no current placement");
+  return load_placement(c, c ? &c->next : nullptr, n2b, bp, ba, bd, B);
+}
+
+int ugc_refresh_evict(ugc_ctx* c, int replica_id, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (!c->next.valid) return fail(UGC_ERR_STATE, "call ugc_refresh_set_placement first");
+  if (r->refresh_open) return fail(UGC_ERR_STATE, "a refresh is already open on replica %d", replica_id);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int G = c->cfg.num_device;
+  const int me = replica_id;
+  UGC_CUDA(cudaSetDevice(r->device));
+  const Placement& old_p = c->cur;
+  const Placement& new_p = c->next;
+
+  // step 1: sources under the new placement
+  uint64_t counts[kMaxLocation];
+  for (auto& v : r->next_keys_by_src) v.clear();
+  classify_keys(new_p, me, c->cfg.num_total_item, r->next_keys_by_src, counts);
+  const uint64_t n_new_local = r->next_keys_by_src[me].size();
+  if (n_new_local > r->capacity)
+    return fail(UGC_ERR_CAPACITY, "new placement stores %llu rows on replica %d, slice holds %llu",
+                (unsigned long long)n_new_local, me, (unsigned long long)r->capacity);
+  uint64_t n_new_entries = n_new_local;
+  for (int s2 = 0; s2 < G; s2++)
+    if (s2 != me) n_new_entries += r->next_keys_by_src[s2].size();
+  if (r->table.kind == kTableHashed && n_new_entries > r->table_entry_cap)
+    return fail(UGC_ERR_CAPACITY, "new placement needs %llu table entries, table is sized for %llu",
+                (unsigned long long)n_new_entries, (unsigned long long)r->table_entry_cap);
+
+  // step 2: rows to bring in = stored here now, not before
+  r->pending_insert = select_keys(r->next_keys_by_src[me], [&](uint32_t k) { return !old_p.stored_on(me, k); });
+  // step 3: rows to drop = stored here before, not now; their slots return to the free list
+  std::vector<uint32_t> evict = select_keys(r->keys_by_src[me], [&](uint32_t k) { return !new_p.stored_on(me, k); });
+  if (!evict.empty()) {
+    UGC_TRY(upload_u32(c, r->stage_a, evict.data(), evict.size(), s));
+    UGC_TRY(ensure(c, r->stage_b, evict.size() * sizeof(uint32_t)));
+    UGC_CUDA(launch_table_resolve(r->table, static_cast<uint32_t*>(r->stage_a.ptr), (uint32_t)evict.size(),
+                                  (uint32_t)me, static_cast<uint32_t*>(r->stage_b.ptr), r->counters, s));
+    std::vector<uint32_t> slots(evict.size());
+    UGC_CUDA(cudaMemcpyAsync(slots.data(), r->stage_b.ptr, evict.size() * sizeof(uint32_t),
+                             cudaMemcpyDeviceToHost, s));
+    UGC_CUDA(launch_table_evict(r->table, static_cast<uint32_t*>(r->stage_a.ptr), (uint32_t)evict.size(),
+                                r->counters, s));
+    UGC_TRY(check_table_errors(r, s, "refresh evict"));
+    for (uint32_t o : slots) r->free_slots.push_back(o);
+  }
+  if (r->pending_insert.size() > r->free_slots.size())
+    return fail(UGC_ERR_CAPACITY, "refresh needs %zu free slots, %zu available", r->pending_insert.size(),
+                r->free_slots.size());
+  // step 4: remote entries whose source changed (coll_cache_lib/cache_context.cu:3103-3136)
+  std::vector<uint32_t> drop_remote;
+  for (int src = 0; src < G; src++) {
+    if (src == me) continue;
+    for (uint32_t k : r->keys_by_src[src])
+      if (new_p.access(me, new_p.nid_to_block[k]) != src) drop_remote.push_back(k);
+  }
+  if (!drop_remote.empty()) {
+    UGC_TRY(upload_u32(c, r->stage_a, drop_remote.data(), drop_remote.size(), s));
+    UGC_CUDA(launch_table_evict(r->table, static_cast<uint32_t*>(r->stage_a.ptr),
+                                (uint32_t)drop_remote.size(), r->counters, s));
+    UGC_TRY(check_table_errors(r, s, "refresh evict remote"));
+  }
+  r->refresh_open = true;
+  return UGC_OK;
+}
+
+int ugc_refresh_fill(ugc_ctx* c, int replica_id, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (!r->refresh_open) return fail(UGC_ERR_STATE, "call ugc_refresh_evict first");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  UGC_CUDA(cudaSetDevice(r->device));
+  const size_t n = r->pending_insert.size();
+  if (n) {
+    // new rows take slots from the FRONT of the free list
+    // (coll_cache_lib/cuda/cache_hashtable.cuh:637-645)
+    std::vector<uint32_t> slots(n);
+    for (size_t i = 0; i < n; i++) {
+      slots[i] = r->free_slots.front();
+      r->free_slots.pop_front();
+    }
+    UGC_TRY(upload_u32(c, r->stage_a, r->pending_insert.data(), n, s));
+    UGC_TRY(upload_u32(c, r->stage_b, slots.data(), n, s));
+    // A small grid keeps the refill from taking bandwidth from running lookups
+    // (the reference limits it to 20 blocks, coll_cache_lib/cache_context.cu:4067).
+    UGC_CUDA(launch_fill_scatter(c->host_dev, r->slice, static_cast<uint32_t*>(r->stage_a.ptr),
+                                 static_cast<uint32_t*>(r->stage_b.ptr), 0, (uint32_t)n,
+                                 c->cfg.row_bytes, c->cfg.empty_feat, 20, s));
+    UGC_CUDA(launch_table_insert(r->table, static_cast<uint32_t*>(r->stage_a.ptr),
+                                 static_cast<uint32_t*>(r->stage_b.ptr), 0, (uint32_t)replica_id,
+                                 (uint32_t)n, r->counters, s));
+    UGC_TRY(check_table_errors(r, s, "refresh insert"));
+  }
+  return UGC_OK;
+}
+
+int ugc_refresh_attach(ugc_ctx* c, int replica_id, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (!r->refresh_open) return fail(UGC_ERR_STATE, "call ugc_refresh_evict first");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  UGC_CUDA(cudaSetDevice(r->device));
+  const int G = c->cfg.num_device;
+  const Placement& old_p = c->cur;
+  for (int src = 0; src < G; src++) {
+    if (src == replica_id) continue;
+    std::vector<uint32_t> fresh = select_keys(r->next_keys_by_src[src], [&](uint32_t k) {
+      return old_p.access(replica_id, old_p.nid_to_block[k]) != src;
+    });
+    UGC_TRY(attach_keys(c, r, src, fresh, s));
+  }
+  for (int src = 0; src < G; src++) r->keys_by_src[src] = std::move(r->next_keys_by_src[src]);
+  r->pending_insert.clear();
+  r->refresh_open = false;
+  return UGC_OK;
+}
+
+int ugc_refresh_commit(ugc_ctx* c) {
+  if (!c) return fail(UGC_ERR_INVALID, "null context");
+  if (!c->next.valid) return fail(UGC_ERR_STATE, "no new placement to commit");
+  for (auto& r : c->reps)
+    if (r.built && r.refresh_open)
+      return fail(UGC_ERR_STATE, "replica %d has not finished its refresh", r.id);
+  c->cur = std::move(c->next);
+  c->next = Placement{};
+  return UGC_OK;
+}
+
+// --------------------------------------------------------------------------------------
+int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (!out) return fail(UGC_ERR_INVALID, "null output");
+  UGC_CUDA(cudaSetDevice(r->device));
+  Counters h;
+  UGC_TRY(read_counters(r, &h));
+  memset(out, 0, sizeof(*out));
+  const int G = c->cfg.num_device;
+  out->num_local_rows = r->keys_by_src[replica_id].size();
+  for (int s = 0; s < G; s++)
+    if (s != replica_id) out->num_remote_keys += r->keys_by_src[s].size();
+  out->num_host_keys = c->cfg.num_total_item - out->num_local_rows - out->num_remote_keys;
+  out->capacity_rows = r->capacity;
+  out->free_rows = r->free_slots.size();
+  out->table_kind = r->table.kind;
+  out->table_bytes = r->table_bytes;
+  out->slice_bytes = r->slice_bytes;
+  out->last_keys = h.last_keys;
+  out->last_local = h.last_count[kGroupLocal];
+  out->last_remote = h.last_count[kGroupRemote];
+  out->last_host = h.last_count[kGroupHost];
+  out->err_key_range = h.err_key_range;
+  out->err_table = h.err_table;
+  out->lookups = r->lookups;
+  return UGC_OK;
+}
+
+int ugc_table_words(ugc_ctx* c, int replica_id, const uint32_t* keys, size_t n, uint32_t* words,
+                    void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  UGC_CUDA(cudaSetDevice(r->device));
+  UGC_CUDA(launch_table_words(r->table, keys, (uint32_t)n, words, static_cast<cudaStream_t>(stream)));
+  return UGC_OK;
+}
+
+int ugc_gen_table(void* dst, uint64_t seed, uint64_t row_begin, uint64_t n_rows, uint64_t dim,
+                  int elem_bytes, void* stream) {
+  if (!dst) return fail(UGC_ERR_INVALID, "null destination");
+  if (elem_bytes != 4 && elem_bytes != 2) return fail(UGC_ERR_INVALID, "elem_bytes must be 4 or 2");
+  if (elem_bytes == 2 && dim % 2) return fail(UGC_ERR_INVALID, "fp16 rows need an even dim");
+  UGC_CUDA(launch_gen_table(dst, seed, row_begin, n_rows, dim, elem_bytes, static_cast<cudaStream_t>(stream)));
+  return UGC_OK;
+}
+
+}  // extern "C"

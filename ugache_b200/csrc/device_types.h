@@ -1,0 +1,80 @@
+// Types shared by the host runtime and the sm_100a kernels.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace ugc {
+
+constexpr int kMaxDevice = 8;
+constexpr int kMaxLocation = kMaxDevice + 1;     // GPUs + host
+constexpr uint32_t kEmptyWord = 0xffffffffu;     // "not in the table" / never-used slot key
+constexpr uint32_t kTombstone = 0x80000000u;     // top bit of a slot key: evicted entry
+constexpr int kSlotsPerLine = 4;                 // one 32-byte line = 4 x {key, word}
+
+// Packed (location, row offset) word: the reference's EmbCacheOff
+// (coll_cache_lib/cuda/cache_hashtable.h:20-28): 4-bit location above a 28-bit offset.
+constexpr uint32_t kOffBits = 28;
+constexpr uint32_t kOffMask = (1u << kOffBits) - 1;
+__host__ __device__ inline uint32_t pack_word(uint32_t loc, uint32_t off) {
+  return (loc << kOffBits) + off;
+}
+__host__ __device__ inline uint32_t word_loc(uint32_t w) { return (w >> kOffBits) & 0xfu; }
+__host__ __device__ inline uint32_t word_off(uint32_t w) { return w & kOffMask; }
+
+// Index record emitted by the lookup for one output row:
+//   bits  0..31  source row offset (slice row, or host row)
+//   bits 32..35  source location
+//   bits 36..63  destination row in the output (28 bits)
+// The reference's 8-byte SrcKeyDstVal (coll_cache_lib/cache_context.h:47-52) keeps only 28
+// offset bits, which cannot address host rows beyond 2^28.
+constexpr uint32_t kMaxBatch = 1u << 28;
+__host__ __device__ inline uint64_t make_record(uint32_t dst, uint32_t loc, uint32_t off) {
+  return ((uint64_t)dst << 36) | ((uint64_t)loc << 32) | off;
+}
+__host__ __device__ inline uint32_t rec_off(uint64_t r) { return (uint32_t)r; }
+__host__ __device__ inline uint32_t rec_loc(uint64_t r) { return (uint32_t)(r >> 32) & 0xfu; }
+__host__ __device__ inline uint32_t rec_dst(uint64_t r) { return (uint32_t)(r >> 36); }
+
+enum TableKind : int { kTableNone = 0, kTableFlat = 1, kTableHashed = 2 };
+
+// Device view of one replica's key -> word table.
+//  flat:   words[key], kEmptyWord = absent                       (4 B / key of the id space)
+//  hashed: open addressing over 32-byte lines of 4 slots {key, word}; line index =
+//          murmur3(key) & line_mask, linear probing over lines; a slot key of kEmptyWord
+//          has never been used (search stops), top bit set = evicted (search goes on).
+struct TableView {
+  int kind;
+  uint32_t* flat;
+  uint2* slots;
+  uint32_t line_mask;
+  uint64_t num_keys;  // N, for range checks
+};
+
+// Source groups of the factored extraction.
+enum Group : int { kGroupLocal = 0, kGroupRemote = 1, kGroupHost = 2, kNumGroup = 3 };
+
+// Device-resident counters of one replica (zeroed at build; the gather's last CTA
+// re-zeroes the per-lookup part).
+struct Counters {
+  uint32_t count[kNumGroup];     // records emitted per group by the current lookup
+  uint32_t done_ctas;            // gather CTAs that have finished
+  uint32_t last_count[kNumGroup];// copy of count[] of the last finished lookup
+  uint32_t last_keys;
+  unsigned long long err_key_range;  // sticky
+  unsigned long long err_table;      // sticky
+};
+
+// Everything the role-partitioned gather needs.
+struct GatherParams {
+  const void* src_base[kMaxLocation];  // per location: slice base / peer slice / host table
+  void* out;
+  const uint64_t* list[kNumGroup];
+  Counters* counters;
+  uint32_t row_bytes;
+  uint32_t n_keys;
+  int remote_cta_cap;   // CTA budget of the peer group
+  int host_cta_cap;     // CTA budget of the host group
+  int rows_per_cta_min; // do not give a group more CTAs than count / this
+};
+
+}  // namespace ugc

@@ -1,0 +1,734 @@
+// sm_100a kernels of the extraction path.  Everything here is integer index arithmetic
+// and raw byte copies; rows move as 16- or 32-byte vectors (4-byte words when a row size
+// is not a multiple of 16).
+#include "kernels.cuh"
+
+namespace ugc {
+
+namespace {
+
+constexpr int kBlock = 256;          // threads per CTA everywhere
+constexpr int kWarpsPerBlock = kBlock / 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+// ------------------------------------------------------------------------------------
+// memory access helpers
+// ------------------------------------------------------------------------------------
+
+template <int BYTES>
+struct Vec;
+template <>
+struct Vec<4> {
+  uint32_t v[1];
+};
+template <>
+struct __align__(16) Vec<16> {
+  uint32_t v[4];
+};
+template <>
+struct __align__(32) Vec<32> {
+  uint32_t v[8];
+};
+
+// Row payload loads: read-only path, no L1 allocation (every byte is used once per CTA).
+__device__ __forceinline__ void ld_row(Vec<4>& r, const void* p) {
+  asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(r.v[0]) : "l"(p));
+}
+__device__ __forceinline__ void ld_row(Vec<16>& r, const void* p) {
+  asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3])
+               : "l"(p));
+}
+__device__ __forceinline__ void ld_row(Vec<32>& r, const void* p) {
+  asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]),
+                 "=r"(r.v[5]), "=r"(r.v[6]), "=r"(r.v[7])
+               : "l"(p));
+}
+// Output stores: streaming (evict-first) so the written rows do not push hot cache rows
+// out of L2.
+__device__ __forceinline__ void st_row(void* p, const Vec<4>& r) {
+  asm volatile("st.global.cs.b32 [%0], %1;" ::"l"(p), "r"(r.v[0]) : "memory");
+}
+__device__ __forceinline__ void st_row(void* p, const Vec<16>& r) {
+  asm volatile("st.global.cs.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(r.v[0]), "r"(r.v[1]),
+               "r"(r.v[2]), "r"(r.v[3])
+               : "memory");
+}
+__device__ __forceinline__ void st_row(void* p, const Vec<32>& r) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r.v[0]),
+               "r"(r.v[1]), "r"(r.v[2]), "r"(r.v[3]), "r"(r.v[4]), "r"(r.v[5]), "r"(r.v[6]),
+               "r"(r.v[7])
+               : "memory");
+}
+// Plain (write-back) store used when the destination is the cache slice itself.
+__device__ __forceinline__ void st_keep(void* p, const Vec<4>& r) {
+  *reinterpret_cast<uint32_t*>(p) = r.v[0];
+}
+__device__ __forceinline__ void st_keep(void* p, const Vec<16>& r) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(r.v[0], r.v[1], r.v[2], r.v[3]);
+}
+__device__ __forceinline__ void st_keep(void* p, const Vec<32>& r) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r.v[0]),
+               "r"(r.v[1]), "r"(r.v[2]), "r"(r.v[3]), "r"(r.v[4]), "r"(r.v[5]), "r"(r.v[6]),
+               "r"(r.v[7])
+               : "memory");
+}
+
+// One 32-byte table line = 4 slots {key, word}.  Coherent load (a refresh may be
+// inserting or evicting while lookups run), L2 only.
+struct Line {
+  uint32_t key[kSlotsPerLine];
+  uint32_t word[kSlotsPerLine];
+};
+__device__ __forceinline__ Line ld_line(const uint2* slots, uint32_t line) {
+  Line l;
+  const uint2* p = slots + (size_t)line * kSlotsPerLine;
+  asm volatile("ld.global.cg.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(l.key[0]), "=r"(l.word[0]), "=r"(l.key[1]), "=r"(l.word[1]),
+                 "=r"(l.key[2]), "=r"(l.word[2]), "=r"(l.key[3]), "=r"(l.word[3])
+               : "l"(p));
+  return l;
+}
+
+// MurmurHash3_32 of one 32-bit key, seed 0: the hash of the reference's probing table
+// (coll_cache_lib/cuda/cache_hashtable.cuh:56-135); here it picks the first line.
+__host__ __device__ __forceinline__ uint32_t murmur3_32(uint32_t key) {
+  uint32_t k1 = key * 0xcc9e2d51u;
+  k1 = (k1 << 15) | (k1 >> 17);
+  k1 *= 0x1b873593u;
+  uint32_t h1 = k1;
+  h1 = (h1 << 13) | (h1 >> 19);
+  h1 = h1 * 5u + 0xe6546b64u;
+  h1 ^= 4u;
+  h1 ^= h1 >> 16;
+  h1 *= 0x85ebca6bu;
+  h1 ^= h1 >> 13;
+  h1 *= 0xc2b2ae35u;
+  h1 ^= h1 >> 16;
+  return h1;
+}
+
+// Result of inspecting one line for `key`: the word if a live slot matches, else whether
+// the search may stop (a never-used slot was seen).
+__device__ __forceinline__ bool line_find(const Line& l, uint32_t key, uint32_t& word, bool& stop) {
+  stop = false;
+#pragma unroll
+  for (int s = 0; s < kSlotsPerLine; s++) {
+    if (l.key[s] == key) {  // live slots carry the key with the top bit clear
+      word = l.word[s];
+      return true;
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < kSlotsPerLine; s++) stop |= (l.key[s] == kEmptyWord);
+  return false;
+}
+
+// Probes after the first line (already loaded by the caller).  Bounded by the table size.
+__device__ __forceinline__ uint32_t probe_rest(const uint2* slots, uint32_t line_mask, uint32_t key,
+                                            uint32_t line) {
+  for (uint32_t step = 0; step < line_mask; step++) {
+    line = (line + 1) & line_mask;
+    Line l = ld_line(slots, line);
+    uint32_t w;
+    bool stop;
+    if (line_find(l, key, w, stop)) return w;
+    if (stop) return kEmptyWord;
+  }
+  return kEmptyWord;
+}
+
+__device__ __forceinline__ uint32_t table_lookup(const TableView& t, uint32_t key) {
+  if (t.kind == kTableFlat) {
+    uint32_t w;
+    asm volatile("ld.global.cg.b32 %0, [%1];" : "=r"(w) : "l"(t.flat + key));
+    return w;
+  }
+  uint32_t line = murmur3_32(key) & t.line_mask;
+  Line l = ld_line(t.slots, line);
+  uint32_t w;
+  bool stop;
+  if (line_find(l, key, w, stop)) return w;
+  if (stop) return kEmptyWord;
+  return probe_rest(t.slots, t.line_mask, key, line);
+}
+
+// ------------------------------------------------------------------------------------
+// lookup + group by source
+// ------------------------------------------------------------------------------------
+constexpr int kKeysPerThread = 4;
+constexpr int kLookupTile = kBlock * kKeysPerThread;
+
+template <typename KeyT>
+__global__ void __launch_bounds__(kBlock)
+    lookup_group_kernel(const KeyT* __restrict__ keys, uint32_t n, TableView t, uint32_t local_loc,
+                        uint32_t host_loc, uint32_t host_mask, uint64_t* __restrict__ list_local,
+                        uint64_t* __restrict__ list_remote, uint64_t* __restrict__ list_host,
+                        Counters* counters) {
+  __shared__ uint32_t s_cnt[kWarpsPerBlock][kKeysPerThread][kNumGroup];
+  __shared__ uint32_t s_base[kNumGroup];
+
+  const uint32_t tid = threadIdx.x;
+  const uint32_t warp = tid >> 5, lane = tid & 31;
+  const uint32_t tile_base = blockIdx.x * kLookupTile;
+
+  uint32_t key[kKeysPerThread];
+  bool valid[kKeysPerThread];
+  uint32_t bad = 0;
+#pragma unroll
+  for (int j = 0; j < kKeysPerThread; j++) {
+    uint32_t idx = tile_base + j * kBlock + tid;
+    valid[j] = idx < n;
+    uint64_t k = valid[j] ? (uint64_t)keys[idx] : 0;
+    if (k >= t.num_keys) {  // also catches negative int64 ids
+      valid[j] = false;
+      bad++;
+      k = 0;
+    }
+    key[j] = (uint32_t)k;
+  }
+  if (bad) atomicAdd(&counters->err_key_range, (unsigned long long)bad);
+
+  // First probe of every key is issued before any is consumed.
+  uint32_t word[kKeysPerThread];
+  if (t.kind == kTableFlat) {
+#pragma unroll
+    for (int j = 0; j < kKeysPerThread; j++) {
+      word[j] = kEmptyWord;
+      if (valid[j]) asm volatile("ld.global.cg.b32 %0, [%1];" : "=r"(word[j]) : "l"(t.flat + key[j]));
+    }
+  } else {
+    Line first[kKeysPerThread];
+    uint32_t line[kKeysPerThread];
+#pragma unroll
+    for (int j = 0; j < kKeysPerThread; j++) {
+      line[j] = murmur3_32(key[j]) & t.line_mask;
+      first[j] = ld_line(t.slots, line[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kKeysPerThread; j++) {
+      uint32_t w;
+      bool stop;
+      if (line_find(first[j], key[j], w, stop)) {
+        word[j] = w;
+      } else if (stop) {
+        word[j] = kEmptyWord;
+      } else {
+        word[j] = probe_rest(t.slots, t.line_mask, key[j], line[j]);
+      }
+    }
+  }
+
+  // Group, count per warp with ballots.
+  uint32_t group[kKeysPerThread], rank_in_warp[kKeysPerThread];
+  uint64_t rec[kKeysPerThread];
+#pragma unroll
+  for (int j = 0; j < kKeysPerThread; j++) {
+    uint32_t idx = tile_base + j * kBlock + tid;
+    uint32_t loc, off;
+    if (word[j] == kEmptyWord) {
+      loc = host_loc;
+      off = key[j] & host_mask;
+      group[j] = kGroupHost;
+    } else {
+      loc = word_loc(word[j]);
+      off = word_off(word[j]);
+      group[j] = (loc == local_loc) ? kGroupLocal : kGroupRemote;
+    }
+    if (!valid[j]) group[j] = kNumGroup;
+    rec[j] = make_record(idx, loc, off);
+    rank_in_warp[j] = 0;
+#pragma unroll
+    for (int g = 0; g < kNumGroup; g++) {
+      unsigned m = __ballot_sync(kFull, group[j] == (uint32_t)g);
+      if (group[j] == (uint32_t)g) rank_in_warp[j] = __popc(m & ((1u << lane) - 1));
+      if (lane == 0) s_cnt[warp][j][g] = __popc(m);
+    }
+  }
+  __syncthreads();
+  // Exclusive scan of the 8x4 per-warp counts of each group (one thread per group), then
+  // one global atomic per (CTA, group).
+  if (tid < kNumGroup) {
+    uint32_t run = 0;
+    for (int j = 0; j < kKeysPerThread; j++)
+      for (int w = 0; w < kWarpsPerBlock; w++) {
+        uint32_t c = s_cnt[w][j][tid];
+        s_cnt[w][j][tid] = run;
+        run += c;
+      }
+    s_base[tid] = run ? atomicAdd(&counters->count[tid], run) : 0;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kKeysPerThread; j++) {
+    if (group[j] == kNumGroup) continue;
+    uint32_t pos = s_base[group[j]] + s_cnt[warp][j][group[j]] + rank_in_warp[j];
+    uint64_t* dst = group[j] == kGroupLocal ? list_local
+                                             : (group[j] == kGroupRemote ? list_remote : list_host);
+    dst[pos] = rec[j];
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// row copy core: a "worker" is a group of LPR lanes that copies one row at a time,
+// UNROLL rows in flight per worker.
+// ------------------------------------------------------------------------------------
+struct RecordIndex {  // rows described by 64-bit records
+  const uint64_t* list;
+  const void* const* src_base;  // per location
+  char* out;
+  uint32_t row_bytes;
+  __device__ __forceinline__ void get(uint32_t i, const char*& src, char*& dst) const {
+    uint64_t r = list[i];
+    src = static_cast<const char*>(src_base[rec_loc(r)]) + (size_t)rec_off(r) * row_bytes;
+    dst = out + (size_t)rec_dst(r) * row_bytes;
+  }
+};
+struct KeySlotIndex {  // fill: host row of a key -> cache slot
+  const uint32_t* keys;
+  const uint32_t* slots;  // may be null: slot = slot_base + i
+  uint32_t slot_base;
+  uint32_t host_mask;
+  const char* host;
+  char* slice;
+  uint32_t row_bytes;
+  __device__ __forceinline__ void get(uint32_t i, const char*& src, char*& dst) const {
+    uint32_t k = keys[i] & host_mask;
+    uint32_t s = slots ? slots[i] : slot_base + i;
+    src = host + (size_t)k * row_bytes;
+    dst = slice + (size_t)s * row_bytes;
+  }
+};
+
+template <int VEC, int LPR, int UNROLL, bool STREAM_OUT, typename Index>
+__device__ __forceinline__ void copy_rows(const Index& ix, uint32_t count, uint32_t worker,
+                                          uint32_t n_workers, uint32_t sublane,
+                                          uint32_t vecs_per_row) {
+  for (uint32_t base = worker; base < count; base += n_workers * UNROLL) {
+    const char* src[UNROLL];
+    char* dst[UNROLL];
+    bool ok[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; u++) {
+      uint32_t i = base + u * n_workers;
+      ok[u] = i < count;
+      src[u] = nullptr;
+      dst[u] = nullptr;
+      if (ok[u]) ix.get(i, src[u], dst[u]);
+    }
+    for (uint32_t c = sublane; c < vecs_per_row; c += LPR) {
+      Vec<VEC> v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; u++)
+        if (ok[u]) ld_row(v[u], src[u] + (size_t)c * VEC);
+#pragma unroll
+      for (int u = 0; u < UNROLL; u++)
+        if (ok[u]) {
+          if (STREAM_OUT) {
+            st_row(dst[u] + (size_t)c * VEC, v[u]);
+          } else {
+            st_keep(dst[u] + (size_t)c * VEC, v[u]);
+          }
+        }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// role-partitioned gather
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ int ceil_div_i(uint32_t a, uint32_t b) { return (int)((a + b - 1) / b); }
+
+// Splits the grid (>= 3 CTAs) into host / remote / local groups from the device-resident
+// counts.  CTAs [0, n_host) serve host rows, [n_host, n_host+n_remote) peer rows, the rest
+// local rows: the long-latency sources get the lowest block indices, which start first.
+// A non-empty group always gets at least one CTA.
+__device__ __forceinline__ void split_roles(const GatherParams& p, const uint32_t cnt[kNumGroup],
+                                            int grid, int& n_host, int& n_remote) {
+  const uint32_t rmin = (uint32_t)p.rows_per_cta_min;
+  n_host = cnt[kGroupHost] ? max(1, min(p.host_cta_cap, ceil_div_i(cnt[kGroupHost], rmin))) : 0;
+  n_remote =
+      cnt[kGroupRemote] ? max(1, min(p.remote_cta_cap, ceil_div_i(cnt[kGroupRemote], rmin))) : 0;
+  const int avail = grid - (cnt[kGroupLocal] ? 1 : 0);
+  while (n_host + n_remote > avail) {  // small grids only
+    if (n_remote >= n_host && n_remote > 1) {
+      n_remote--;
+    } else if (n_host > 1) {
+      n_host--;
+    } else {
+      n_remote--;
+    }
+  }
+  if (cnt[kGroupLocal] == 0) {  // nothing local: the spare CTAs help the other groups
+    if (cnt[kGroupRemote]) {
+      n_remote = grid - n_host;
+    } else if (cnt[kGroupHost]) {
+      n_host = grid;
+    }
+  }
+}
+
+template <int VEC, int LPR, int UNROLL>
+__global__ void __launch_bounds__(kBlock) gather_roles_kernel(GatherParams p) {
+  const int grid = (int)gridDim.x;
+  const int b = (int)blockIdx.x;
+  uint32_t cnt[kNumGroup];
+#pragma unroll
+  for (int g = 0; g < kNumGroup; g++) cnt[g] = p.counters->count[g];
+
+  int n_host, n_remote;
+  split_roles(p, cnt, grid, n_host, n_remote);
+
+  const uint32_t vecs_per_row = p.row_bytes / VEC;
+  constexpr uint32_t kWorkersPerCta = kBlock / LPR;
+  const uint32_t worker_in_cta = threadIdx.x / LPR;
+  const uint32_t sublane = threadIdx.x % LPR;
+
+  int g, first, num;
+  if (b < n_host) {
+    g = kGroupHost;
+    first = 0;
+    num = n_host;
+  } else if (b < n_host + n_remote) {
+    g = kGroupRemote;
+    first = n_host;
+    num = n_remote;
+  } else {
+    g = kGroupLocal;
+    first = n_host + n_remote;
+    num = grid - first;
+  }
+  if (cnt[g] != 0) {
+    RecordIndex ix;
+    ix.list = p.list[g];
+    ix.src_base = p.src_base;
+    ix.out = static_cast<char*>(p.out);
+    ix.row_bytes = p.row_bytes;
+    const uint32_t worker = (uint32_t)(b - first) * kWorkersPerCta + worker_in_cta;
+    const uint32_t n_workers = (uint32_t)num * kWorkersPerCta;
+    copy_rows<VEC, LPR, UNROLL, true>(ix, cnt[g], worker, n_workers, sublane, vecs_per_row);
+  }
+
+  // The last CTA to finish publishes the counts of this lookup and re-arms the counters.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    uint32_t done = atomicAdd(&p.counters->done_ctas, 1u);
+    if (done == (uint32_t)grid - 1) {
+#pragma unroll
+      for (int g = 0; g < kNumGroup; g++) {
+        p.counters->last_count[g] = cnt[g];
+        p.counters->count[g] = 0;
+      }
+      p.counters->last_keys = p.n_keys;
+      p.counters->done_ctas = 0;
+      __threadfence();
+    }
+  }
+}
+
+template <int VEC, int LPR, int UNROLL>
+__global__ void __launch_bounds__(kBlock) fill_scatter_kernel(KeySlotIndex ix, uint32_t n) {
+  const uint32_t vecs_per_row = ix.row_bytes / VEC;
+  constexpr uint32_t kWorkersPerCta = kBlock / LPR;
+  const uint32_t worker = blockIdx.x * kWorkersPerCta + threadIdx.x / LPR;
+  copy_rows<VEC, LPR, UNROLL, false>(ix, n, worker, gridDim.x * kWorkersPerCta, threadIdx.x % LPR,
+                                     vecs_per_row);
+}
+
+// ------------------------------------------------------------------------------------
+// table maintenance
+// ------------------------------------------------------------------------------------
+__global__ void table_clear_kernel(uint4* p, size_t n16) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n16; i += stride) p[i] = make_uint4(kEmptyWord, kEmptyWord, kEmptyWord, kEmptyWord);
+}
+
+// Inserts a key that is not live in the table.  A slot is free when its key has the top
+// bit set (never used, or evicted).  Key and word are published by one 64-bit
+// compare-and-swap, so a concurrent lookup sees the slot either free or complete.
+__device__ __forceinline__ bool insert_hashed(const TableView& t, uint32_t key, uint32_t word) {
+  uint32_t line = murmur3_32(key) & t.line_mask;
+  for (uint32_t step = 0; step <= t.line_mask; step++) {
+    Line l = ld_line(t.slots, line);
+#pragma unroll
+    for (int s = 0; s < kSlotsPerLine; s++) {
+      if (l.key[s] == key) return false;  // already live: caller counts it as an error
+      if (l.key[s] & kTombstone) {
+        unsigned long long* slot =
+            reinterpret_cast<unsigned long long*>(t.slots + (size_t)line * kSlotsPerLine + s);
+        unsigned long long expect = ((unsigned long long)l.word[s] << 32) | l.key[s];
+        unsigned long long want = ((unsigned long long)word << 32) | key;
+        if (atomicCAS(slot, expect, want) == expect) return true;
+        // lost the race for this slot: keep scanning (the winner holds a different key)
+      }
+    }
+    line = (line + 1) & t.line_mask;
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(kBlock)
+    table_insert_kernel(TableView t, const uint32_t* __restrict__ keys,
+                        const uint32_t* __restrict__ offs, uint32_t off_base, uint32_t loc,
+                        uint32_t n, Counters* counters) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t key = keys[i];
+  uint32_t word = pack_word(loc, offs ? offs[i] : off_base + i);
+  bool ok;
+  if (key >= t.num_keys) {
+    ok = false;
+  } else if (t.kind == kTableFlat) {
+    ok = atomicExch(t.flat + key, word) == kEmptyWord;
+  } else {
+    ok = insert_hashed(t, key, word);
+  }
+  if (!ok) atomicAdd(&counters->err_table, 1ull);
+}
+
+__global__ void __launch_bounds__(kBlock)
+    table_evict_kernel(TableView t, const uint32_t* __restrict__ keys, uint32_t n,
+                       Counters* counters) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t key = keys[i];
+  bool ok = false;
+  if (key < t.num_keys) {
+    if (t.kind == kTableFlat) {
+      ok = atomicExch(t.flat + key, kEmptyWord) != kEmptyWord;
+    } else {
+      uint32_t line = murmur3_32(key) & t.line_mask;
+      for (uint32_t step = 0; step <= t.line_mask && !ok; step++) {
+        Line l = ld_line(t.slots, line);
+        bool stop = false;
+#pragma unroll
+        for (int s = 0; s < kSlotsPerLine; s++) {
+          if (l.key[s] == key && !ok) {
+            atomicOr(&t.slots[(size_t)line * kSlotsPerLine + s].x, kTombstone);
+            ok = true;
+          }
+          stop |= (l.key[s] == kEmptyWord);
+        }
+        if (stop) break;
+        line = (line + 1) & t.line_mask;
+      }
+    }
+  }
+  if (!ok) atomicAdd(&counters->err_table, 1ull);
+}
+
+__global__ void __launch_bounds__(kBlock)
+    table_words_kernel(TableView t, const uint32_t* __restrict__ keys, uint32_t n,
+                       uint32_t* __restrict__ words) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t key = keys[i];
+  words[i] = key < t.num_keys ? table_lookup(t, key) : kEmptyWord;
+}
+
+__global__ void __launch_bounds__(kBlock)
+    table_resolve_kernel(TableView peer, const uint32_t* __restrict__ keys, uint32_t n,
+                         uint32_t expect_loc, uint32_t* __restrict__ offs, Counters* counters) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t key = keys[i];
+  uint32_t w = key < peer.num_keys ? table_lookup(peer, key) : kEmptyWord;
+  if (w == kEmptyWord || word_loc(w) != expect_loc) {
+    atomicAdd(&counters->err_table, 1ull);
+    offs[i] = 0;
+  } else {
+    offs[i] = word_off(w);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// synthetic table rows
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9e3779b97f4a7c15ull;
+  x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+  x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+  return x ^ (x >> 31);
+}
+__device__ __forceinline__ uint32_t gen_f32_bits(uint64_t seed, uint64_t e) {
+  uint64_t x = splitmix64(seed ^ splitmix64(e));
+  return __float_as_uint((float)(x >> 40) * (1.0f / 8388608.0f) - 1.0f);
+}
+__device__ __forceinline__ uint32_t gen_f16_bits(uint64_t seed, uint64_t e) {
+  uint64_t x = splitmix64(seed ^ splitmix64(e));
+  int v = (int)(x >> 53) - 1024;  // value = v * 2^-10
+  if (v == 0) return 0;
+  uint32_t sign = 0;
+  if (v < 0) {
+    sign = 0x8000u;
+    v = -v;
+  }
+  int msb = 31 - __clz(v);
+  uint32_t exp = (uint32_t)(msb - 10 + 15);
+  uint32_t man = ((uint32_t)v << (10 - msb)) & 0x3ffu;
+  return sign | (exp << 10) | man;
+}
+
+// One thread writes 4 bytes: one fp32 element or two fp16 elements.
+__global__ void gen_table_kernel(uint32_t* dst, uint64_t seed, uint64_t elem_begin, uint64_t n_words,
+                                 int elem_bytes) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n_words; i += stride) {
+    uint32_t w;
+    if (elem_bytes == 4) {
+      w = gen_f32_bits(seed, elem_begin + i);
+    } else {
+      uint64_t e = elem_begin + 2 * i;
+      w = gen_f16_bits(seed, e) | (gen_f16_bits(seed, e + 1) << 16);
+    }
+    dst[i] = w;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// dispatch helpers
+// ------------------------------------------------------------------------------------
+inline int grid_for(uint32_t n) { return (int)((n + kBlock - 1) / kBlock); }
+
+// Lanes per row: the smallest power of two >= vectors per row, at most a warp.
+inline int lanes_per_row(uint32_t row_bytes, int vec) {
+  uint32_t vecs = row_bytes / (uint32_t)vec;
+  int l = 1;
+  while ((uint32_t)l < vecs && l < 32) l <<= 1;
+  return l;
+}
+
+template <int VEC, int UNROLL>
+cudaError_t gather_dispatch_lpr(const GatherParams& p, int grid, cudaStream_t s) {
+  switch (lanes_per_row(p.row_bytes, VEC)) {
+    case 1: gather_roles_kernel<VEC, 1, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
+    case 2: gather_roles_kernel<VEC, 2, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
+    case 4: gather_roles_kernel<VEC, 4, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
+    case 8: gather_roles_kernel<VEC, 8, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
+    case 16: gather_roles_kernel<VEC, 16, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
+    default: gather_roles_kernel<VEC, 32, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
+  }
+  return cudaGetLastError();
+}
+
+template <int VEC, int UNROLL>
+cudaError_t fill_dispatch_lpr(const KeySlotIndex& ix, uint32_t n, int grid, cudaStream_t s) {
+  switch (lanes_per_row(ix.row_bytes, VEC)) {
+    case 1: fill_scatter_kernel<VEC, 1, UNROLL><<<grid, kBlock, 0, s>>>(ix, n); break;
+    case 2: fill_scatter_kernel<VEC, 2, UNROLL><<<grid, kBlock, 0, s>>>(ix, n); break;
+    case 4: fill_scatter_kernel<VEC, 4, UNROLL><<<grid, kBlock, 0, s>>>(ix, n); break;
+    case 8: fill_scatter_kernel<VEC, 8, UNROLL><<<grid, kBlock, 0, s>>>(ix, n); break;
+    case 16: fill_scatter_kernel<VEC, 16, UNROLL><<<grid, kBlock, 0, s>>>(ix, n); break;
+    default: fill_scatter_kernel<VEC, 32, UNROLL><<<grid, kBlock, 0, s>>>(ix, n); break;
+  }
+  return cudaGetLastError();
+}
+
+inline uint32_t host_mask_of(int empty_feat) {
+  return empty_feat > 0 && empty_feat < 32 ? ((1u << empty_feat) - 1u) : 0xffffffffu;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------
+// launchers
+// ------------------------------------------------------------------------------------
+cudaError_t launch_lookup_group(const void* keys, int key_bytes, uint32_t n, const TableView& table,
+                                uint32_t local_loc, uint32_t host_loc, int empty_feat,
+                                uint64_t* list_local, uint64_t* list_remote, uint64_t* list_host,
+                                Counters* counters, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  const int grid = (int)((n + kLookupTile - 1) / kLookupTile);
+  const uint32_t mask = host_mask_of(empty_feat);
+  if (key_bytes == 8) {
+    lookup_group_kernel<long long><<<grid, kBlock, 0, stream>>>(
+        static_cast<const long long*>(keys), n, table, local_loc, host_loc, mask, list_local,
+        list_remote, list_host, counters);
+  } else {
+    lookup_group_kernel<uint32_t><<<grid, kBlock, 0, stream>>>(
+        static_cast<const uint32_t*>(keys), n, table, local_loc, host_loc, mask, list_local,
+        list_remote, list_host, counters);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_roles(const GatherParams& p, int grid, int vec_bytes, cudaStream_t stream) {
+  if (grid < 3) grid = 3;  // one CTA per source group at least
+  if (vec_bytes == 32 && p.row_bytes % 32 == 0) return gather_dispatch_lpr<32, 2>(p, grid, stream);
+  if (p.row_bytes % 16 == 0) return gather_dispatch_lpr<16, 4>(p, grid, stream);
+  return gather_dispatch_lpr<4, 4>(p, grid, stream);
+}
+
+cudaError_t launch_fill_scatter(const void* host_table, void* slice, const uint32_t* keys,
+                                const uint32_t* slots, uint32_t slot_base, uint32_t n,
+                                uint32_t row_bytes, int empty_feat, int grid, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  KeySlotIndex ix;
+  ix.keys = keys;
+  ix.slots = slots;
+  ix.slot_base = slot_base;
+  ix.host_mask = host_mask_of(empty_feat);
+  ix.host = static_cast<const char*>(host_table);
+  ix.slice = static_cast<char*>(slice);
+  ix.row_bytes = row_bytes;
+  if (grid < 1) grid = 1;
+  if (row_bytes % 16 == 0) return fill_dispatch_lpr<16, 8>(ix, n, grid, stream);
+  return fill_dispatch_lpr<4, 8>(ix, n, grid, stream);
+}
+
+cudaError_t launch_table_clear(const TableView& t, cudaStream_t stream) {
+  size_t bytes = t.kind == kTableFlat ? (size_t)t.num_keys * 4
+                                      : ((size_t)t.line_mask + 1) * kSlotsPerLine * sizeof(uint2);
+  // flat tables are allocated rounded up to 16 bytes by the runtime
+  size_t n16 = (bytes + 15) / 16;
+  void* base = t.kind == kTableFlat ? static_cast<void*>(t.flat) : static_cast<void*>(t.slots);
+  table_clear_kernel<<<1184, kBlock, 0, stream>>>(static_cast<uint4*>(base), n16);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_table_insert(const TableView& t, const uint32_t* keys, const uint32_t* offs,
+                                uint32_t off_base, uint32_t loc, uint32_t n, Counters* counters,
+                                cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  table_insert_kernel<<<grid_for(n), kBlock, 0, stream>>>(t, keys, offs, off_base, loc, n, counters);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_table_evict(const TableView& t, const uint32_t* keys, uint32_t n,
+                               Counters* counters, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  table_evict_kernel<<<grid_for(n), kBlock, 0, stream>>>(t, keys, n, counters);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_table_words(const TableView& t, const uint32_t* keys, uint32_t n,
+                               uint32_t* words, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  table_words_kernel<<<grid_for(n), kBlock, 0, stream>>>(t, keys, n, words);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_table_resolve(const TableView& peer, const uint32_t* keys, uint32_t n,
+                                 uint32_t expect_loc, uint32_t* offs, Counters* counters,
+                                 cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  table_resolve_kernel<<<grid_for(n), kBlock, 0, stream>>>(peer, keys, n, expect_loc, offs, counters);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gen_table(void* dst, uint64_t seed, uint64_t row_begin, uint64_t n_rows,
+                             uint64_t dim, int elem_bytes, cudaStream_t stream) {
+  uint64_t n_words = n_rows * dim * (uint64_t)elem_bytes / 4;
+  if (n_words == 0) return cudaSuccess;
+  uint64_t blocks = (n_words + kBlock - 1) / kBlock;
+  int grid = (int)(blocks < 148ull * 16 ? blocks : 148ull * 16);
+  gen_table_kernel<<<grid, kBlock, 0, stream>>>(static_cast<uint32_t*>(dst), seed, row_begin * dim,
+                                                n_words, elem_bytes);
+  return cudaGetLastError();
+}
+
+}  // namespace ugc

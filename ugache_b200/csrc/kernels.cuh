@@ -1,0 +1,50 @@
+// sm_100a kernels of the extraction path and their launchers.
+//
+//   lookup_group   keys -> (location, offset) through the replica's table, grouped by
+//                  source into three record lists (local / peers / host) with the counts
+//                  left in device memory: no sort, no host round trip.
+//   gather_roles   one launch whose CTAs split into per-source groups sized from those
+//                  counts and the link budgets; each group copies its rows with vector
+//                  loads (local HBM, peer HBM over NVLink P2P, zero-copy host over PCIe).
+//   fill_scatter   host rows -> cache slots (build and refresh).
+//   table_*        insert / evict / word lookup / peer-table resolve.
+//   gen_table      seeded synthetic table rows (benchmark input helper).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "device_types.h"
+
+namespace ugc {
+
+// All launchers enqueue on `stream` and return the launch status; none synchronises.
+
+cudaError_t launch_lookup_group(const void* keys, int key_bytes, uint32_t n, const TableView& table,
+                                uint32_t local_loc, uint32_t host_loc, int empty_feat,
+                                uint64_t* list_local, uint64_t* list_remote, uint64_t* list_host,
+                                Counters* counters, cudaStream_t stream);
+
+cudaError_t launch_gather_roles(const GatherParams& p, int grid, int vec_bytes, cudaStream_t stream);
+
+// slice[slot(j)] = host[key(j) & mask]; slots == nullptr means slot(j) = slot_base + j.
+cudaError_t launch_fill_scatter(const void* host_table, void* slice, const uint32_t* keys,
+                                const uint32_t* slots, uint32_t slot_base, uint32_t n,
+                                uint32_t row_bytes, int empty_feat, int grid, cudaStream_t stream);
+
+cudaError_t launch_table_clear(const TableView& t, cudaStream_t stream);
+// word(j) = pack(loc, offs ? offs[j] : off_base + j)
+cudaError_t launch_table_insert(const TableView& t, const uint32_t* keys, const uint32_t* offs,
+                                uint32_t off_base, uint32_t loc, uint32_t n, Counters* counters,
+                                cudaStream_t stream);
+cudaError_t launch_table_evict(const TableView& t, const uint32_t* keys, uint32_t n,
+                               Counters* counters, cudaStream_t stream);
+cudaError_t launch_table_words(const TableView& t, const uint32_t* keys, uint32_t n,
+                               uint32_t* words, cudaStream_t stream);
+// offs[j] = offset the peer's table holds for keys[j] (must be stored on `expect_loc`).
+cudaError_t launch_table_resolve(const TableView& peer, const uint32_t* keys, uint32_t n,
+                                 uint32_t expect_loc, uint32_t* offs, Counters* counters,
+                                 cudaStream_t stream);
+
+cudaError_t launch_gen_table(void* dst, uint64_t seed, uint64_t row_begin, uint64_t n_rows,
+                             uint64_t dim, int elem_bytes, cudaStream_t stream);
+
+}  // namespace ugc

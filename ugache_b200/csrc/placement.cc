@@ -1,0 +1,203 @@
+#include "placement.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "../../include/ugache_b200.h"
+
+namespace ugc {
+
+std::string validate_placement(const Placement& p, int G, uint64_t N) {
+  if (p.num_block <= 0) return "placement has no blocks";
+  if (p.nid_to_block.size() != N) return "nid_to_block must have num_total_item entries";
+  if (p.block_placement.size() != (size_t)p.num_block) return "block_placement size mismatch";
+  if (p.block_access_from.size() != (size_t)G * p.num_block) return "block_access_from size mismatch";
+  for (int b = 0; b < p.num_block; b++) {
+    if (G < 8 && (p.block_placement[b] >> G)) return "block_placement names a GPU >= num_device";
+    for (int g = 0; g < G; g++) {
+      int s = p.access(g, b);
+      if (s > G) return "block_access_from names a location > num_device";
+      bool stored_here = (p.block_placement[b] >> g) & 1;
+      if (s < G && !((p.block_placement[b] >> s) & 1))
+        return "a reader's source does not store the block";
+      if (stored_here != (s == g)) return "a GPU that stores a block must read its own copy (and only then)";
+    }
+  }
+  bool bad = false;
+  const uint32_t nb = (uint32_t)p.num_block;
+#pragma omp parallel for reduction(|| : bad)
+  for (int64_t k = 0; k < (int64_t)N; k++) bad = bad || (p.nid_to_block[k] >= nb);
+  if (bad) return "nid_to_block holds a block id >= num_block";
+  return "";
+}
+
+void b200_link_model(int num_device, double* t_local, double* t_remote, double* t_cpu) {
+  (void)num_device;
+  *t_local = 1.0;
+  *t_remote = 8000.0 / 900.0;
+  *t_cpu = 8000.0 / 64.0;
+}
+
+bool reference_prefers_flat_table(uint64_t num, uint64_t N) {
+  uint64_t e = (uint64_t)(1.0 + std::log2((double)(num >> 1)));
+  uint64_t table_size = ((uint64_t)1 << e) << 2;
+  return table_size > N / 2;
+}
+
+uint64_t cache_capacity_rows(uint64_t N, double frac) { return (uint64_t)((double)N * (frac + 0.001)); }
+
+namespace {
+
+void alloc_out(Placement* out, int G, uint64_t N, int B) {
+  out->nid_to_block.assign(N, 0);
+  out->block_placement.assign(B, 0);
+  out->block_access_from.assign((size_t)G * B, 0);
+  out->block_density.assign(B, 0.0);
+  out->num_block = B;
+  out->num_device = G;
+}
+
+std::string solve_intuitive(int G, uint32_t N, const uint32_t* ids, const uint32_t* freq, double pct,
+                            double T_local, double T_remote, double T_cpu, Placement* out) {
+  if (!freq) return "the intuitive policy needs rank_freqs";
+  alloc_out(out, G, N, G + 2);
+  const uint32_t cached = (uint32_t)(N * (pct / 100.0));
+  uint32_t lo = 0, hi = 0;
+  if (G > 1) hi = std::min<uint32_t>(cached, (N - cached) / (uint32_t)(G - 1));
+  auto lb = [&](uint32_t p) { return cached - p; };
+  auto rb = [&](uint32_t p) { return std::max<uint32_t>(cached + p * (uint32_t)(G - 1), 1u) - 1u; };
+  const double mu = 1 + (T_cpu - T_remote) / (T_remote - T_local) * G;
+  auto colder = [&](uint32_t p) { return (double)freq[lb(p)] < (double)freq[rb(p)] * mu; };
+  uint32_t part = lo;
+  if (mu < 1) {
+    part = lo;
+  } else if (colder(hi)) {
+    part = hi;
+  } else {
+    while (hi - lo > 1) {
+      part = (lo + hi) / 2;
+      if (colder(part)) lo = part; else hi = part;
+    }
+    part = hi;
+  }
+  const uint32_t L = lb(part), R = rb(part);
+#pragma omp parallel for
+  for (int64_t rank = 0; rank < (int64_t)N; rank++) {
+    uint32_t b;
+    if ((uint32_t)rank < L) b = 0;
+    else if ((uint32_t)rank <= R) b = (uint32_t)rank % (uint32_t)G + 1;
+    else b = (uint32_t)G + 1;
+    out->nid_to_block[ids[rank]] = b;
+  }
+  const int B = G + 2;
+  out->block_placement[0] = (uint8_t)((1 << G) - 1);
+  for (int g = 0; g < G; g++) out->block_placement[g + 1] = (uint8_t)(1 << g);
+  for (int g = 0; g < G; g++) {
+    uint8_t* row = &out->block_access_from[(size_t)g * B];
+    row[0] = (uint8_t)g;
+    for (int b = 1; b <= G; b++) row[b] = (uint8_t)(b - 1);
+    row[G + 1] = (uint8_t)G;
+  }
+  out->block_density[0] = (double)L * 100 / (double)N;
+  for (int b = 1; b <= G; b++) out->block_density[b] = part * 100.0 / (double)N;
+  out->block_density[G + 1] = 100 - (R / (double)N) * 100;
+  return "";
+}
+
+std::string solve_rep(int G, uint32_t N, const uint32_t* ids, double pct, Placement* out) {
+  alloc_out(out, G, N, 2);
+  const uint32_t rep = (uint32_t)(N * (pct / 100.0));
+#pragma omp parallel for
+  for (int64_t rank = 0; rank < (int64_t)N; rank++) out->nid_to_block[ids[rank]] = (uint32_t)rank < rep ? 0 : 1;
+  out->block_placement[0] = (uint8_t)((1 << G) - 1);
+  for (int g = 0; g < G; g++) {
+    out->block_access_from[(size_t)g * 2 + 0] = (uint8_t)g;
+    out->block_access_from[(size_t)g * 2 + 1] = (uint8_t)G;
+  }
+  out->block_density[0] = (double)rep * 100 / (double)N;
+  out->block_density[1] = (double)(N - rep) * 100 / (double)N;
+  return "";
+}
+
+std::string solve_clique(int G, uint32_t N, const uint32_t* ids, double pct, Placement* out) {
+  const int C = G;  // one NVSwitch domain: the clique is the whole box
+  alloc_out(out, G, N, C + 1);
+  const uint32_t cached = (uint32_t)std::ceil(N * (pct / 100.0));
+  const uint32_t part = std::min<uint32_t>(cached, (N + (uint32_t)C - 1) / (uint32_t)C);
+  const uint64_t covered = (uint64_t)part * C;
+#pragma omp parallel for
+  for (int64_t rank = 0; rank < (int64_t)N; rank++)
+    out->nid_to_block[ids[rank]] = (uint64_t)rank < covered ? (uint32_t)rank % (uint32_t)C : (uint32_t)C;
+  const int B = C + 1;
+  for (int b = 0; b < C; b++) {
+    out->block_placement[b] = (uint8_t)(1 << b);
+    for (int g = 0; g < G; g++) out->block_access_from[(size_t)g * B + b] = (uint8_t)b;
+    out->block_density[b] = (double)part * 100 / (double)N;
+  }
+  for (int g = 0; g < G; g++) out->block_access_from[(size_t)g * B + C] = (uint8_t)G;
+  out->block_density[C] = ((double)N - (double)covered) * 100 / (double)N;
+  return "";
+}
+
+}  // namespace
+
+std::string solve_placement(int policy, int G, uint64_t N, const uint32_t* ids, const uint32_t* freq,
+                            double pct, double T_local, double T_remote, double T_cpu, Placement* out) {
+  if (G < 1 || G > UGC_MAX_DEVICE) return "num_device must be 1..8";
+  if (N == 0 || N >= 0x7fffffffull) return "num_total_item must be in [1, 2^31-1)";
+  if (!ids) return "rank_ids is required";
+  if (pct < 0 || pct > 100) return "cache_percent must be in [0, 100]";
+  std::string err;
+  switch (policy) {
+    case UGC_POLICY_INTUITIVE:
+      err = solve_intuitive(G, (uint32_t)N, ids, freq, pct, T_local, T_remote, T_cpu, out);
+      break;
+    case UGC_POLICY_REP: err = solve_rep(G, (uint32_t)N, ids, pct, out); break;
+    case UGC_POLICY_CLIQUE_PART: err = solve_clique(G, (uint32_t)N, ids, pct, out); break;
+    default: return "unknown policy (supported: 9 intuitive, 12 rep, 14 clique_part)";
+  }
+  out->valid = err.empty();
+  return err;
+}
+
+void classify_keys(const Placement& p, int reader, uint64_t N, std::vector<uint32_t> keys_by_src[],
+                   uint64_t* counts) {
+  const int G = p.num_device;
+  const uint8_t* acc = &p.block_access_from[(size_t)reader * p.num_block];
+  const uint32_t* n2b = p.nid_to_block.data();
+  // Two passes over fixed chunks keep the lists in ascending key order whatever the
+  // thread count.
+  const uint64_t kChunk = 1u << 20;
+  const int64_t n_chunk = (int64_t)((N + kChunk - 1) / kChunk);
+  std::vector<uint64_t> chunk_cnt((size_t)n_chunk * (G + 1), 0);
+#pragma omp parallel for schedule(dynamic, 4)
+  for (int64_t c = 0; c < n_chunk; c++) {
+    uint64_t local[UGC_MAX_DEVICE + 1] = {0};
+    const uint64_t end = std::min<uint64_t>(N, (uint64_t)(c + 1) * kChunk);
+    for (uint64_t k = (uint64_t)c * kChunk; k < end; k++) local[acc[n2b[k]]]++;
+    for (int s = 0; s <= G; s++) chunk_cnt[(size_t)c * (G + 1) + s] = local[s];
+  }
+  for (int s = 0; s <= G; s++) {
+    uint64_t run = 0;
+    for (int64_t c = 0; c < n_chunk; c++) {
+      uint64_t v = chunk_cnt[(size_t)c * (G + 1) + s];
+      chunk_cnt[(size_t)c * (G + 1) + s] = run;
+      run += v;
+    }
+    counts[s] = run;
+    if (s < G) keys_by_src[s].resize(run);
+  }
+#pragma omp parallel for schedule(dynamic, 4)
+  for (int64_t c = 0; c < n_chunk; c++) {
+    uint64_t pos[UGC_MAX_DEVICE + 1];
+    for (int s = 0; s <= G; s++) pos[s] = chunk_cnt[(size_t)c * (G + 1) + s];
+    const uint64_t end = std::min<uint64_t>(N, (uint64_t)(c + 1) * kChunk);
+    for (uint64_t k = (uint64_t)c * kChunk; k < end; k++) {
+      int s = acc[n2b[k]];
+      if (s < G) keys_by_src[s][pos[s]++] = (uint32_t)k;
+    }
+  }
+}
+
+}  // namespace ugc

@@ -1,0 +1,72 @@
+// Host-side (no CUDA) parts of the runtime: the placement arrays, the reference's non-MILP
+// placement heuristics, the B200 link model and the per-reader key classification.
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+namespace ugc {
+
+// The four arrays the policy hands to the cache runtime
+// (coll_cache_lib/facade.cc:238-261, coll_cache_lib/coll_cache/optimal_solver_class.h:34-70).
+struct Placement {
+  std::vector<uint32_t> nid_to_block;       // [N]
+  std::vector<uint8_t> block_placement;     // [B] bit g: rows of the block are stored on GPU g
+  std::vector<uint8_t> block_access_from;   // [G][B] source location per reader (G = host)
+  std::vector<double> block_density;        // [B] percent of N
+  int num_block = 0;
+  int num_device = 0;
+  bool valid = false;
+
+  uint8_t access(int reader, uint32_t block) const {
+    return block_access_from[(size_t)reader * num_block + block];
+  }
+  bool stored_on(int gpu, uint32_t key) const {
+    return (block_placement[nid_to_block[key]] >> gpu) & 1;
+  }
+};
+
+// Checks that the arrays describe a placement the runtime can serve: every reader's
+// source for a block stores that block, and a GPU that stores a block reads its own copy.
+// Returns an empty string or the reason.
+std::string validate_placement(const Placement& p, int num_device, uint64_t num_total_item);
+
+// Time-per-byte ratios local : peer : host on an NVSwitch-connected B200 box (HBM3e ~8 TB/s,
+// NVLink 5 900 GB/s per direction, PCIe Gen5 ~64 GB/s).  With G-1 peers read concurrently the
+// aggregated peer time is t_remote (the reference divides by the link count,
+// coll_cache_lib/coll_cache/asymm_link_desc.cc:412-419; on NVSwitch every peer shares the one
+// 900 GB/s port, so no division applies here).
+void b200_link_model(int num_device, double* t_local, double* t_remote, double* t_cpu);
+
+// IntuitiveSolver / RepSolver / CliquePartSolver of the reference
+// (coll_cache_lib/coll_cache/optimal_solver_class.cc:1251-1404, :1869-1924, :1926-2058).
+// cache_percent in percent.  Returns an empty string or the reason for failure.
+std::string solve_placement(int policy, int num_device, uint64_t num_total_item,
+                            const uint32_t* rank_ids, const uint32_t* rank_freqs,
+                            double cache_percent, double t_local, double t_remote, double t_cpu,
+                            Placement* out);
+
+// Keys served to `reader` by each GPU source, ascending key order
+// (replaces coll_cache_lib/cuda/cache_hashtable.cuh:741-835).  counts has G+1 entries
+// (index G = host keys, which are not listed).
+void classify_keys(const Placement& p, int reader, uint64_t num_total_item,
+                   std::vector<uint32_t> keys_by_src[], uint64_t* counts);
+
+// Keys of `input` for which pred(key) holds, order preserved
+// (replaces DetectKeysWithCond, coll_cache_lib/cuda/cache_hashtable.cuh:693-740).
+template <typename Pred>
+std::vector<uint32_t> select_keys(const std::vector<uint32_t>& input, Pred pred) {
+  std::vector<uint32_t> out;
+  for (uint32_t k : input)
+    if (pred(k)) out.push_back(k);
+  return out;
+}
+
+// Rule of the reference for choosing the direct-index table over the probing one
+// (coll_cache_lib/cache_context.cu:2489-2497 with cuda/cache_hashtable.cu:222-225).
+bool reference_prefers_flat_table(uint64_t cached_plus_remote, uint64_t num_total_item);
+
+// Rows of one GPU's cache slice (coll_cache_lib/cache_context.cu:2473).
+uint64_t cache_capacity_rows(uint64_t num_total_item, double cache_fraction);
+
+}  // namespace ugc

@@ -1,0 +1,232 @@
+"""Python face of the C ABI: a thin object wrapper that moves pointers, nothing else.
+
+PyTorch appears here only to own device memory and streams; every operation is a call
+into ``libugache_b200.so``.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import (POLICY_CLIQUE_PART, POLICY_INTUITIVE, POLICY_REP, TABLE_AUTO, TABLE_FLAT,
+                   TABLE_HASHED, UgcError, check)
+
+POLICIES = {"intuitive": POLICY_INTUITIVE, "coll_intuitive": POLICY_INTUITIVE,
+            "rep": POLICY_REP, "clique_part": POLICY_CLIQUE_PART}
+
+
+class PlacementArrays:
+    """The four placement arrays (numpy, host)."""
+
+    def __init__(self, nid_to_block, block_placement, block_access_from, block_density):
+        self.nid_to_block = np.ascontiguousarray(nid_to_block, dtype=np.uint32)
+        self.block_placement = np.ascontiguousarray(block_placement, dtype=np.uint8)
+        self.block_access_from = np.ascontiguousarray(block_access_from, dtype=np.uint8)
+        self.block_density = np.ascontiguousarray(block_density, dtype=np.float64)
+
+    @property
+    def num_block(self):
+        return len(self.block_placement)
+
+    @property
+    def num_device(self):
+        return self.block_access_from.shape[0]
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def link_model(num_device):
+    tl, tr, tc = C.c_double(), C.c_double(), C.c_double()
+    check(_lib.lib().ugc_link_model(num_device, C.byref(tl), C.byref(tr), C.byref(tc)))
+    return tl.value, tr.value, tc.value
+
+
+def solve_placement(policy, num_device, rank_ids, rank_freqs, cache_percent, t_local=None,
+                    t_remote=None, t_cpu=None):
+    """The reference's non-MILP placement heuristics; cache_percent in percent (0..100)."""
+    pol = POLICIES[policy] if isinstance(policy, str) else int(policy)
+    rank_ids = np.ascontiguousarray(rank_ids, dtype=np.uint32)
+    N = len(rank_ids)
+    freqs = None if rank_freqs is None else np.ascontiguousarray(rank_freqs, dtype=np.uint32)
+    dl, dr, dc = link_model(num_device)
+    t_local = dl if t_local is None else t_local
+    t_remote = dr if t_remote is None else t_remote
+    t_cpu = dc if t_cpu is None else t_cpu
+    B = num_device + 2
+    n2b = np.zeros(N, dtype=np.uint32)
+    bp = np.zeros(B, dtype=np.uint8)
+    ba = np.zeros(num_device * B, dtype=np.uint8)
+    bd = np.zeros(B, dtype=np.float64)
+    nb = C.c_int(0)
+    check(_lib.lib().ugc_solve_placement(pol, num_device, N, _ptr(rank_ids),
+                                         _ptr(freqs) if freqs is not None else None,
+                                         cache_percent, t_local, t_remote, t_cpu, _ptr(n2b),
+                                         _ptr(bp), _ptr(ba), _ptr(bd), C.byref(nb)))
+    b = nb.value
+    return PlacementArrays(n2b, bp[:b].copy(), ba[:num_device * b].reshape(num_device, b).copy(),
+                           bd[:b].copy())
+
+
+class Cache:
+    """One process' view of the multi-GPU embedding cache (a ``ugc_ctx``)."""
+
+    def __init__(self, num_device, num_total_item, row_bytes, cache_percentage, max_batch=1 << 20,
+                 empty_feat=0, table_kind=TABLE_AUTO, gather_ctas_per_sm=0, host_ctas=0,
+                 remote_ctas=0, register_host=True):
+        L = _lib.lib()
+        cfg = _lib.Config()
+        check(L.ugc_config_default(C.byref(cfg)))
+        cfg.num_device = num_device
+        cfg.num_total_item = num_total_item
+        cfg.row_bytes = row_bytes
+        cfg.cache_percentage = cache_percentage
+        cfg.max_batch = max_batch
+        cfg.empty_feat = empty_feat
+        cfg.table_kind = table_kind
+        cfg.gather_ctas_per_sm = gather_ctas_per_sm
+        cfg.host_ctas = host_ctas
+        cfg.remote_ctas = remote_ctas
+        cfg.register_host = 1 if register_host else 0
+        self.cfg = cfg
+        self._h = C.c_void_p()
+        check(L.ugc_create(C.byref(cfg), C.byref(self._h)))
+        self._keep = []  # host arrays the library reads in place
+
+    # -- lifetime -----------------------------------------------------------------
+    def close(self):
+        if self._h:
+            _lib.lib().ugc_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- placement ----------------------------------------------------------------
+    def set_placement(self, p):
+        check(_lib.lib().ugc_set_placement(self._h, _ptr(p.nid_to_block), _ptr(p.block_placement),
+                                           _ptr(p.block_access_from), _ptr(p.block_density),
+                                           p.num_block))
+
+    def classify_keys(self, replica_id, want_keys=False):
+        G = self.cfg.num_device
+        counts = np.zeros(G + 1, dtype=np.uint64)
+        keys = np.zeros(self.cfg.num_total_item, dtype=np.uint32) if want_keys else None
+        check(_lib.lib().ugc_classify_keys(self._h, replica_id, _ptr(counts),
+                                           _ptr(keys) if want_keys else None))
+        if not want_keys:
+            return counts
+        out, pos = [], 0
+        for s in range(G):
+            out.append(keys[pos:pos + int(counts[s])].copy())
+            pos += int(counts[s])
+        return counts, out
+
+    # -- build ----------------------------------------------------------------------
+    def build(self, replica_id, device_id, host_table_ptr, stream=0):
+        """host_table_ptr: integer address of the host table (kept alive by the caller)."""
+        check(_lib.lib().ugc_build(self._h, replica_id, device_id, C.c_void_p(host_table_ptr),
+                                   C.c_void_p(stream)))
+
+    def export(self, replica_id):
+        h = _lib.PeerHandle()
+        check(_lib.lib().ugc_export(self._h, replica_id, C.byref(h)))
+        return h
+
+    def import_peer(self, replica_id, handle):
+        check(_lib.lib().ugc_import_peer(self._h, replica_id, C.byref(handle)))
+
+    def connect_local(self):
+        check(_lib.lib().ugc_connect_local(self._h))
+
+    def attach_peers(self, replica_id, stream=0):
+        check(_lib.lib().ugc_attach_peers(self._h, replica_id, C.c_void_p(stream)))
+
+    # -- lookup ---------------------------------------------------------------------
+    def lookup_ptr(self, replica_id, keys_ptr, key_bytes, n, out_ptr, stream=0):
+        fn = _lib.lib().ugc_lookup_i64 if key_bytes == 8 else _lib.lib().ugc_lookup_u32
+        check(fn(self._h, replica_id, C.c_void_p(keys_ptr), n, C.c_void_p(out_ptr),
+                 C.c_void_p(stream)))
+
+    def lookup(self, replica_id, keys, out=None, stream=None):
+        """keys: CUDA tensor (int64 / int32 / uint32); returns a uint8 [n, row_bytes] tensor
+        unless ``out`` (any dtype, n*row_bytes bytes) is given."""
+        import torch
+        n = keys.numel()
+        if keys.dtype == torch.int64:
+            kb = 8
+        elif keys.dtype in (torch.int32, torch.uint32):
+            kb = 4
+        else:
+            raise TypeError("keys must be int64, int32 or uint32")
+        if out is None:
+            out = torch.empty((n, self.cfg.row_bytes), dtype=torch.uint8, device=keys.device)
+        s = torch.cuda.current_stream(keys.device).cuda_stream if stream is None else stream
+        self.lookup_ptr(replica_id, keys.data_ptr(), kb, n, out.data_ptr(), s)
+        return out
+
+    def lookup_host(self, replica_id, keys_np, out_np, stream=0):
+        keys_np = np.ascontiguousarray(keys_np)
+        kb = keys_np.dtype.itemsize
+        check(_lib.lib().ugc_lookup_host(self._h, replica_id, _ptr(keys_np), kb, len(keys_np),
+                                         _ptr(out_np), C.c_void_p(stream)))
+        return out_np
+
+    def lookup_host_ptr(self, replica_id, keys_ptr, key_bytes, n, out_ptr, stream=0):
+        check(_lib.lib().ugc_lookup_host(self._h, replica_id, C.c_void_p(keys_ptr), key_bytes, n,
+                                         C.c_void_p(out_ptr), C.c_void_p(stream)))
+
+    # -- refresh ----------------------------------------------------------------------
+    def refresh_set_placement(self, p):
+        check(_lib.lib().ugc_refresh_set_placement(self._h, _ptr(p.nid_to_block),
+                                                   _ptr(p.block_placement),
+                                                   _ptr(p.block_access_from),
+                                                   _ptr(p.block_density), p.num_block))
+
+    def refresh_evict(self, replica_id, stream=0):
+        check(_lib.lib().ugc_refresh_evict(self._h, replica_id, C.c_void_p(stream)))
+
+    def refresh_fill(self, replica_id, stream=0):
+        check(_lib.lib().ugc_refresh_fill(self._h, replica_id, C.c_void_p(stream)))
+
+    def refresh_attach(self, replica_id, stream=0):
+        check(_lib.lib().ugc_refresh_attach(self._h, replica_id, C.c_void_p(stream)))
+
+    def refresh_commit(self):
+        check(_lib.lib().ugc_refresh_commit(self._h))
+
+    def refresh_all_local(self, p, replicas, stream=0):
+        """Whole refresh for replicas that all live in this process (no barriers needed:
+        the phases run replica after replica)."""
+        self.refresh_set_placement(p)
+        for r in replicas:
+            self.refresh_evict(r, stream)
+        for r in replicas:
+            self.refresh_fill(r, stream)
+        for r in replicas:
+            self.refresh_attach(r, stream)
+        self.refresh_commit()
+
+    # -- introspection ------------------------------------------------------------------
+    def stats(self, replica_id):
+        s = _lib.Stats()
+        check(_lib.lib().ugc_stats(self._h, replica_id, C.byref(s)))
+        return {name: getattr(s, name) for name, _ in s._fields_}
+
+    def table_words(self, replica_id, keys_u32, stream=None):
+        import torch
+        words = torch.empty(keys_u32.numel(), dtype=torch.int32, device=keys_u32.device)
+        s = torch.cuda.current_stream(keys_u32.device).cuda_stream if stream is None else stream
+        check(_lib.lib().ugc_table_words(self._h, replica_id, C.c_void_p(keys_u32.data_ptr()),
+                                         keys_u32.numel(), C.c_void_p(words.data_ptr()),
+                                         C.c_void_p(s)))
+        return words
+
+
+def gen_table(dst_ptr, seed, row_begin, n_rows, dim, elem_bytes, stream=0):
+    check(_lib.lib().ugc_gen_table(C.c_void_p(dst_ptr), seed, row_begin, n_rows, dim, elem_bytes,
+                                   C.c_void_p(stream)))
