@@ -75,6 +75,7 @@ typedef struct {
   int32_t gather_ctas_per_sm; /* CTAs of the gather kernel per SM; 0 = default          */
   int32_t host_ctas;          /* CTA budget of the host-row group; 0 = default          */
   int32_t remote_ctas;        /* CTA budget of the peer-row group; 0 = default          */
+  int32_t gather_vec_bytes;   /* 16 (default) or 32: bytes per lane per load in the gather */
   ugc_alloc_fn alloc;
   ugc_free_fn free;
   void* alloc_user;
@@ -225,6 +226,15 @@ int ugc_refresh_commit(ugc_ctx* ctx);
 
 /* -- introspection --------------------------------------------------------------------- */
 int ugc_stats(ugc_ctx* ctx, int replica_id, ugc_stats_t* out);
+
+/* Per-kernel device timing of the lookups issued between begin and end: CUDA events are
+ * recorded on the lookup's stream around the lookup_group kernel and around the gather
+ * kernel.  Replaces the host-timer phase breakdown the reference logs per step
+ * (kLogL3CacheGetIndexTime / kLogL3CacheCombine*Time, coll_cache_lib/cache_context.cu:1662-1679).
+ * ugc_profile_end synchronises the device and returns the summed kernel times (ms). */
+int ugc_profile_begin(ugc_ctx* ctx, int replica_id, int max_lookups);
+int ugc_profile_end(ugc_ctx* ctx, int replica_id, double* lookup_group_ms, double* gather_ms,
+                    uint64_t* lookups);
 
 /* Debug / test aid: the packed (location << 28 | offset) word the replica's table holds
  * for each of n keys (0xffffffff = not in the table, i.e. served by the host).  keys and

@@ -34,6 +34,7 @@ class Config(C.Structure):
         ("gather_ctas_per_sm", C.c_int32),
         ("host_ctas", C.c_int32),
         ("remote_ctas", C.c_int32),
+        ("gather_vec_bytes", C.c_int32),
         ("alloc", ALLOC_FN),
         ("free", FREE_FN),
         ("alloc_user", C.c_void_p),
@@ -111,6 +112,8 @@ SIGNATURES = {
     "ugc_refresh_attach": (_I, [_P, _I, _P]),
     "ugc_refresh_commit": (_I, [_P]),
     "ugc_stats": (_I, [_P, _I, C.POINTER(Stats)]),
+    "ugc_profile_begin": (_I, [_P, _I, _I]),
+    "ugc_profile_end": (_I, [_P, _I, C.POINTER(_D), C.POINTER(_D), C.POINTER(_U64)]),
     "ugc_table_words": (_I, [_P, _I, _P, _SZ, _P, _P]),
     "ugc_gen_table": (_I, [_P, _U64, _U64, _U64, _U64, _I, _P]),
 }

@@ -104,6 +104,10 @@ struct Replica {
   uint64_t lookups = 0;
   int gather_grid = 0;
   int host_ctas = 0, remote_ctas = 0;
+  // per-kernel profiling (three events per lookup)
+  std::vector<cudaEvent_t> prof_events;
+  size_t prof_used = 0;
+  bool prof_on = false;
 };
 
 }  // namespace
@@ -249,6 +253,7 @@ int alloc_table(ugc_ctx* c, Replica* r, uint64_t entries, cudaStream_t s) {
 
 void release_replica(ugc_ctx* c, Replica* r) {
   if (r->device >= 0) cudaSetDevice(r->device);
+  for (cudaEvent_t e : r->prof_events) cudaEventDestroy(e);
   for (int i = 0; i < r->n_ipc_opened; i++) cudaIpcCloseMemHandle(r->ipc_opened[i]);
   ctx_free(c, r->slice);
   ctx_free(c, r->table_mem);
@@ -286,11 +291,18 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
       if (s2 != r->id && !r->keys_by_src[s2].empty())
         return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
   }
+  const bool prof = r->prof_on && r->prof_used + 3 <= r->prof_events.size();
+  if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used], s));
   UGC_CUDA(launch_lookup_group(keys, key_bytes, (uint32_t)n, r->table, (uint32_t)r->id,
                                (uint32_t)c->cfg.num_device, c->cfg.empty_feat, r->list[kGroupLocal],
                                r->list[kGroupRemote], r->list[kGroupHost], r->counters, s));
+  if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 1], s));
   GatherParams p = gather_params(c, r, out, (uint32_t)n);
-  UGC_CUDA(launch_gather_roles(p, r->gather_grid, 16, s));
+  UGC_CUDA(launch_gather_roles(p, r->gather_grid, c->cfg.gather_vec_bytes == 32 ? 32 : 16, s));
+  if (prof) {
+    UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 2], s));
+    r->prof_used += 3;
+  }
   r->lookups++;
   return UGC_OK;
 }
@@ -854,6 +866,44 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   out->err_key_range = h.err_key_range;
   out->err_table = h.err_table;
   out->lookups = r->lookups;
+  return UGC_OK;
+}
+
+int ugc_profile_begin(ugc_ctx* c, int replica_id, int max_lookups) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (max_lookups < 1 || max_lookups > (1 << 20)) return fail(UGC_ERR_INVALID, "max_lookups out of range");
+  UGC_CUDA(cudaSetDevice(r->device));
+  while (r->prof_events.size() < (size_t)max_lookups * 3) {
+    cudaEvent_t e;
+    UGC_CUDA(cudaEventCreate(&e));
+    r->prof_events.push_back(e);
+  }
+  r->prof_used = 0;
+  r->prof_on = true;
+  return UGC_OK;
+}
+
+int ugc_profile_end(ugc_ctx* c, int replica_id, double* lookup_ms, double* gather_ms, uint64_t* lookups) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (!lookup_ms || !gather_ms || !lookups) return fail(UGC_ERR_INVALID, "null output");
+  if (!r->prof_on) return fail(UGC_ERR_STATE, "profiling is not on");
+  UGC_CUDA(cudaSetDevice(r->device));
+  UGC_CUDA(cudaDeviceSynchronize());
+  double a = 0, b = 0;
+  for (size_t i = 0; i + 3 <= r->prof_used; i += 3) {
+    float ms = 0;
+    UGC_CUDA(cudaEventElapsedTime(&ms, r->prof_events[i], r->prof_events[i + 1]));
+    a += ms;
+    UGC_CUDA(cudaEventElapsedTime(&ms, r->prof_events[i + 1], r->prof_events[i + 2]));
+    b += ms;
+  }
+  *lookup_ms = a;
+  *gather_ms = b;
+  *lookups = r->prof_used / 3;
+  r->prof_on = false;
+  r->prof_used = 0;
   return UGC_OK;
 }
 

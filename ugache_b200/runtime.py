@@ -74,7 +74,7 @@ class Cache:
 
     def __init__(self, num_device, num_total_item, row_bytes, cache_percentage, max_batch=1 << 20,
                  empty_feat=0, table_kind=TABLE_AUTO, gather_ctas_per_sm=0, host_ctas=0,
-                 remote_ctas=0, register_host=True):
+                 remote_ctas=0, register_host=True, gather_vec_bytes=16):
         L = _lib.lib()
         cfg = _lib.Config()
         check(L.ugc_config_default(C.byref(cfg)))
@@ -88,6 +88,7 @@ class Cache:
         cfg.gather_ctas_per_sm = gather_ctas_per_sm
         cfg.host_ctas = host_ctas
         cfg.remote_ctas = remote_ctas
+        cfg.gather_vec_bytes = gather_vec_bytes
         cfg.register_host = 1 if register_host else 0
         self.cfg = cfg
         self._h = C.c_void_p()
@@ -216,6 +217,15 @@ class Cache:
         s = _lib.Stats()
         check(_lib.lib().ugc_stats(self._h, replica_id, C.byref(s)))
         return {name: getattr(s, name) for name, _ in s._fields_}
+
+    def profile_begin(self, replica_id, max_lookups):
+        check(_lib.lib().ugc_profile_begin(self._h, replica_id, max_lookups))
+
+    def profile_end(self, replica_id):
+        """(lookup_group ms, gather ms, lookups) summed over the profiled lookups."""
+        a, b, n = C.c_double(), C.c_double(), C.c_uint64()
+        check(_lib.lib().ugc_profile_end(self._h, replica_id, C.byref(a), C.byref(b), C.byref(n)))
+        return a.value, b.value, n.value
 
     def table_words(self, replica_id, keys_u32, stream=None):
         import torch
