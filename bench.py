@@ -1,0 +1,561 @@
+#!/usr/bin/env python
+"""Benchmark of the embedding-extraction hot path.
+
+One "step" = one lookup of one key batch per GPU: keys -> table -> grouped by source ->
+rows gathered from local HBM / peer HBM / pinned host memory into a dense [n, dim] output.
+
+Default workload (the DLR-shaped configuration): one hashed id space of 100 M rows x 128 fp32
+(51.2 GB) in pinned host memory, 10 % of the rows cached per GPU by hotness, 212,992 int64
+keys per GPU per step (8192 x 26 fields), Zipf alpha 1.2, seeded per rank, not deduplicated.
+Data are synthetic (seeded generators of ugache_b200.workload).
+
+    python bench.py --gpus 1 --steps 100 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...     # the CPU restatement on the box's host cores
+
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import mmap
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+NOMINAL = dict(hbm=8000.0, nvlink=900.0, pcie=64.0)          # GB/s, the metric's roofline
+FALLBACK_HBM = 6650.0                                        # GB/s if no measured peak file
+MEASURED_NVLINK = 770.0                                      # GB/s per direction, peer copy
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=100_000_000)
+    ap.add_argument("--dim", type=int, default=128)
+    ap.add_argument("--dtype", default="float32", choices=["float32", "float16"])
+    ap.add_argument("--cache-pct", type=float, default=0.10, help="fraction of rows per GPU")
+    ap.add_argument("--alpha", type=float, default=1.2)
+    ap.add_argument("--batch", type=int, default=8192 * 26)
+    ap.add_argument("--policy", default="intuitive", choices=["intuitive", "rep", "clique_part"])
+    ap.add_argument("--table-kind", type=int, default=0)
+    ap.add_argument("--empty-feat", type=int, default=0,
+                    help="k>0: host table holds 2^k rows, host offsets wrap (mock)")
+    ap.add_argument("--seed", type=int, default=2024)
+    ap.add_argument("--vec", type=int, default=16)
+    ap.add_argument("--ctas-per-sm", type=int, default=0)
+    ap.add_argument("--host-ctas", type=int, default=0)
+    ap.add_argument("--remote-ctas", type=int, default=0)
+    ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 30)")
+    ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--verify", type=int, default=1, help="check one batch against the oracle")
+    ap.add_argument("--sweep-out", default="", help="write extra per-phase numbers here (json)")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+
+    def summary(self, t0, t1):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.rows:
+            if ts < t0 - 0.05 or ts > t1 + 0.15:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM, "fallback"
+
+
+# ---------------------------------------------------------------------------------------
+class HostTable:
+    """The host-resident embedding table: anonymous memory for one process, a /dev/shm file
+    shared by all ranks otherwise (the reference shares it the same way,
+    python/collcache/torch/adapter.cc:239-270)."""
+
+    def __init__(self, rows, row_bytes, rank, world, tag, library_owned=False):
+        self.nbytes = rows * row_bytes
+        self.path = None
+        self.owned = False
+        if world == 1 and library_owned:
+            # one process: let the library allocate (large GPU pages for the host table)
+            import ctypes
+            from ugache_b200 import runtime as rt
+            self.ptr, self.dev_ptr = rt.host_alloc(self.nbytes)
+            self.owned = True
+            self.rank = rank
+            self.mm = (ctypes.c_uint8 * self.nbytes).from_address(self.ptr)
+            self.np = np.ctypeslib.as_array(self.mm)
+            return
+        if world == 1:
+            self.mm = mmap.mmap(-1, self.nbytes, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
+        else:
+            self.path = "/dev/shm/ugache_b200_table_%s" % tag
+            if rank == 0:
+                fd = os.open(self.path, os.O_CREAT | os.O_RDWR | os.O_TRUNC, 0o600)
+                os.ftruncate(fd, self.nbytes)
+            barrier()
+            if rank != 0:
+                fd = os.open(self.path, os.O_RDWR)
+            self.mm = mmap.mmap(fd, self.nbytes, flags=mmap.MAP_SHARED)
+            os.close(fd)
+        self.np = np.frombuffer(self.mm, dtype=np.uint8)
+        self.ptr = self.np.ctypes.data
+        self.dev_ptr = None
+        self.rank = rank
+
+    def map_for_gpu(self):
+        """Device-side address of the table (registers the memory if the library does not own it)."""
+        if self.dev_ptr is None:
+            from ugache_b200 import runtime as rt
+            self.dev_ptr = rt.host_register(self.ptr, self.nbytes)
+        return self.dev_ptr
+
+    def release(self):
+        from ugache_b200 import runtime as rt
+        try:
+            if self.owned:
+                rt.host_free(self.ptr)
+            elif self.dev_ptr is not None:
+                rt.host_unregister(self.ptr)
+        except Exception:
+            pass
+
+    def unlink(self):
+        if self.path and self.rank == 0:
+            try:
+                os.unlink(self.path)
+            except OSError:
+                pass
+
+
+_DIST = {"on": False}
+
+
+def barrier():
+    if _DIST["on"]:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def all_max(x):
+    if not _DIST["on"]:
+        return x
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def all_sum(x):
+    if not _DIST["on"]:
+        return x
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def workload_name(a):
+    return ("dlr_zipf%.2f_%dMx%d%s_cache%.0f%%_batch%d" %
+            (a.alpha, a.rows // 1_000_000, a.dim, "f32" if a.dtype == "float32" else "f16",
+             a.cache_pct * 100, a.batch))
+
+
+def make_keys(a, rank, count):
+    from ugache_b200 import workload as wl
+    out = np.empty((count, a.batch), dtype=np.int64)
+    for i in range(count):
+        out[i] = wl.zipf_keys(a.seed * 1000003 + rank * 1009 + i, a.batch, a.rows, a.alpha)
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+def run_reference(a):
+    """The reference has no CPU extraction routine; its gather (extract_data) restated on the
+    CPU is timed here on the box's host cores, all threads, over the same table and keys."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    elem = 4 if a.dtype == "float32" else 2
+    row_bytes = a.dim * elem
+    host_rows = (1 << a.empty_feat) if a.empty_feat else a.rows
+    try:
+        mm = mmap.mmap(-1, host_rows * row_bytes, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
+    except (OSError, MemoryError, ValueError):
+        a.empty_feat = 24
+        host_rows = 1 << 24
+        mm = mmap.mmap(-1, host_rows * row_bytes, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
+    table = np.frombuffer(mm, dtype=np.float32 if elem == 4 else np.float16).reshape(host_rows, a.dim)
+    chunk = 1 << 20
+    lib = orc.lib()
+    import ctypes as C
+    for r0 in range(0, host_rows, chunk):
+        n = min(chunk, host_rows - r0)
+        fn = lib.orc_gen_rows_f32 if elem == 4 else lib.orc_gen_rows_f16
+        fn(C.c_uint64(a.seed), C.c_uint64(r0), C.c_uint64(n), C.c_uint64(a.dim),
+           C.c_void_p(table[r0:r0 + n].ctypes.data))
+    threads = orc.max_threads()
+    total = a.warmup + a.steps
+    keys = make_keys(a, 0, total)
+    out = np.empty((a.batch, a.dim), dtype=table.dtype)
+    for i in range(a.warmup):
+        orc.gather(table, keys[i], empty_feat=a.empty_feat, num_threads=threads, out=out)
+    t0 = time.perf_counter()
+    for i in range(a.warmup, total):
+        orc.gather(table, keys[i], empty_feat=a.empty_feat, num_threads=threads, out=out)
+    dt = time.perf_counter() - t0
+    gbs = a.steps * a.batch * row_bytes / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "extracted_embedding_throughput", "value": gbs,
+        "unit": "GB/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": dt / a.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": workload_name(a), "rows": a.rows, "dim": a.dim,
+                   "keys_per_step": a.batch, "alpha": a.alpha, "empty_feat": a.empty_feat,
+                   "note": "CPU restatement of the reference gather; the reference itself has "
+                           "no CPU extraction routine"},
+        "mkeys_per_s": a.steps * a.batch / dt / 1e6,
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "%d full batches of %d keys" % (a.steps, a.batch)},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------
+def run_ours(a):
+    import torch
+    from ugache_b200 import build as ubuild
+    ubuild.build()
+    from ugache_b200 import runtime as rt, workload as wl
+
+    rank, world, local = dist_env()
+    if world != a.gpus and world > 1:
+        a.gpus = world
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        _DIST["on"] = True
+    G = world
+    elem = 4 if a.dtype == "float32" else 2
+    row_bytes = a.dim * elem
+    tag = os.environ.get("MASTER_PORT", "0")
+    t_setup = time.time()
+
+    # ---- host table ---------------------------------------------------------------
+    note = {}
+    try:
+        host_rows = (1 << a.empty_feat) if a.empty_feat else a.rows
+        table = HostTable(host_rows, row_bytes, rank, world, tag, library_owned=True)
+        table_dev = table.map_for_gpu()
+    except Exception as e:  # not enough host memory: the reference's mock-table mode
+        note["host_table_fallback"] = "%s: %s" % (type(e).__name__, str(e)[:80])
+        a.empty_feat = 24
+        host_rows = 1 << 24
+        table = HostTable(host_rows, row_bytes, rank, world, tag + "m", library_owned=True)
+        table_dev = table.map_for_gpu()
+    stream = torch.cuda.current_stream().cuda_stream
+    if rank == 0:
+        rt.gen_table(table_dev, a.seed, 0, host_rows, a.dim, elem, stream)
+        torch.cuda.synchronize()
+    barrier()
+
+    # ---- hotness, placement, build ---------------------------------------------------
+    ids, freqs = wl.analytic_hotness(a.rows, a.alpha)
+    placement = rt.solve_placement(a.policy, G, ids, freqs, a.cache_pct * 100.0)
+    del ids, freqs
+    cache = rt.Cache(G, a.rows, row_bytes, a.cache_pct, max_batch=a.batch,
+                     empty_feat=a.empty_feat, table_kind=a.table_kind,
+                     gather_ctas_per_sm=a.ctas_per_sm, host_ctas=a.host_ctas,
+                     remote_ctas=a.remote_ctas, gather_vec_bytes=a.vec, register_host=False)
+    cache.set_placement(placement)
+    cache.build(rank, local, table.ptr, stream)
+    if world > 1:
+        import torch.distributed as dist
+        h = cache.export(rank)
+        blob = torch.frombuffer(bytearray(bytes(h)), dtype=torch.uint8).to(dev)
+        gathered = [torch.empty_like(blob) for _ in range(world)]
+        dist.all_gather(gathered, blob)
+        from ugache_b200 import _lib
+        for r in range(world):
+            if r != rank:
+                ph = _lib.PeerHandle.from_buffer_copy(bytes(gathered[r].cpu().numpy()))
+                cache.import_peer(rank, ph)
+        barrier()
+        cache.attach_peers(rank, stream)
+        barrier()
+    st = cache.stats(rank)
+    setup_s = time.time() - t_setup
+
+    # ---- keys ---------------------------------------------------------------------------
+    total = a.warmup + a.steps
+    keys_np = make_keys(a, rank, total)
+    keys_dev = torch.from_numpy(keys_np).to(dev)
+    out = torch.empty((a.batch, row_bytes), dtype=torch.uint8, device=dev)
+
+    def step(i):
+        cache.lookup_ptr(rank, keys_dev[i].data_ptr(), 8, a.batch, out.data_ptr(), stream)
+
+    # ---- optional verification of one batch against the oracle -------------------------
+    verified = None
+    if a.verify and rank == 0:
+        from oracle import oracle as orc
+        step(0)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        tv = table.np.reshape(host_rows, row_bytes)
+        want = orc.gather(tv, keys_np[0], empty_feat=a.empty_feat)
+        verified = bool(got.tobytes() == want.tobytes())
+        # the table itself against the oracle's generator on sampled rows
+        rows = np.unique(keys_np[0][:64] % host_rows)
+        want_rows = orc.gen_rows_for_keys(a.seed, rows, a.dim,
+                                          np.float32 if elem == 4 else np.float16)
+        verified = verified and bool(tv[rows].tobytes() == want_rows.tobytes())
+        if not verified:
+            raise SystemExit("bench: lookup output differs from the oracle")
+    barrier()
+
+    # ---- warm-up, then the timed region (inputs resident in HBM) ----------------------
+    for i in range(a.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    e0.record()
+    for i in range(a.warmup, total):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    barrier()
+    ms_total = all_max(e0.elapsed_time(e1))
+    st_last = cache.stats(rank)
+
+    # ---- same steps again with per-kernel events (for the roofline of the gather) ------
+    cache.profile_begin(rank, a.steps)
+    for i in range(a.warmup, total):
+        step(i)
+    lk_ms, ga_ms, nprof = cache.profile_end(rank)
+    t2 = time.time()
+    sampler.stop()
+    clocks = sampler.summary(t0, t2)
+
+    # per-source bytes over the timed steps (host recount through the table words)
+    words = cache.table_words(rank, keys_dev[a.warmup:total].reshape(-1).to(torch.int32)).view(-1)
+    torch.cuda.synchronize()
+    w = words.cpu().numpy().view(np.uint32)
+    n_host = int((w == 0xFFFFFFFF).sum())
+    n_local = int(((w != 0xFFFFFFFF) & ((w >> 28) == rank)).sum())
+    n_all = len(w)
+    n_remote = n_all - n_host - n_local
+    del words, w
+
+    # ---- end to end with host buffers -------------------------------------------------
+    e2e = None
+    if not a.no_e2e:
+        ke = a.e2e_steps or min(a.steps, 30)
+        kpin = torch.from_numpy(keys_np[a.warmup:a.warmup + ke]).pin_memory()
+        opin = torch.empty((a.batch, row_bytes), dtype=torch.uint8).pin_memory()
+        for i in range(2):
+            cache.lookup_host_ptr(rank, kpin[i].data_ptr(), 8, a.batch, opin.data_ptr(), stream)
+        barrier()
+        torch.cuda.synchronize()
+        ee0, ee1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ee0.record()
+        for i in range(ke):
+            cache.lookup_host_ptr(rank, kpin[i].data_ptr(), 8, a.batch, opin.data_ptr(), stream)
+        ee1.record()
+        torch.cuda.synchronize()
+        barrier()
+        e2e_ms = all_max(ee0.elapsed_time(ee1))
+        e2e = {"value": G * ke * a.batch * row_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": a.batch * 8, "d2h_bytes_per_step": a.batch * row_bytes,
+               "steps": ke, "ms_per_step": e2e_ms / ke,
+               "note": "ugc_lookup_host: pinned host keys in, pinned host rows out, every step"}
+
+    # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not a.no_cpu_baseline:
+        from oracle import oracle as orc
+        tv = table.np.reshape(host_rows, row_bytes)
+        threads = orc.max_threads()
+        o = np.empty((a.batch, row_bytes), dtype=np.uint8)
+        orc.gather(tv, keys_np[0], empty_feat=a.empty_feat, num_threads=threads, out=o)
+        c0 = time.perf_counter()
+        for i in range(a.cpu_steps):
+            orc.gather(tv, keys_np[1 + i], empty_feat=a.empty_feat, num_threads=threads, out=o)
+        cdt = time.perf_counter() - c0
+        cpu = {"value": a.cpu_steps * a.batch * row_bytes / cdt / 1e9, "unit": "GB/s",
+               "cores": threads, "kind": "port",
+               "sample": "%d batches of %d keys over the same host table" % (a.cpu_steps, a.batch)}
+
+    # ---- the line -------------------------------------------------------------------------
+    sec = ms_total * 1e-3
+    bytes_out_rank = a.steps * a.batch * row_bytes
+    value = G * bytes_out_rank / sec / 1e9
+    hbm_peak, peak_kind = measured_peaks()
+    gather_ms_avg = ga_ms / max(nprof, 1)
+    lookup_ms_avg = lk_ms / max(nprof, 1)
+    algo_bytes = 2.0 * a.batch * row_bytes
+    achieved = algo_bytes / (gather_ms_avg * 1e-3) / 1e9 if gather_ms_avg > 0 else 0.0
+    # mixed-source roofline per step and GPU: max over sources of bytes / bandwidth
+    b_loc = n_local / a.steps * row_bytes
+    b_rem = n_remote / a.steps * row_bytes
+    b_host = n_host / a.steps * row_bytes
+    b_out = a.batch * row_bytes
+
+    def tstar(hbm, nvl, pcie):
+        return max((b_loc + b_out) / hbm, b_rem / nvl, b_host / pcie) / 1e9 * 1e6  # us
+
+    step_us = ms_total / a.steps * 1e3
+    mixed = {
+        "t_star_us_nominal": tstar(NOMINAL["hbm"], NOMINAL["nvlink"], NOMINAL["pcie"]),
+        "t_star_us_measured_links": tstar(hbm_peak, MEASURED_NVLINK, NOMINAL["pcie"]),
+        "step_us": step_us,
+        "bytes_per_step": {"local": b_loc, "remote": b_rem, "host": b_host, "out": b_out},
+    }
+    mixed["frac_nominal"] = mixed["t_star_us_nominal"] / step_us
+    mixed["frac_measured_links"] = mixed["t_star_us_measured_links"] / step_us
+    line = {
+        "metric": "extracted_embedding_throughput", "value": value, "unit": "GB/s",
+        "n_gpus": G, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_total / a.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+        "data": "synthetic",
+        "config": {"workload": workload_name(a), "rows": a.rows, "dim": a.dim,
+                   "row_bytes": row_bytes, "keys_per_gpu_per_step": a.batch, "alpha": a.alpha,
+                   "cache_fraction_per_gpu": a.cache_pct, "policy": a.policy,
+                   "table": {1: "flat", 2: "hashed"}.get(st["table_kind"], "?"),
+                   "parallelism": "replicas=%d, cache partitioned+replicated by placement, "
+                                  "one-sided P2P reads, no collective" % G,
+                   "empty_feat": a.empty_feat,
+                   "l2": "inputs larger than L2 (%.1f GB slice + %.1f GB host table), a new key "
+                         "batch every step, no flush" % (st["slice_bytes"] / 1e9,
+                                                         host_rows * row_bytes / 1e9),
+                   **note},
+        "per_gpu_gbs": value / G, "mkeys_per_s_per_gpu": a.steps * a.batch / sec / 1e6,
+        "source_split": {"local": n_local / n_all, "remote": n_remote / n_all,
+                         "host": n_host / n_all},
+        "mixed_roofline": mixed,
+        "roofline": {"bound": "hbm", "kernel": "gather_roles", "achieved": achieved,
+                     "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "peak_kind": "of " + peak_kind, "traffic": None,
+                     "algorithmic_bytes_per_launch": algo_bytes,
+                     "avg_launch_us": gather_ms_avg * 1e3,
+                     "lookup_group_avg_us": lookup_ms_avg * 1e3},
+        "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": 2 * a.steps * G,
+        "verified_vs_oracle": verified, "setup_s": setup_s,
+        "cache": {"local_rows": st["num_local_rows"], "remote_keys": st["num_remote_keys"],
+                  "host_keys": st["num_host_keys"], "table_bytes": st["table_bytes"]},
+        "errors": {"key_range": st_last["err_key_range"], "table": st_last["err_table"]},
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+        if a.sweep_out:
+            with open(a.sweep_out, "w") as f:
+                json.dump(line, f)
+    cache.close()
+    table.release()
+    barrier()
+    table.unlink()
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

@@ -227,6 +227,15 @@ int ugc_refresh_commit(ugc_ctx* ctx);
 /* -- introspection --------------------------------------------------------------------- */
 int ugc_stats(ugc_ctx* ctx, int replica_id, ugc_stats_t* out);
 
+/* Changes the launch shape of the gather for later lookups of one replica: CTAs per SM,
+ * CTA budgets of the host and peer groups, bytes per lane per load (16 or 32), threads per
+ * CTA (256 / 512 / 1024); a value of 0 keeps the current setting.  bulk_mask selects which
+ * far sources are staged through shared memory by the bulk-async copy engine (bit 0: host
+ * rows, bit 1: peer rows; -1 keeps the current setting).  The reference fixes these per platform in its link tables
+ * (coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289: SMs for the host and peer streams). */
+int ugc_tune(ugc_ctx* ctx, int replica_id, int gather_ctas_per_sm, int host_ctas, int remote_ctas,
+             int gather_vec_bytes, int block_threads, int bulk_mask);
+
 /* Per-kernel device timing of the lookups issued between begin and end: CUDA events are
  * recorded on the lookup's stream around the lookup_group kernel and around the gather
  * kernel.  Replaces the host-timer phase breakdown the reference logs per step
@@ -242,6 +251,24 @@ int ugc_profile_end(ugc_ctx* ctx, int replica_id, double* lookup_group_ms, doubl
  * (coll_cache_lib/cuda/cache_hashtable.h:20-28). */
 int ugc_table_words(ugc_ctx* ctx, int replica_id, const uint32_t* keys, size_t n,
                     uint32_t* words, void* stream);
+
+/* Pins caller-owned host memory and maps it for every GPU; *dev_ptr receives the address
+ * kernels use for it.  The library does this itself inside ugc_build when register_host is
+ * set (as the reference does, coll_cache_lib/facade.cc:476); the explicit form lets a
+ * harness fill the table from the GPU before the build. */
+int ugc_host_register(void* host_ptr, size_t nbytes, void** dev_ptr);
+int ugc_host_unregister(void* host_ptr);
+/* Pinned, GPU-mapped host memory for callers that let the library own the host table's
+ * storage, as the reference's binding does for its embedding table
+ * (python/collcache/torch/adapter.cc:239-270, coll_cache_lib/cpu/cpu_device.cc:36-112).
+ * The memory is taken through the CUDA virtual-memory API at the GPU's host NUMA node when
+ * the driver offers that (2 MiB chunks, mapped by the GPU with large pages, which keeps
+ * random row reads over tens of GB from missing in address translation); cudaHostAlloc
+ * otherwise.  *host_ptr is valid on the CPU, *dev_ptr in kernels. */
+int ugc_host_alloc(size_t nbytes, void** host_ptr, void** dev_ptr);
+int ugc_host_free(void* host_ptr);
+/* 1 if host_ptr came from ugc_host_alloc through the virtual-memory route, else 0. */
+int ugc_host_is_large_page(const void* host_ptr);
 
 /* Synthetic-input helper for benchmarks: writes rows [row_begin, row_begin+n_rows) of the
  * seeded uniform[-1,1) table into dst (device memory, or GPU-visible pinned host memory).

@@ -112,9 +112,15 @@ SIGNATURES = {
     "ugc_refresh_attach": (_I, [_P, _I, _P]),
     "ugc_refresh_commit": (_I, [_P]),
     "ugc_stats": (_I, [_P, _I, C.POINTER(Stats)]),
+    "ugc_tune": (_I, [_P, _I, _I, _I, _I, _I, _I, _I]),
     "ugc_profile_begin": (_I, [_P, _I, _I]),
     "ugc_profile_end": (_I, [_P, _I, C.POINTER(_D), C.POINTER(_D), C.POINTER(_U64)]),
     "ugc_table_words": (_I, [_P, _I, _P, _SZ, _P, _P]),
+    "ugc_host_register": (_I, [_P, _SZ, C.POINTER(_P)]),
+    "ugc_host_unregister": (_I, [_P]),
+    "ugc_host_alloc": (_I, [_SZ, C.POINTER(_P), C.POINTER(_P)]),
+    "ugc_host_free": (_I, [_P]),
+    "ugc_host_is_large_page": (_I, [_P]),
     "ugc_gen_table": (_I, [_P, _U64, _U64, _U64, _U64, _I, _P]),
 }
 

@@ -1,6 +1,7 @@
 // C ABI of the extraction path: context, build, peer exchange, lookup, refresh, stats.
 // Host runtime in C++; device work in kernels.cu.  Nothing here throws across the ABI or
 // aborts: every entry point returns a ugc_status and records a per-thread message.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <unistd.h>
 
@@ -9,6 +10,7 @@
 #include <cstdio>
 #include <cstring>
 #include <deque>
+#include <map>
 #include <mutex>
 #include <new>
 #include <string>
@@ -104,6 +106,9 @@ struct Replica {
   uint64_t lookups = 0;
   int gather_grid = 0;
   int host_ctas = 0, remote_ctas = 0;
+  int vec_bytes = 16;
+  int block_threads = 256;
+  int bulk_mask = 0;
   // per-kernel profiling (three events per lookup)
   std::vector<cudaEvent_t> prof_events;
   size_t prof_used = 0;
@@ -169,6 +174,16 @@ int map_host_table(ugc_ctx* c, const void* host_table) {
                                                : c->cfg.num_total_item;
   const size_t bytes = (size_t)rows * c->cfg.row_bytes;
   void* dptr = nullptr;
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, host_table) == cudaSuccess && attr.devicePointer &&
+      (attr.type == cudaMemoryTypeHost || attr.type == cudaMemoryTypeManaged ||
+       attr.type == cudaMemoryTypeDevice)) {
+    // already GPU-visible (pinned, registered, or mapped through the virtual-memory API)
+    c->host_table = host_table;
+    c->host_dev = attr.devicePointer;
+    return UGC_OK;
+  }
+  cudaGetLastError();
   cudaError_t e = cudaHostGetDevicePointer(&dptr, const_cast<void*>(host_table), 0);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -277,6 +292,7 @@ GatherParams gather_params(ugc_ctx* c, Replica* r, void* out, uint32_t n) {
   p.remote_cta_cap = r->remote_ctas;
   p.host_cta_cap = r->host_ctas;
   p.rows_per_cta_min = 32;
+  p.bulk_mask = r->bulk_mask;
   return p;
 }
 
@@ -298,7 +314,7 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
                                r->list[kGroupRemote], r->list[kGroupHost], r->counters, s));
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 1], s));
   GatherParams p = gather_params(c, r, out, (uint32_t)n);
-  UGC_CUDA(launch_gather_roles(p, r->gather_grid, c->cfg.gather_vec_bytes == 32 ? 32 : 16, s));
+  UGC_CUDA(launch_gather_roles(p, r->gather_grid, r->block_threads, r->vec_bytes, s));
   if (prof) {
     UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 2], s));
     r->prof_used += 3;
@@ -308,6 +324,140 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
 }
 
 }  // namespace
+
+// Host tables allocated through the virtual-memory API at a host NUMA location come in
+// 2 MiB physical chunks, which the GPU maps with large pages: random row reads over a table
+// of tens of GB then stop missing in the GPU's address translation (4 KiB mappings of
+// registered memory made those reads several times slower while HBM traffic was running).
+// The driver entry points are resolved at run time so that the library still loads on a
+// machine without a driver.
+namespace {
+struct VmmApi {
+  CUresult (*create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+  CUresult (*release)(CUmemGenericAllocationHandle) = nullptr;
+  CUresult (*reserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+  CUresult (*addr_free)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+  CUresult (*unmap)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*set_access)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+  CUresult (*granularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
+  bool ok = false;
+};
+struct VmmBlock {
+  CUmemGenericAllocationHandle handle;
+  size_t size;
+};
+std::mutex g_vmm_mu;
+std::map<void*, VmmBlock> g_vmm_blocks;
+
+template <typename F>
+bool resolve(const char* name, F* out) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult st;
+  if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &st) != cudaSuccess || !fn ||
+      st != cudaDriverEntryPointSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  *out = reinterpret_cast<F>(fn);
+  return true;
+}
+
+const VmmApi& vmm_api() {
+  static VmmApi api = [] {
+    VmmApi a;
+    a.ok = resolve("cuMemCreate", &a.create) && resolve("cuMemRelease", &a.release) &&
+           resolve("cuMemAddressReserve", &a.reserve) && resolve("cuMemAddressFree", &a.addr_free) &&
+           resolve("cuMemMap", &a.map) && resolve("cuMemUnmap", &a.unmap) &&
+           resolve("cuMemSetAccess", &a.set_access) &&
+           resolve("cuMemGetAllocationGranularity", &a.granularity);
+    return a;
+  }();
+  return api;
+}
+
+// Returns nullptr if this route is not available; the caller falls back to cudaHostAlloc.
+void* vmm_host_alloc(size_t nbytes, size_t* mapped) {
+  const VmmApi& a = vmm_api();
+  if (!a.ok) return nullptr;
+  int dev = 0, supported = 0, n_dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceCount(&n_dev) != cudaSuccess) return nullptr;
+  if (cudaDeviceGetAttribute(&supported, static_cast<cudaDeviceAttr>(141) /* host-NUMA virtual memory management supported */, dev) != cudaSuccess ||
+      !supported) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  int numa = 0;
+  if (cudaDeviceGetAttribute(&numa, cudaDevAttrHostNumaId, dev) != cudaSuccess || numa < 0) {
+    cudaGetLastError();
+    numa = 0;
+  }
+  CUmemAllocationProp prop;
+  memset(&prop, 0, sizeof(prop));
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_HOST_NUMA;
+  prop.location.id = numa;
+  size_t gran = 0;
+  if (a.granularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS || !gran) return nullptr;
+  const size_t size = (nbytes + gran - 1) / gran * gran;
+  CUmemGenericAllocationHandle h;
+  if (a.create(&h, size, &prop, 0) != CUDA_SUCCESS) return nullptr;
+  CUdeviceptr va = 0;
+  if (a.reserve(&va, size, gran, 0, 0) != CUDA_SUCCESS) {
+    a.release(h);
+    return nullptr;
+  }
+  if (a.map(va, size, 0, h, 0) != CUDA_SUCCESS) {
+    a.addr_free(va, size);
+    a.release(h);
+    return nullptr;
+  }
+  std::vector<CUmemAccessDesc> acc;
+  for (int d = 0; d < n_dev; d++) {  // every GPU of this process may read the table
+    CUmemAccessDesc x;
+    memset(&x, 0, sizeof(x));
+    x.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    x.location.id = d;
+    x.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    acc.push_back(x);
+  }
+  CUmemAccessDesc hostacc;
+  memset(&hostacc, 0, sizeof(hostacc));
+  hostacc.location.type = CU_MEM_LOCATION_TYPE_HOST_NUMA;
+  hostacc.location.id = numa;
+  hostacc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  acc.push_back(hostacc);
+  if (a.set_access(va, size, acc.data(), acc.size()) != CUDA_SUCCESS) {
+    a.unmap(va, size);
+    a.addr_free(va, size);
+    a.release(h);
+    return nullptr;
+  }
+  void* p = reinterpret_cast<void*>(va);
+  std::lock_guard<std::mutex> lock(g_vmm_mu);
+  g_vmm_blocks[p] = VmmBlock{h, size};
+  *mapped = size;
+  return p;
+}
+
+bool vmm_host_free(void* p) {
+  VmmBlock b;
+  {
+    std::lock_guard<std::mutex> lock(g_vmm_mu);
+    auto it = g_vmm_blocks.find(p);
+    if (it == g_vmm_blocks.end()) return false;
+    b = it->second;
+    g_vmm_blocks.erase(it);
+  }
+  const VmmApi& a = vmm_api();
+  CUdeviceptr va = reinterpret_cast<CUdeviceptr>(p);
+  a.unmap(va, b.size);
+  a.addr_free(va, b.size);
+  a.release(b.handle);
+  return true;
+}
+}  // namespace
+
 
 // --------------------------------------------------------------------------------------
 extern "C" {
@@ -469,8 +619,9 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
   r->sm_count = prop.multiProcessorCount;
   const int per_sm = c->cfg.gather_ctas_per_sm > 0 ? c->cfg.gather_ctas_per_sm : 4;
   r->gather_grid = r->sm_count * per_sm;
-  r->host_ctas = c->cfg.host_ctas > 0 ? c->cfg.host_ctas : std::max(2, r->sm_count / 8);
-  r->remote_ctas = c->cfg.remote_ctas > 0 ? c->cfg.remote_ctas : std::max(2, r->sm_count * per_sm / 4);
+  r->host_ctas = c->cfg.host_ctas > 0 ? c->cfg.host_ctas : std::max(2, r->sm_count);
+  r->remote_ctas = c->cfg.remote_ctas > 0 ? c->cfg.remote_ctas : std::max(2, r->sm_count * per_sm / 2);
+  r->vec_bytes = c->cfg.gather_vec_bytes == 32 ? 32 : 16;
 
   // 1. which source serves each key (ascending key lists per GPU source)
   classify_keys(c->cur, replica_id, N, r->keys_by_src, r->counts);
@@ -869,6 +1020,23 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   return UGC_OK;
 }
 
+int ugc_tune(ugc_ctx* c, int replica_id, int per_sm, int host_ctas, int remote_ctas, int vec,
+             int block_threads, int bulk_mask) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (per_sm < 0 || per_sm > 32 || host_ctas < 0 || remote_ctas < 0 || (vec != 0 && vec != 16 && vec != 32) ||
+      (block_threads != 0 && block_threads != 256 && block_threads != 512 && block_threads != 1024) ||
+      bulk_mask > 3)
+    return fail(UGC_ERR_INVALID, "bad tuning value");
+  if (block_threads) r->block_threads = block_threads;
+  if (bulk_mask >= 0) r->bulk_mask = bulk_mask;
+  if (per_sm) r->gather_grid = r->sm_count * per_sm;
+  if (host_ctas) r->host_ctas = host_ctas;
+  if (remote_ctas) r->remote_ctas = remote_ctas;
+  if (vec) r->vec_bytes = vec;
+  return UGC_OK;
+}
+
 int ugc_profile_begin(ugc_ctx* c, int replica_id, int max_lookups) {
   Replica* r;
   UGC_TRY(get_replica(c, replica_id, true, &r));
@@ -913,6 +1081,54 @@ int ugc_table_words(ugc_ctx* c, int replica_id, const uint32_t* keys, size_t n, 
   UGC_TRY(get_replica(c, replica_id, true, &r));
   UGC_CUDA(cudaSetDevice(r->device));
   UGC_CUDA(launch_table_words(r->table, keys, (uint32_t)n, words, static_cast<cudaStream_t>(stream)));
+  return UGC_OK;
+}
+
+int ugc_host_register(void* host_ptr, size_t nbytes, void** dev_ptr) {
+  if (!host_ptr || !nbytes || !dev_ptr) return fail(UGC_ERR_INVALID, "null argument");
+  cudaError_t e = cudaHostRegister(host_ptr, nbytes, cudaHostRegisterPortable | cudaHostRegisterMapped);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(UGC_ERR_CUDA, "cudaHostRegister of %zu bytes failed: %s", nbytes, cudaGetErrorString(e));
+  }
+  UGC_CUDA(cudaHostGetDevicePointer(dev_ptr, host_ptr, 0));
+  return UGC_OK;
+}
+
+int ugc_host_alloc(size_t nbytes, void** host_ptr, void** dev_ptr) {
+  if (!nbytes || !host_ptr || !dev_ptr) return fail(UGC_ERR_INVALID, "null argument");
+  UGC_CUDA(cudaFree(0));  // make sure the primary context exists
+  size_t mapped = 0;
+  void* p = vmm_host_alloc(nbytes, &mapped);
+  if (p) {
+    *host_ptr = p;
+    *dev_ptr = p;  // one address for CPU and GPU
+    return UGC_OK;
+  }
+  cudaError_t e = cudaHostAlloc(host_ptr, nbytes, cudaHostAllocPortable | cudaHostAllocMapped);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(UGC_ERR_NOMEM, "cudaHostAlloc of %zu bytes failed: %s", nbytes, cudaGetErrorString(e));
+  }
+  UGC_CUDA(cudaHostGetDevicePointer(dev_ptr, *host_ptr, 0));
+  return UGC_OK;
+}
+
+int ugc_host_is_large_page(const void* host_ptr) {
+  std::lock_guard<std::mutex> lock(g_vmm_mu);
+  return g_vmm_blocks.count(const_cast<void*>(host_ptr)) ? 1 : 0;
+}
+
+int ugc_host_free(void* host_ptr) {
+  if (!host_ptr) return UGC_OK;
+  if (vmm_host_free(host_ptr)) return UGC_OK;
+  UGC_CUDA(cudaFreeHost(host_ptr));
+  return UGC_OK;
+}
+
+int ugc_host_unregister(void* host_ptr) {
+  if (!host_ptr) return fail(UGC_ERR_INVALID, "null argument");
+  UGC_CUDA(cudaHostUnregister(host_ptr));
   return UGC_OK;
 }
 

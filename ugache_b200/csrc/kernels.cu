@@ -369,8 +369,105 @@ __device__ __forceinline__ void split_roles(const GatherParams& p, const uint32_
   }
 }
 
+// ---- bulk-async (TMA engine) staging of rows whose source is far away -------------------
+// One elected lane per warp moves whole rows: cp.async.bulk global -> shared with an mbarrier
+// counting the bytes, then cp.async.bulk shared -> global.  The copy engine keeps many rows
+// in flight without holding registers or load-queue slots of the SM.  No cluster, no
+// multicast; source may be pinned host memory or a peer GPU's memory.
+constexpr int kBulkSlots = 8;          // rows in flight per warp
+constexpr uint32_t kBulkSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          dst_smem),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+               "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+
+// Rows [worker, worker + n_workers, ...) of the list, one warp per worker, lane 0 drives.
+// Returns false if a wait ran out (the caller records it; the kernel still terminates).
+__device__ __forceinline__ bool copy_rows_bulk(const RecordIndex& ix, uint32_t count,
+                                               uint32_t worker, uint32_t n_workers,
+                                               unsigned char* stage, uint64_t* bars) {
+  const uint32_t lane = threadIdx.x & 31;
+  bool ok_all = true;
+  if (lane == 0) {
+    uint32_t parity = 0;
+    for (int u = 0; u < kBulkSlots; u++) mbar_init(smem_u32(&bars[u]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (uint32_t base = worker; base < count; base += n_workers * kBulkSlots) {
+      char* dst[kBulkSlots];
+      bool ok[kBulkSlots];
+#pragma unroll
+      for (int u = 0; u < kBulkSlots; u++) {
+        uint32_t i = base + u * n_workers;
+        ok[u] = i < count;
+        dst[u] = nullptr;
+        if (ok[u]) {
+          const char* src;
+          ix.get(i, src, dst[u]);
+          uint32_t bar = smem_u32(&bars[u]);
+          mbar_expect_tx(bar, ix.row_bytes);
+          bulk_g2s(smem_u32(stage + (size_t)u * ix.row_bytes), src, ix.row_bytes, bar);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kBulkSlots; u++) {
+        if (!ok[u]) continue;
+        uint32_t bar = smem_u32(&bars[u]);
+        uint32_t spins = 0;
+        while (!mbar_try_wait(bar, parity)) {
+          if (++spins > kBulkSpinLimit) {
+            ok_all = false;
+            break;
+          }
+        }
+        if (!ok_all) break;
+        bulk_s2g(dst[u], smem_u32(stage + (size_t)u * ix.row_bytes), ix.row_bytes);
+      }
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      // the slots are reused by the next round: wait until the stores have read them
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      if (!ok_all) break;
+      parity ^= 1;
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+  __syncwarp();
+  return ok_all;
+}
+
 template <int VEC, int LPR, int UNROLL>
-__global__ void __launch_bounds__(kBlock) gather_roles_kernel(GatherParams p) {
+__global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
   const int grid = (int)gridDim.x;
   const int b = (int)blockIdx.x;
   uint32_t cnt[kNumGroup];
@@ -381,7 +478,7 @@ __global__ void __launch_bounds__(kBlock) gather_roles_kernel(GatherParams p) {
   split_roles(p, cnt, grid, n_host, n_remote);
 
   const uint32_t vecs_per_row = p.row_bytes / VEC;
-  constexpr uint32_t kWorkersPerCta = kBlock / LPR;
+  const uint32_t workers_per_cta = blockDim.x / LPR;
   const uint32_t worker_in_cta = threadIdx.x / LPR;
   const uint32_t sublane = threadIdx.x % LPR;
 
@@ -405,9 +502,21 @@ __global__ void __launch_bounds__(kBlock) gather_roles_kernel(GatherParams p) {
     ix.src_base = p.src_base;
     ix.out = static_cast<char*>(p.out);
     ix.row_bytes = p.row_bytes;
-    const uint32_t worker = (uint32_t)(b - first) * kWorkersPerCta + worker_in_cta;
-    const uint32_t n_workers = (uint32_t)num * kWorkersPerCta;
-    copy_rows<VEC, LPR, UNROLL, true>(ix, cnt[g], worker, n_workers, sublane, vecs_per_row);
+    const bool bulk = (g == kGroupHost && (p.bulk_mask & 1)) || (g == kGroupRemote && (p.bulk_mask & 2));
+    if (bulk) {
+      const uint32_t warps_per_cta = blockDim.x >> 5;
+      const uint32_t warp = threadIdx.x >> 5;
+      uint64_t* bars = reinterpret_cast<uint64_t*>(dyn_smem) + (size_t)warp * kBulkSlots;
+      unsigned char* stage = dyn_smem + (size_t)warps_per_cta * kBulkSlots * sizeof(uint64_t) +
+                             (size_t)warp * kBulkSlots * p.row_bytes;
+      bool ok = copy_rows_bulk(ix, cnt[g], (uint32_t)(b - first) * warps_per_cta + warp,
+                               (uint32_t)num * warps_per_cta, stage, bars);
+      if (!ok && (threadIdx.x & 31) == 0) atomicAdd(&p.counters->err_table, 1ull);
+    } else {
+      const uint32_t worker = (uint32_t)(b - first) * workers_per_cta + worker_in_cta;
+      const uint32_t n_workers = (uint32_t)num * workers_per_cta;
+      copy_rows<VEC, LPR, UNROLL, true>(ix, cnt[g], worker, n_workers, sublane, vecs_per_row);
+    }
   }
 
   // The last CTA to finish publishes the counts of this lookup and re-arms the counters.
@@ -417,9 +526,9 @@ __global__ void __launch_bounds__(kBlock) gather_roles_kernel(GatherParams p) {
     uint32_t done = atomicAdd(&p.counters->done_ctas, 1u);
     if (done == (uint32_t)grid - 1) {
 #pragma unroll
-      for (int g = 0; g < kNumGroup; g++) {
-        p.counters->last_count[g] = cnt[g];
-        p.counters->count[g] = 0;
+      for (int g2 = 0; g2 < kNumGroup; g2++) {
+        p.counters->last_count[g2] = cnt[g2];
+        p.counters->count[g2] = 0;
       }
       p.counters->last_keys = p.n_keys;
       p.counters->done_ctas = 0;
@@ -602,17 +711,27 @@ inline int lanes_per_row(uint32_t row_bytes, int vec) {
   return l;
 }
 
-template <int VEC, int UNROLL>
-cudaError_t gather_dispatch_lpr(const GatherParams& p, int grid, cudaStream_t s) {
-  switch (lanes_per_row(p.row_bytes, VEC)) {
-    case 1: gather_roles_kernel<VEC, 1, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
-    case 2: gather_roles_kernel<VEC, 2, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
-    case 4: gather_roles_kernel<VEC, 4, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
-    case 8: gather_roles_kernel<VEC, 8, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
-    case 16: gather_roles_kernel<VEC, 16, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
-    default: gather_roles_kernel<VEC, 32, UNROLL><<<grid, kBlock, 0, s>>>(p); break;
+template <int VEC, int LPR, int UNROLL>
+cudaError_t gather_launch(const GatherParams& p, int grid, int block, size_t smem, cudaStream_t s) {
+  auto kern = gather_roles_kernel<VEC, LPR, UNROLL>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
   }
+  kern<<<grid, block, smem, s>>>(p);
   return cudaGetLastError();
+}
+
+template <int VEC, int UNROLL>
+cudaError_t gather_dispatch_lpr(const GatherParams& p, int grid, int block, size_t smem, cudaStream_t s) {
+  switch (lanes_per_row(p.row_bytes, VEC)) {
+    case 1: return gather_launch<VEC, 1, UNROLL>(p, grid, block, smem, s);
+    case 2: return gather_launch<VEC, 2, UNROLL>(p, grid, block, smem, s);
+    case 4: return gather_launch<VEC, 4, UNROLL>(p, grid, block, smem, s);
+    case 8: return gather_launch<VEC, 8, UNROLL>(p, grid, block, smem, s);
+    case 16: return gather_launch<VEC, 16, UNROLL>(p, grid, block, smem, s);
+    default: return gather_launch<VEC, 32, UNROLL>(p, grid, block, smem, s);
+  }
 }
 
 template <int VEC, int UNROLL>
@@ -656,11 +775,24 @@ cudaError_t launch_lookup_group(const void* keys, int key_bytes, uint32_t n, con
   return cudaGetLastError();
 }
 
-cudaError_t launch_gather_roles(const GatherParams& p, int grid, int vec_bytes, cudaStream_t stream) {
+cudaError_t launch_gather_roles(const GatherParams& p_in, int grid, int block, int vec_bytes,
+                                cudaStream_t stream) {
+  GatherParams p = p_in;
   if (grid < 3) grid = 3;  // one CTA per source group at least
-  if (vec_bytes == 32 && p.row_bytes % 32 == 0) return gather_dispatch_lpr<32, 2>(p, grid, stream);
-  if (p.row_bytes % 16 == 0) return gather_dispatch_lpr<16, 4>(p, grid, stream);
-  return gather_dispatch_lpr<4, 4>(p, grid, stream);
+  if (block != 256 && block != 512 && block != 1024) block = 256;
+  // bulk staging needs 16-byte aligned rows on both sides
+  if (p.row_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(p.out) & 15)) p.bulk_mask = 0;
+  size_t smem = 0;
+  if (p.bulk_mask) {
+    smem = (size_t)(block / 32) * kBulkSlots * (sizeof(uint64_t) + p.row_bytes);
+    if (smem > 200 * 1024) {
+      p.bulk_mask = 0;
+      smem = 0;
+    }
+  }
+  if (vec_bytes == 32 && p.row_bytes % 32 == 0) return gather_dispatch_lpr<32, 2>(p, grid, block, smem, stream);
+  if (p.row_bytes % 16 == 0) return gather_dispatch_lpr<16, 4>(p, grid, block, smem, stream);
+  return gather_dispatch_lpr<4, 4>(p, grid, block, smem, stream);
 }
 
 cudaError_t launch_fill_scatter(const void* host_table, void* slice, const uint32_t* keys,

@@ -23,7 +23,8 @@ cudaError_t launch_lookup_group(const void* keys, int key_bytes, uint32_t n, con
                                 uint64_t* list_local, uint64_t* list_remote, uint64_t* list_host,
                                 Counters* counters, cudaStream_t stream);
 
-cudaError_t launch_gather_roles(const GatherParams& p, int grid, int vec_bytes, cudaStream_t stream);
+cudaError_t launch_gather_roles(const GatherParams& p, int grid, int block, int vec_bytes,
+                                cudaStream_t stream);
 
 // slice[slot(j)] = host[key(j) & mask]; slots == nullptr means slot(j) = slot_base + j.
 cudaError_t launch_fill_scatter(const void* host_table, void* slice, const uint32_t* keys,

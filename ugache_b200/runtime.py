@@ -218,6 +218,11 @@ class Cache:
         check(_lib.lib().ugc_stats(self._h, replica_id, C.byref(s)))
         return {name: getattr(s, name) for name, _ in s._fields_}
 
+    def tune(self, replica_id, gather_ctas_per_sm=0, host_ctas=0, remote_ctas=0, gather_vec_bytes=0,
+             block_threads=0, bulk_mask=-1):
+        check(_lib.lib().ugc_tune(self._h, replica_id, gather_ctas_per_sm, host_ctas, remote_ctas,
+                                  gather_vec_bytes, block_threads, bulk_mask))
+
     def profile_begin(self, replica_id, max_lookups):
         check(_lib.lib().ugc_profile_begin(self._h, replica_id, max_lookups))
 
@@ -240,3 +245,29 @@ class Cache:
 def gen_table(dst_ptr, seed, row_begin, n_rows, dim, elem_bytes, stream=0):
     check(_lib.lib().ugc_gen_table(C.c_void_p(dst_ptr), seed, row_begin, n_rows, dim, elem_bytes,
                                    C.c_void_p(stream)))
+
+
+def host_register(host_ptr, nbytes):
+    """Pins and maps caller-owned host memory; returns the device-side address."""
+    d = C.c_void_p()
+    check(_lib.lib().ugc_host_register(C.c_void_p(host_ptr), nbytes, C.byref(d)))
+    return d.value
+
+
+def host_unregister(host_ptr):
+    check(_lib.lib().ugc_host_unregister(C.c_void_p(host_ptr)))
+
+
+def host_alloc(nbytes):
+    """Pinned GPU-mapped host memory; returns (host address, device-side address)."""
+    h, d = C.c_void_p(), C.c_void_p()
+    check(_lib.lib().ugc_host_alloc(nbytes, C.byref(h), C.byref(d)))
+    return h.value, d.value
+
+
+def host_free(host_ptr):
+    check(_lib.lib().ugc_host_free(C.c_void_p(host_ptr)))
+
+
+def host_is_large_page(host_ptr):
+    return bool(_lib.lib().ugc_host_is_large_page(C.c_void_p(host_ptr)))
