@@ -56,6 +56,10 @@ def parse_args():
     ap.add_argument("--ctas-per-sm", type=int, default=0)
     ap.add_argument("--host-ctas", type=int, default=0)
     ap.add_argument("--remote-ctas", type=int, default=0)
+    ap.add_argument("--block-threads", type=int, default=0)
+    ap.add_argument("--bulk-mask", type=int, default=-1)
+    ap.add_argument("--lookup-kpt", type=int, default=0)
+    ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 30)")
     ap.add_argument("--cpu-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -88,10 +92,13 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
+            t_end = time.time() + 5.0      # nvidia-smi needs a moment before its first line
+            while not self.rows and time.time() < t_end:
+                time.sleep(0.02)
         except Exception:
             self.proc = None
 
@@ -191,7 +198,7 @@ class HostTable:
             if self.owned:
                 rt.host_free(self.ptr)
             elif self.dev_ptr is not None:
-                rt.host_unregister(self.ptr)
+                rt.host_unregister(self.ptr, self.nbytes)
         except Exception:
             pass
 
@@ -351,6 +358,17 @@ def run_ours(a):
                      remote_ctas=a.remote_ctas, gather_vec_bytes=a.vec, register_host=False)
     cache.set_placement(placement)
     cache.build(rank, local, table.ptr, stream)
+    tune = {}
+    if a.block_threads:
+        tune["gather_block_threads"] = a.block_threads
+    if a.bulk_mask >= 0:
+        tune["bulk_mask"] = a.bulk_mask
+    if a.lookup_kpt:
+        tune["lookup_keys_per_thread"] = a.lookup_kpt
+    if a.no_pdl:
+        tune["programmatic_launch"] = 0
+    if tune:
+        cache.tune(rank, **tune)
     if world > 1:
         import torch.distributed as dist
         h = cache.export(rank)
@@ -530,7 +548,7 @@ def run_ours(a):
                      "lookup_group_avg_us": lookup_ms_avg * 1e3},
         "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
         "gpu_launches": 2 * a.steps * G,
-        "verified_vs_oracle": verified, "setup_s": setup_s,
+        "verified_vs_oracle": verified, "setup_s": setup_s, "tuning": cache.get_tuning(rank),
         "cache": {"local_rows": st["num_local_rows"], "remote_keys": st["num_remote_keys"],
                   "host_keys": st["num_host_keys"], "table_bytes": st["table_bytes"]},
         "errors": {"key_range": st_last["err_key_range"], "table": st_last["err_table"]},

@@ -227,14 +227,27 @@ int ugc_refresh_commit(ugc_ctx* ctx);
 /* -- introspection --------------------------------------------------------------------- */
 int ugc_stats(ugc_ctx* ctx, int replica_id, ugc_stats_t* out);
 
-/* Changes the launch shape of the gather for later lookups of one replica: CTAs per SM,
- * CTA budgets of the host and peer groups, bytes per lane per load (16 or 32), threads per
- * CTA (256 / 512 / 1024); a value of 0 keeps the current setting.  bulk_mask selects which
- * far sources are staged through shared memory by the bulk-async copy engine (bit 0: host
- * rows, bit 1: peer rows; -1 keeps the current setting).  The reference fixes these per platform in its link tables
- * (coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289: SMs for the host and peer streams). */
-int ugc_tune(ugc_ctx* ctx, int replica_id, int gather_ctas_per_sm, int host_ctas, int remote_ctas,
-             int gather_vec_bytes, int block_threads, int bulk_mask);
+/* Launch shape of one replica's lookups.  The reference fixes the corresponding numbers per
+ * platform in its link tables (SMs for the host and peer streams,
+ * coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289) and in constant.h:74-75 (block and
+ * tile size).  ugc_get_tuning fills the struct with the current values; ugc_set_tuning
+ * applies it (struct_size must be set). */
+typedef struct {
+  uint32_t struct_size;
+  int32_t gather_ctas_per_sm;     /* CTAs of the gather kernel per SM                       */
+  int32_t gather_block_threads;   /* 256, 512 or 1024                                       */
+  int32_t gather_vec_bytes;       /* 16 or 32 bytes per lane per load                       */
+  int32_t host_ctas;              /* CTA budget of the host-row group                       */
+  int32_t remote_ctas;            /* CTA budget of the peer-row group                       */
+  int32_t bulk_mask;              /* far sources staged through shared memory by the
+                                     bulk-async copy engine: bit 0 host rows, bit 1 peer rows */
+  int32_t lookup_keys_per_thread; /* 1, 2 or 4                                              */
+  int32_t programmatic_launch;    /* 1: lookup and gather kernels are launched with
+                                     programmatic stream serialization, so each one's
+                                     prologue overlaps the tail of its predecessor          */
+} ugc_tuning;
+int ugc_get_tuning(ugc_ctx* ctx, int replica_id, ugc_tuning* out);
+int ugc_set_tuning(ugc_ctx* ctx, int replica_id, const ugc_tuning* in);
 
 /* Per-kernel device timing of the lookups issued between begin and end: CUDA events are
  * recorded on the lookup's stream around the lookup_group kernel and around the gather
@@ -257,7 +270,8 @@ int ugc_table_words(ugc_ctx* ctx, int replica_id, const uint32_t* keys, size_t n
  * set (as the reference does, coll_cache_lib/facade.cc:476); the explicit form lets a
  * harness fill the table from the GPU before the build. */
 int ugc_host_register(void* host_ptr, size_t nbytes, void** dev_ptr);
-int ugc_host_unregister(void* host_ptr);
+int ugc_host_unregister(void* host_ptr);                       /* regions up to 1 GiB */
+int ugc_host_unregister_sized(void* host_ptr, size_t nbytes);  /* any size */
 /* Pinned, GPU-mapped host memory for callers that let the library own the host table's
  * storage, as the reference's binding does for its embedding table
  * (python/collcache/torch/adapter.cc:239-270, coll_cache_lib/cpu/cpu_device.cc:36-112).

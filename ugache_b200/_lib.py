@@ -76,6 +76,20 @@ class Stats(C.Structure):
     ]
 
 
+class Tuning(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("gather_ctas_per_sm", C.c_int32),
+        ("gather_block_threads", C.c_int32),
+        ("gather_vec_bytes", C.c_int32),
+        ("host_ctas", C.c_int32),
+        ("remote_ctas", C.c_int32),
+        ("bulk_mask", C.c_int32),
+        ("lookup_keys_per_thread", C.c_int32),
+        ("programmatic_launch", C.c_int32),
+    ]
+
+
 class UgcError(RuntimeError):
     def __init__(self, status, message):
         super().__init__("ugache_b200 status %d: %s" % (status, message))
@@ -112,12 +126,14 @@ SIGNATURES = {
     "ugc_refresh_attach": (_I, [_P, _I, _P]),
     "ugc_refresh_commit": (_I, [_P]),
     "ugc_stats": (_I, [_P, _I, C.POINTER(Stats)]),
-    "ugc_tune": (_I, [_P, _I, _I, _I, _I, _I, _I, _I]),
+    "ugc_get_tuning": (_I, [_P, _I, C.POINTER(Tuning)]),
+    "ugc_set_tuning": (_I, [_P, _I, C.POINTER(Tuning)]),
     "ugc_profile_begin": (_I, [_P, _I, _I]),
     "ugc_profile_end": (_I, [_P, _I, C.POINTER(_D), C.POINTER(_D), C.POINTER(_U64)]),
     "ugc_table_words": (_I, [_P, _I, _P, _SZ, _P, _P]),
     "ugc_host_register": (_I, [_P, _SZ, C.POINTER(_P)]),
     "ugc_host_unregister": (_I, [_P]),
+    "ugc_host_unregister_sized": (_I, [_P, _SZ]),
     "ugc_host_alloc": (_I, [_SZ, C.POINTER(_P), C.POINTER(_P)]),
     "ugc_host_free": (_I, [_P]),
     "ugc_host_is_large_page": (_I, [_P]),

@@ -109,6 +109,8 @@ struct Replica {
   int vec_bytes = 16;
   int block_threads = 256;
   int bulk_mask = 0;
+  int lookup_kpt = 1;
+  int pdl = 1;
   // per-kernel profiling (three events per lookup)
   std::vector<cudaEvent_t> prof_events;
   size_t prof_used = 0;
@@ -124,6 +126,7 @@ struct ugc_ctx {
   const void* host_table = nullptr;
   const void* host_dev = nullptr;
   bool host_registered_here = false;
+  size_t host_registered_bytes = 0;
   std::mutex mu;
 };
 
@@ -191,21 +194,10 @@ int map_host_table(ugc_ctx* c, const void* host_table) {
       return fail(UGC_ERR_INVALID,
                   "host table is not GPU-visible (pin it, or set register_host): %s",
                   cudaGetErrorString(e));
-    // The reference registers the table read-only (coll_cache_lib/facade.cc:476); not every
-    // platform takes that flag, so fall back to a plain mapped registration.
-    e = cudaHostRegister(const_cast<void*>(host_table), bytes,
-                         cudaHostRegisterPortable | cudaHostRegisterMapped |
-                             cudaHostRegisterReadOnly);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      e = cudaHostRegister(const_cast<void*>(host_table), bytes,
-                           cudaHostRegisterPortable | cudaHostRegisterMapped);
-    }
-    if (e != cudaSuccess)
-      return fail(UGC_ERR_CUDA, "cudaHostRegister of %zu bytes failed: %s", bytes,
-                  cudaGetErrorString(e));
+    // The reference registers the table here as well (coll_cache_lib/facade.cc:476).
+    UGC_TRY(ugc_host_register(const_cast<void*>(host_table), bytes, &dptr));
     c->host_registered_here = true;
-    UGC_CUDA(cudaHostGetDevicePointer(&dptr, const_cast<void*>(host_table), 0));
+    c->host_registered_bytes = bytes;
   }
   c->host_table = host_table;
   c->host_dev = dptr;
@@ -293,6 +285,7 @@ GatherParams gather_params(ugc_ctx* c, Replica* r, void* out, uint32_t n) {
   p.host_cta_cap = r->host_ctas;
   p.rows_per_cta_min = 32;
   p.bulk_mask = r->bulk_mask;
+  p.pdl = r->pdl;
   return p;
 }
 
@@ -311,7 +304,7 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used], s));
   UGC_CUDA(launch_lookup_group(keys, key_bytes, (uint32_t)n, r->table, (uint32_t)r->id,
                                (uint32_t)c->cfg.num_device, c->cfg.empty_feat, r->list[kGroupLocal],
-                               r->list[kGroupRemote], r->list[kGroupHost], r->counters, s));
+                               r->list[kGroupRemote], r->list[kGroupHost], r->counters, r->lookup_kpt, r->pdl != 0, s));
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 1], s));
   GatherParams p = gather_params(c, r, out, (uint32_t)n);
   UGC_CUDA(launch_gather_roles(p, r->gather_grid, r->block_threads, r->vec_bytes, s));
@@ -523,7 +516,8 @@ int ugc_destroy(ugc_ctx* c) {
   if (!c) return UGC_OK;
   for (auto& r : c->reps)
     if (r.built) release_replica(c, &r);
-  if (c->host_registered_here && c->host_table) cudaHostUnregister(const_cast<void*>(c->host_table));
+  if (c->host_registered_here && c->host_table)
+    ugc_host_unregister_sized(const_cast<void*>(c->host_table), c->host_registered_bytes);
   delete c;
   return UGC_OK;
 }
@@ -1020,20 +1014,40 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   return UGC_OK;
 }
 
-int ugc_tune(ugc_ctx* c, int replica_id, int per_sm, int host_ctas, int remote_ctas, int vec,
-             int block_threads, int bulk_mask) {
+int ugc_get_tuning(ugc_ctx* c, int replica_id, ugc_tuning* out) {
   Replica* r;
   UGC_TRY(get_replica(c, replica_id, true, &r));
-  if (per_sm < 0 || per_sm > 32 || host_ctas < 0 || remote_ctas < 0 || (vec != 0 && vec != 16 && vec != 32) ||
-      (block_threads != 0 && block_threads != 256 && block_threads != 512 && block_threads != 1024) ||
-      bulk_mask > 3)
-    return fail(UGC_ERR_INVALID, "bad tuning value");
-  if (block_threads) r->block_threads = block_threads;
-  if (bulk_mask >= 0) r->bulk_mask = bulk_mask;
-  if (per_sm) r->gather_grid = r->sm_count * per_sm;
-  if (host_ctas) r->host_ctas = host_ctas;
-  if (remote_ctas) r->remote_ctas = remote_ctas;
-  if (vec) r->vec_bytes = vec;
+  if (!out) return fail(UGC_ERR_INVALID, "null output");
+  memset(out, 0, sizeof(*out));
+  out->struct_size = sizeof(*out);
+  out->gather_ctas_per_sm = r->gather_grid / std::max(r->sm_count, 1);
+  out->gather_block_threads = r->block_threads;
+  out->gather_vec_bytes = r->vec_bytes;
+  out->host_ctas = r->host_ctas;
+  out->remote_ctas = r->remote_ctas;
+  out->bulk_mask = r->bulk_mask;
+  out->lookup_keys_per_thread = r->lookup_kpt;
+  out->programmatic_launch = r->pdl;
+  return UGC_OK;
+}
+
+int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (!t || t->struct_size != sizeof(ugc_tuning)) return fail(UGC_ERR_INVALID, "bad ugc_tuning");
+  const int bt = t->gather_block_threads, kpt = t->lookup_keys_per_thread, vec = t->gather_vec_bytes;
+  if (t->gather_ctas_per_sm < 1 || t->gather_ctas_per_sm > 32 || (bt != 256 && bt != 512 && bt != 1024) ||
+      (vec != 16 && vec != 32) || t->host_ctas < 1 || t->remote_ctas < 1 || t->bulk_mask < 0 ||
+      t->bulk_mask > 3 || (kpt != 1 && kpt != 2 && kpt != 4))
+    return fail(UGC_ERR_INVALID, "ugc_tuning holds a value outside its range");
+  r->gather_grid = r->sm_count * t->gather_ctas_per_sm;
+  r->block_threads = bt;
+  r->vec_bytes = vec;
+  r->host_ctas = t->host_ctas;
+  r->remote_ctas = t->remote_ctas;
+  r->bulk_mask = t->bulk_mask;
+  r->lookup_kpt = kpt;
+  r->pdl = t->programmatic_launch ? 1 : 0;
   return UGC_OK;
 }
 
@@ -1084,14 +1098,54 @@ int ugc_table_words(ugc_ctx* c, int replica_id, const uint32_t* keys, size_t n, 
   return UGC_OK;
 }
 
+// Registration goes chunk by chunk: one call over tens of GB of a shared-memory mapping was
+// refused by the OS on the test machines, 1 GiB pieces are accepted.
+static const size_t kRegisterChunk = (size_t)1 << 30;
+
+int ugc_host_unregister_sized(void* host_ptr, size_t nbytes) {
+  if (!host_ptr) return fail(UGC_ERR_INVALID, "null argument");
+  char* base = static_cast<char*>(host_ptr);
+  int rc = UGC_OK;
+  for (size_t off = 0; off < std::max<size_t>(nbytes, 1); off += kRegisterChunk) {
+    cudaError_t e = cudaHostUnregister(base + off);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      rc = fail(UGC_ERR_CUDA, "cudaHostUnregister failed: %s", cudaGetErrorString(e));
+    }
+  }
+  return rc;
+}
+
+int ugc_host_unregister(void* host_ptr) { return ugc_host_unregister_sized(host_ptr, 1); }
+
 int ugc_host_register(void* host_ptr, size_t nbytes, void** dev_ptr) {
   if (!host_ptr || !nbytes || !dev_ptr) return fail(UGC_ERR_INVALID, "null argument");
-  cudaError_t e = cudaHostRegister(host_ptr, nbytes, cudaHostRegisterPortable | cudaHostRegisterMapped);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    return fail(UGC_ERR_CUDA, "cudaHostRegister of %zu bytes failed: %s", nbytes, cudaGetErrorString(e));
+  char* base = static_cast<char*>(host_ptr);
+  size_t done = 0;
+  while (done < nbytes) {
+    size_t len = std::min(kRegisterChunk, nbytes - done);
+    cudaError_t e = cudaHostRegister(base + done, len, cudaHostRegisterPortable | cudaHostRegisterMapped);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      for (size_t off = 0; off < done; off += kRegisterChunk) cudaHostUnregister(base + off);
+      cudaGetLastError();
+      return fail(UGC_ERR_CUDA, "cudaHostRegister of %zu bytes at offset %zu failed: %s", len, done,
+                  cudaGetErrorString(e));
+    }
+    done += len;
   }
-  UGC_CUDA(cudaHostGetDevicePointer(dev_ptr, host_ptr, 0));
+  void* d0 = nullptr;
+  UGC_CUDA(cudaHostGetDevicePointer(&d0, host_ptr, 0));
+  // the chunks must form one contiguous device range (true with unified addressing)
+  for (size_t off = kRegisterChunk; off < nbytes; off += kRegisterChunk) {
+    void* d = nullptr;
+    UGC_CUDA(cudaHostGetDevicePointer(&d, base + off, 0));
+    if (d != static_cast<char*>(d0) + off) {
+      ugc_host_unregister_sized(host_ptr, nbytes);
+      return fail(UGC_ERR_UNSUPPORTED, "registered chunks are not contiguous on the device");
+    }
+  }
+  *dev_ptr = d0;
   return UGC_OK;
 }
 
@@ -1126,11 +1180,6 @@ int ugc_host_free(void* host_ptr) {
   return UGC_OK;
 }
 
-int ugc_host_unregister(void* host_ptr) {
-  if (!host_ptr) return fail(UGC_ERR_INVALID, "null argument");
-  UGC_CUDA(cudaHostUnregister(host_ptr));
-  return UGC_OK;
-}
 
 int ugc_gen_table(void* dst, uint64_t seed, uint64_t row_begin, uint64_t n_rows, uint64_t dim,
                   int elem_bytes, void* stream) {

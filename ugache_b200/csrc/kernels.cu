@@ -3,6 +3,8 @@
 // is not a multiple of 16).
 #include "kernels.cuh"
 
+#include <cstring>
+
 namespace ugc {
 
 namespace {
@@ -157,10 +159,7 @@ __device__ __forceinline__ uint32_t table_lookup(const TableView& t, uint32_t ke
 // ------------------------------------------------------------------------------------
 // lookup + group by source
 // ------------------------------------------------------------------------------------
-constexpr int kKeysPerThread = 4;
-constexpr int kLookupTile = kBlock * kKeysPerThread;
-
-template <typename KeyT>
+template <typename KeyT, int kKeysPerThread>
 __global__ void __launch_bounds__(kBlock)
     lookup_group_kernel(const KeyT* __restrict__ keys, uint32_t n, TableView t, uint32_t local_loc,
                         uint32_t host_loc, uint32_t host_mask, uint64_t* __restrict__ list_local,
@@ -171,7 +170,7 @@ __global__ void __launch_bounds__(kBlock)
 
   const uint32_t tid = threadIdx.x;
   const uint32_t warp = tid >> 5, lane = tid & 31;
-  const uint32_t tile_base = blockIdx.x * kLookupTile;
+  const uint32_t tile_base = blockIdx.x * (kBlock * kKeysPerThread);
 
   uint32_t key[kKeysPerThread];
   bool valid[kKeysPerThread];
@@ -188,7 +187,9 @@ __global__ void __launch_bounds__(kBlock)
     }
     key[j] = (uint32_t)k;
   }
-  if (bad) atomicAdd(&counters->err_key_range, (unsigned long long)bad);
+  // Let the gather that follows in the stream be scheduled as soon as SM resources allow
+  // (it waits for this grid's completion before it reads the lists).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // First probe of every key is issued before any is consumed.
   uint32_t word[kKeysPerThread];
@@ -219,6 +220,12 @@ __global__ void __launch_bounds__(kBlock)
       }
     }
   }
+
+  // Keys and table have been read; everything below touches the lists and counters that
+  // the previous lookup's gather may still be using: wait for it (no-op unless this kernel
+  // was launched with programmatic stream serialization).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (bad) atomicAdd(&counters->err_key_range, (unsigned long long)bad);
 
   // Group, count per warp with ballots.
   uint32_t group[kKeysPerThread], rank_in_warp[kKeysPerThread];
@@ -470,6 +477,10 @@ __global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
   extern __shared__ __align__(128) unsigned char dyn_smem[];
   const int grid = (int)gridDim.x;
   const int b = (int)blockIdx.x;
+  // The lookup kernel ahead of this one in the stream must have finished writing the lists.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The next lookup's key loads and table probes may start while this grid drains.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   uint32_t cnt[kNumGroup];
 #pragma unroll
   for (int g = 0; g < kNumGroup; g++) cnt[g] = p.counters->count[g];
@@ -711,6 +722,25 @@ inline int lanes_per_row(uint32_t row_bytes, int vec) {
   return l;
 }
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while its
+// predecessor in the stream is still running and orders itself with griddepcontrol.wait.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), int grid, int block, size_t smem, cudaStream_t s,
+                       bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 template <int VEC, int LPR, int UNROLL>
 cudaError_t gather_launch(const GatherParams& p, int grid, int block, size_t smem, cudaStream_t s) {
   auto kern = gather_roles_kernel<VEC, LPR, UNROLL>;
@@ -718,8 +748,7 @@ cudaError_t gather_launch(const GatherParams& p, int grid, int block, size_t sme
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  kern<<<grid, block, smem, s>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(kern, grid, block, smem, s, p.pdl != 0, p);
 }
 
 template <int VEC, int UNROLL>
@@ -759,20 +788,24 @@ inline uint32_t host_mask_of(int empty_feat) {
 cudaError_t launch_lookup_group(const void* keys, int key_bytes, uint32_t n, const TableView& table,
                                 uint32_t local_loc, uint32_t host_loc, int empty_feat,
                                 uint64_t* list_local, uint64_t* list_remote, uint64_t* list_host,
-                                Counters* counters, cudaStream_t stream) {
+                                Counters* counters, int keys_per_thread, bool pdl,
+                                cudaStream_t stream) {
   if (n == 0) return cudaSuccess;
-  const int grid = (int)((n + kLookupTile - 1) / kLookupTile);
   const uint32_t mask = host_mask_of(empty_feat);
+#define UGC_LAUNCH_LOOKUP(KEYT, KPT)                                                             \
+  return launch_pdl(lookup_group_kernel<KEYT, KPT>, (int)((n + kBlock * KPT - 1) / (kBlock * KPT)), \
+                    kBlock, 0, stream, pdl, static_cast<const KEYT*>(keys), n, table, local_loc,   \
+                    host_loc, mask, list_local, list_remote, list_host, counters)
   if (key_bytes == 8) {
-    lookup_group_kernel<long long><<<grid, kBlock, 0, stream>>>(
-        static_cast<const long long*>(keys), n, table, local_loc, host_loc, mask, list_local,
-        list_remote, list_host, counters);
+    if (keys_per_thread == 1) UGC_LAUNCH_LOOKUP(long long, 1);
+    if (keys_per_thread == 2) UGC_LAUNCH_LOOKUP(long long, 2);
+    UGC_LAUNCH_LOOKUP(long long, 4);
   } else {
-    lookup_group_kernel<uint32_t><<<grid, kBlock, 0, stream>>>(
-        static_cast<const uint32_t*>(keys), n, table, local_loc, host_loc, mask, list_local,
-        list_remote, list_host, counters);
+    if (keys_per_thread == 1) UGC_LAUNCH_LOOKUP(uint32_t, 1);
+    if (keys_per_thread == 2) UGC_LAUNCH_LOOKUP(uint32_t, 2);
+    UGC_LAUNCH_LOOKUP(uint32_t, 4);
   }
-  return cudaGetLastError();
+#undef UGC_LAUNCH_LOOKUP
 }
 
 cudaError_t launch_gather_roles(const GatherParams& p_in, int grid, int block, int vec_bytes,

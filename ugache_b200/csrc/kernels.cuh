@@ -21,7 +21,8 @@ namespace ugc {
 cudaError_t launch_lookup_group(const void* keys, int key_bytes, uint32_t n, const TableView& table,
                                 uint32_t local_loc, uint32_t host_loc, int empty_feat,
                                 uint64_t* list_local, uint64_t* list_remote, uint64_t* list_host,
-                                Counters* counters, cudaStream_t stream);
+                                Counters* counters, int keys_per_thread, bool pdl,
+                                cudaStream_t stream);
 
 cudaError_t launch_gather_roles(const GatherParams& p, int grid, int block, int vec_bytes,
                                 cudaStream_t stream);

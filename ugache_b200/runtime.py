@@ -218,10 +218,20 @@ class Cache:
         check(_lib.lib().ugc_stats(self._h, replica_id, C.byref(s)))
         return {name: getattr(s, name) for name, _ in s._fields_}
 
-    def tune(self, replica_id, gather_ctas_per_sm=0, host_ctas=0, remote_ctas=0, gather_vec_bytes=0,
-             block_threads=0, bulk_mask=-1):
-        check(_lib.lib().ugc_tune(self._h, replica_id, gather_ctas_per_sm, host_ctas, remote_ctas,
-                                  gather_vec_bytes, block_threads, bulk_mask))
+    def get_tuning(self, replica_id):
+        t = _lib.Tuning()
+        check(_lib.lib().ugc_get_tuning(self._h, replica_id, C.byref(t)))
+        return {name: getattr(t, name) for name, _ in t._fields_ if name != "struct_size"}
+
+    def tune(self, replica_id, **kw):
+        """Change launch-shape fields of ``ugc_tuning`` by name; others keep their value."""
+        t = _lib.Tuning()
+        check(_lib.lib().ugc_get_tuning(self._h, replica_id, C.byref(t)))
+        for k, v in kw.items():
+            if not hasattr(t, k):
+                raise KeyError(k)
+            setattr(t, k, v)
+        check(_lib.lib().ugc_set_tuning(self._h, replica_id, C.byref(t)))
 
     def profile_begin(self, replica_id, max_lookups):
         check(_lib.lib().ugc_profile_begin(self._h, replica_id, max_lookups))
@@ -254,8 +264,8 @@ def host_register(host_ptr, nbytes):
     return d.value
 
 
-def host_unregister(host_ptr):
-    check(_lib.lib().ugc_host_unregister(C.c_void_p(host_ptr)))
+def host_unregister(host_ptr, nbytes=1):
+    check(_lib.lib().ugc_host_unregister_sized(C.c_void_p(host_ptr), nbytes))
 
 
 def host_alloc(nbytes):

@@ -75,13 +75,15 @@ def zipf_keys(seed, n, N, alpha):
     return rank_to_id(zipf_ranks(u, N, alpha), N)
 
 
-def analytic_hotness(N, alpha, total=1 << 30):
-    """(rank_ids, rank_freqs): ids by descending expected frequency and integer counts
-    ~ total * p(rank), the input the placement solvers take."""
+def analytic_hotness(N, alpha, top=4.0e9):
+    """(rank_ids, rank_freqs): ids by descending expected frequency and 32-bit integer
+    counts proportional to rank^-alpha, the input the placement solvers take.  The hottest id
+    gets `top` counts (close to the 32-bit ceiling) so that the tail keeps non-zero counts as
+    far down as the integer format allows."""
     ranks = np.arange(N, dtype=np.uint64)
     ids = rank_to_id(ranks, N).astype(np.uint32)
     w = (np.arange(1, N + 1, dtype=np.float64)) ** (-alpha)
-    freqs = np.floor(w * (total / w.sum())).astype(np.uint32)
+    freqs = np.floor(w * top).astype(np.uint32)
     return ids, freqs
 
 
