@@ -198,6 +198,12 @@ int ugc_lookup_u32(ugc_ctx* ctx, int replica_id, const uint32_t* keys, size_t n,
 int ugc_lookup_i64(ugc_ctx* ctx, int replica_id, const int64_t* keys, size_t n, void* out,
                    void* stream);
 
+/* Grows the per-replica lookup scratch so that batches of up to max_batch keys are accepted
+ * (the reference re-allocates its output buffer when a larger batch shows up,
+ * python/collcache/torch/adapter.cc:213-224).  Must not run while a lookup of that replica
+ * is in flight. */
+int ugc_reserve_batch(ugc_ctx* ctx, int replica_id, uint32_t max_batch);
+
 /* Host-buffer form: keys and out are HOST pointers (pinned memory gives full speed).
  * Copies the keys to the GPU, runs the lookup, copies the rows back and returns after
  * they have landed.  key_bytes is 4 or 8. */

@@ -14,10 +14,10 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libugache_b200.so")
 STAMP = os.path.join(HERE, "build", "stamp.txt")
 
-CUDA_SOURCES = ["kernels.cu", "api.cu", "compat_api.cu"]
-HOST_SOURCES = ["placement.cc"]
+CUDA_SOURCES = ["kernels.cu", "api.cu"]
+HOST_SOURCES = ["placement.cc", "compat_api.cc"]
 HEADERS = ["device_types.h", "kernels.cuh", "placement.h", "../../include/ugache_b200.h",
-           "../../include/coll_cache_api.h"]
+           "../../include/coll_cache_api.h", "../../include/coll_cache_lib/facade.h"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fopenmp,-Wall", "-Xptxas", "-v"]

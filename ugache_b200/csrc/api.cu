@@ -833,6 +833,29 @@ int ugc_lookup_i64(ugc_ctx* c, int replica_id, const int64_t* keys, size_t n, vo
   return do_lookup(c, r, keys, 8, n, out, static_cast<cudaStream_t>(stream));
 }
 
+int ugc_reserve_batch(ugc_ctx* c, int replica_id, uint32_t max_batch) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (max_batch == 0 || max_batch > kMaxBatch) return fail(UGC_ERR_INVALID, "max_batch must be in [1, 2^28]");
+  if (max_batch <= r->max_batch) return UGC_OK;
+  UGC_CUDA(cudaSetDevice(r->device));
+  UGC_CUDA(cudaDeviceSynchronize());
+  uint64_t* fresh[kNumGroup] = {nullptr, nullptr, nullptr};
+  for (int g = 0; g < kNumGroup; g++) {
+    fresh[g] = static_cast<uint64_t*>(ctx_alloc(c, (size_t)max_batch * sizeof(uint64_t)));
+    if (!fresh[g]) {
+      for (int k = 0; k < g; k++) ctx_free(c, fresh[k]);
+      return fail(UGC_ERR_NOMEM, "scratch allocation for %u keys failed", max_batch);
+    }
+  }
+  for (int g = 0; g < kNumGroup; g++) {
+    ctx_free(c, r->list[g]);
+    r->list[g] = fresh[g];
+  }
+  r->max_batch = max_batch;
+  return UGC_OK;
+}
+
 int ugc_lookup_host(ugc_ctx* c, int replica_id, const void* keys, int key_bytes, size_t n, void* out,
                     void* stream) {
   Replica* r;

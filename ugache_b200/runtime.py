@@ -170,6 +170,9 @@ class Cache:
         self.lookup_ptr(replica_id, keys.data_ptr(), kb, n, out.data_ptr(), s)
         return out
 
+    def reserve_batch(self, replica_id, max_batch):
+        check(_lib.lib().ugc_reserve_batch(self._h, replica_id, max_batch))
+
     def lookup_host(self, replica_id, keys_np, out_np, stream=0):
         keys_np = np.ascontiguousarray(keys_np)
         kb = keys_np.dtype.itemsize
