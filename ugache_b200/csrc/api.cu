@@ -226,12 +226,19 @@ int upload_u32(ugc_ctx* c, DevBuf& buf, const uint32_t* src, size_t n, cudaStrea
   return UGC_OK;
 }
 
-int alloc_table(ugc_ctx* c, Replica* r, uint64_t entries, cudaStream_t s) {
+// `entries`: rows the placement maps to GPUs now (drives the reference's flat-vs-probing
+// rule); `reserve`: entries the table must be able to hold over its lifetime.
+int alloc_table(ugc_ctx* c, Replica* r, uint64_t entries, uint64_t reserve, cudaStream_t s) {
   const uint64_t N = c->cfg.num_total_item;
   int kind = c->cfg.table_kind;
   if (kind == UGC_TABLE_AUTO)
     kind = reference_prefers_flat_table(std::max<uint64_t>(entries, 2), N) ? UGC_TABLE_FLAT
                                                                            : UGC_TABLE_HASHED;
+  // a probing table as large as the direct-index one buys nothing
+  if (kind == UGC_TABLE_HASHED && c->cfg.table_kind == UGC_TABLE_AUTO &&
+      pow2_ceil(std::max<uint64_t>(reserve, 1)) * 16 > N * 4)
+    kind = UGC_TABLE_FLAT;
+  entries = reserve;
   r->table = TableView{};
   r->table.num_keys = N;
   if (kind == UGC_TABLE_FLAT) {
@@ -666,7 +673,12 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
     return bail(fail(UGC_ERR_CUDA, "fill launch failed: %s", cudaGetErrorString(cudaGetLastError())));
 
   // 5. table with the local entries (slot = position in the list)
-  if ((rc = alloc_table(c, r, n_local + n_remote, s)) != UGC_OK) return bail(rc);
+  // Size the table for every row the GPUs can hold together, so that a later refresh to a
+  // placement with more partitioned rows still fits (the reference sizes its table once, for
+  // the build-time entry count, coll_cache_lib/cache_context.cu:2489-2497).
+  const uint64_t max_entries = std::min<uint64_t>(N, (uint64_t)G * r->capacity);
+  if ((rc = alloc_table(c, r, n_local + n_remote, std::max(n_local + n_remote, max_entries), s)) != UGC_OK)
+    return bail(rc);
   if (launch_table_insert(r->table, static_cast<uint32_t*>(r->stage_a.ptr), nullptr, 0,
                           (uint32_t)replica_id, (uint32_t)n_local, r->counters, s) != cudaSuccess)
     return bail(fail(UGC_ERR_CUDA, "insert launch failed: %s", cudaGetErrorString(cudaGetLastError())));
