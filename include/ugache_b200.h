@@ -198,6 +198,26 @@ int ugc_lookup_u32(ugc_ctx* ctx, int replica_id, const uint32_t* keys, size_t n,
 int ugc_lookup_i64(ugc_ctx* ctx, int replica_id, const int64_t* keys, size_t n, void* out,
                    void* stream);
 
+/* ugc_lookup_i64 without any device memory of its own: the index lists and counters of the
+ * lookup live in a fixed array compiled into the library (about 6.3 MB on every GPU that loads
+ * it, held until the process exits) instead of the scratch that ugc_build / ugc_reserve_batch
+ * obtain from the allocator.  Meant for callers that cannot get device memory at the point
+ * where they look keys up: a caller-supplied allocator that is a fixed arena with nothing left
+ * once the cache slice is in it, a serving thread that must not take the device-wide
+ * synchronisation ugc_reserve_batch does when a batch outgrows max_batch, or a lookup issued
+ * while a stream is being captured (allocation calls are not allowed there).  The call
+ * itself performs no allocation of any kind.
+ *   - at most 262,144 keys per call (UGC_ERR_INVALID beyond that);
+ *   - the first call on a GPU asks the runtime for the array's device address; make that
+ *     first call before any stream capture starts;
+ *   - all replicas on one GPU, and all calls, share the one array: two such lookups that
+ *     overlap on the GPU (different streams, different replicas on the same device) race;
+ *     keep them ordered on one stream;
+ *   - out-of-range keys are skipped as usual but are not added to ugc_stats' counters.
+ * Same results as ugc_lookup_i64.  This entry point has no counterpart in the reference. */
+int ugc_lookup_i64_static(ugc_ctx* ctx, int replica_id, const int64_t* keys, size_t n, void* out,
+                          void* stream);
+
 /* Grows the per-replica lookup scratch so that batches of up to max_batch keys are accepted
  * (the reference re-allocates its output buffer when a larger batch shows up,
  * python/collcache/torch/adapter.cc:213-224).  Must not run while a lookup of that replica

@@ -119,6 +119,7 @@ SIGNATURES = {
     "ugc_attach_peers": (_I, [_P, _I, _P]),
     "ugc_lookup_u32": (_I, [_P, _I, _P, _SZ, _P, _P]),
     "ugc_lookup_i64": (_I, [_P, _I, _P, _SZ, _P, _P]),
+    "ugc_lookup_i64_static": (_I, [_P, _I, _P, _SZ, _P, _P]),
     "ugc_reserve_batch": (_I, [_P, _I, C.c_uint32]),
     "ugc_lookup_host": (_I, [_P, _I, _P, _I, _SZ, _P, _P]),
     "ugc_refresh_set_placement": (_I, [_P, _P, _P, _P, _P, _I]),

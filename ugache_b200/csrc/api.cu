@@ -459,6 +459,43 @@ bool vmm_host_free(void* p) {
 }  // namespace
 
 
+// ---- lookup scratch that needs no allocation ------------------------------------------------
+// ugc_lookup_i64_static keeps its index lists and counters in this fixed device array instead
+// of memory obtained at build time.  Every GPU that loads the library carries the array
+// (about 6.3 MB) until the process exits.  Layout: Counters (padded to 256 bytes), then the
+// three record lists of kStaticMaxKeys entries each.
+constexpr uint32_t kStaticMaxKeys = 1u << 18;  // 262,144 keys per call
+constexpr size_t kStaticHeader = 256;
+constexpr size_t kStaticBytes = kStaticHeader + (size_t)kNumGroup * kStaticMaxKeys * sizeof(uint64_t);
+static_assert(sizeof(Counters) <= kStaticHeader, "counters must fit the header");
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_addr[kStaticMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the CURRENT device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use, hence the symbol query;
+// it is made once per device and cached.
+int static_scratch_address(int device, void** out) {
+  if (device < 0 || device >= kStaticMaxDevices) return fail(UGC_ERR_UNSUPPORTED, "device ordinal %d too large", device);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_addr[device]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) {
+      cudaGetLastError();
+      return fail(UGC_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed on device %d: %s", device,
+                  cudaGetErrorString(e));
+    }
+    g_static_addr[device] = p;
+  }
+  *out = g_static_addr[device];
+  return UGC_OK;
+}
+}  // namespace
+
 // --------------------------------------------------------------------------------------
 extern "C" {
 
@@ -843,6 +880,45 @@ int ugc_lookup_i64(ugc_ctx* c, int replica_id, const int64_t* keys, size_t n, vo
   UGC_TRY(get_replica(c, replica_id, true, &r));
   UGC_CUDA(cudaSetDevice(r->device));
   return do_lookup(c, r, keys, 8, n, out, static_cast<cudaStream_t>(stream));
+}
+
+int ugc_lookup_i64_static(ugc_ctx* c, int replica_id, const int64_t* keys, size_t n, void* out,
+                          void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (n == 0) return UGC_OK;
+  if (!keys || !out) return fail(UGC_ERR_INVALID, "keys and out must be non-null");
+  if (n > kStaticMaxKeys)
+    return fail(UGC_ERR_INVALID, "ugc_lookup_i64_static takes at most %u keys per call, got %zu",
+                kStaticMaxKeys, n);
+  if (c->cfg.num_device > 1 && !r->attached)
+    return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  UGC_CUDA(cudaSetDevice(r->device));
+  void* base = nullptr;
+  UGC_TRY(static_scratch_address(r->device, &base));
+  Counters* counters = static_cast<Counters*>(base);
+  uint64_t* lists = reinterpret_cast<uint64_t*>(static_cast<unsigned char*>(base) + kStaticHeader);
+  // The array still holds whatever the previous call (of any replica on this GPU) left:
+  // the per-lookup counts must start from zero.
+  UGC_CUDA(cudaMemsetAsync(counters, 0, sizeof(Counters), s));
+  UGC_CUDA(launch_lookup_group(keys, 8, (uint32_t)n, r->table, (uint32_t)r->id, (uint32_t)c->cfg.num_device,
+                               c->cfg.empty_feat, lists, lists + kStaticMaxKeys, lists + 2 * (size_t)kStaticMaxKeys,
+                               counters, r->lookup_kpt, false, s));
+  GatherParams p{};
+  for (int i = 0; i < kMaxLocation; i++) p.src_base[i] = r->src_base[i];
+  p.out = out;
+  for (int g = 0; g < kNumGroup; g++) p.list[g] = lists + (size_t)g * kStaticMaxKeys;
+  p.counters = counters;
+  p.row_bytes = c->cfg.row_bytes;
+  p.n_keys = (uint32_t)n;
+  p.remote_cta_cap = r->remote_ctas;
+  p.host_cta_cap = r->host_ctas;
+  p.rows_per_cta_min = 32;
+  p.bulk_mask = 0;
+  p.pdl = 0;
+  UGC_CUDA(launch_gather_roles(p, r->gather_grid, r->block_threads, r->vec_bytes, s));
+  return UGC_OK;
 }
 
 int ugc_reserve_batch(ugc_ctx* c, int replica_id, uint32_t max_batch) {
