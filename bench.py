@@ -60,6 +60,7 @@ def parse_args():
     ap.add_argument("--bulk-mask", type=int, default=-1)
     ap.add_argument("--lookup-kpt", type=int, default=0)
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--pdl", type=int, default=-1)
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 30)")
     ap.add_argument("--cpu-steps", type=int, default=20)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -229,6 +230,18 @@ def all_max(x):
     return float(t.item())
 
 
+def all_list(x):
+    """The value of every rank, in rank order."""
+    if not _DIST["on"]:
+        return [x]
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    out = [torch.zeros_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t)
+    return [float(o.item()) for o in out]
+
+
 def all_sum(x):
     if not _DIST["on"]:
         return x
@@ -367,6 +380,8 @@ def run_ours(a):
         tune["lookup_keys_per_thread"] = a.lookup_kpt
     if a.no_pdl:
         tune["programmatic_launch"] = 0
+    if a.pdl >= 0:
+        tune["programmatic_launch"] = a.pdl
     if tune:
         cache.tune(rank, **tune)
     if world > 1:
@@ -432,7 +447,9 @@ def run_ours(a):
     torch.cuda.synchronize()
     t1 = time.time()
     barrier()
-    ms_total = all_max(e0.elapsed_time(e1))
+    ms_rank = e0.elapsed_time(e1)
+    ms_total = all_max(ms_rank)
+    ms_all = all_list(ms_rank)
     st_last = cache.stats(rank)
 
     # ---- same steps again with per-kernel events (for the roofline of the gather) ------
@@ -440,6 +457,7 @@ def run_ours(a):
     for i in range(a.warmup, total):
         step(i)
     lk_ms, ga_ms, nprof = cache.profile_end(rank)
+    ga_all = all_list(ga_ms / max(nprof, 1) * 1e3)
     t2 = time.time()
     sampler.stop()
     clocks = sampler.summary(t0, t2)
@@ -583,6 +601,7 @@ def run_ours(a):
                      "lookup_group_avg_us": lookup_ms_avg * 1e3},
         "cpu_baseline": cpu, "e2e": e2e, "e2e_device_consumer": e2e_dev, "clocks": clocks,
         "gpu_launches": 2 * a.steps * G,
+        "per_rank": {"step_us": [m / a.steps * 1e3 for m in ms_all], "gather_us": ga_all},
         "verified_vs_oracle": verified, "setup_s": setup_s, "tuning": cache.get_tuning(rank),
         "cache": {"local_rows": st["num_local_rows"], "remote_keys": st["num_remote_keys"],
                   "host_keys": st["num_host_keys"], "table_bytes": st["table_bytes"]},

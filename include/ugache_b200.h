@@ -268,9 +268,10 @@ typedef struct {
   int32_t bulk_mask;              /* far sources staged through shared memory by the
                                      bulk-async copy engine: bit 0 host rows, bit 1 peer rows */
   int32_t lookup_keys_per_thread; /* 1, 2 or 4                                              */
-  int32_t programmatic_launch;    /* 1: lookup and gather kernels are launched with
-                                     programmatic stream serialization, so each one's
-                                     prologue overlaps the tail of its predecessor          */
+  int32_t programmatic_launch;    /* programmatic stream serialization: bit 0 for the lookup
+                                     kernel (its key loads and probes overlap the tail of
+                                     the previous gather), bit 1 for the gather kernel (it is
+                                     scheduled while the lookup kernel drains)              */
 } ugc_tuning;
 int ugc_get_tuning(ugc_ctx* ctx, int replica_id, ugc_tuning* out);
 int ugc_set_tuning(ugc_ctx* ctx, int replica_id, const ugc_tuning* in);

@@ -110,7 +110,7 @@ struct Replica {
   int block_threads = 256;
   int bulk_mask = 0;
   int lookup_kpt = 1;
-  int pdl = 1;
+  int pdl = 1;  // bit 0: lookup kernel, bit 1: gather kernel launched with programmatic serialization
   // per-kernel profiling (three events per lookup)
   std::vector<cudaEvent_t> prof_events;
   size_t prof_used = 0;
@@ -292,7 +292,7 @@ GatherParams gather_params(ugc_ctx* c, Replica* r, void* out, uint32_t n) {
   p.host_cta_cap = r->host_ctas;
   p.rows_per_cta_min = 32;
   p.bulk_mask = r->bulk_mask;
-  p.pdl = r->pdl;
+  p.pdl = (r->pdl & 2) ? 1 : 0;
   return p;
 }
 
@@ -311,7 +311,7 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used], s));
   UGC_CUDA(launch_lookup_group(keys, key_bytes, (uint32_t)n, r->table, (uint32_t)r->id,
                                (uint32_t)c->cfg.num_device, c->cfg.empty_feat, r->list[kGroupLocal],
-                               r->list[kGroupRemote], r->list[kGroupHost], r->counters, r->lookup_kpt, r->pdl != 0, s));
+                               r->list[kGroupRemote], r->list[kGroupHost], r->counters, r->lookup_kpt, (r->pdl & 1) != 0, s));
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 1], s));
   GatherParams p = gather_params(c, r, out, (uint32_t)n);
   UGC_CUDA(launch_gather_roles(p, r->gather_grid, r->block_threads, r->vec_bytes, s));
@@ -1158,7 +1158,7 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   r->remote_ctas = t->remote_ctas;
   r->bulk_mask = t->bulk_mask;
   r->lookup_kpt = kpt;
-  r->pdl = t->programmatic_launch ? 1 : 0;
+  r->pdl = t->programmatic_launch & 3;
   return UGC_OK;
 }
 
