@@ -94,8 +94,12 @@ typedef struct {
   uint64_t table_ptr;
   uint64_t table_lines;      /* hashed: number of 32-byte lines; flat: N               */
   int32_t table_kind;
-  int32_t has_ipc;
-  unsigned char slice_ipc[64]; /* cudaIpcMemHandle_t                                   */
+  int32_t has_ipc;             /* 0: pointers only (same process); 1: cudaIpcMemHandle_t in
+                                  the two blobs; 2: {int64 file descriptor in the owner's
+                                  process, int64 mapped size} in the two blobs -- blocks from
+                                  the CUDA virtual-memory API, which the importer maps with
+                                  the owner's 2 MiB pages                               */
+  unsigned char slice_ipc[64];
   unsigned char table_ipc[64];
 } ugc_peer_handle;
 

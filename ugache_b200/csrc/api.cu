@@ -3,6 +3,8 @@
 // aborts: every entry point returns a ugc_status and records a per-thread message.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <sys/prctl.h>
+#include <sys/syscall.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -58,6 +60,297 @@ uint64_t pow2_ceil(uint64_t v) {
   while (p < v) p <<= 1;
   return p;
 }
+
+}  // namespace
+
+// Host tables allocated through the virtual-memory API at a host NUMA location come in
+// 2 MiB physical chunks, which the GPU maps with large pages: random row reads over a table
+// of tens of GB then stop missing in the GPU's address translation (4 KiB mappings of
+// registered memory made those reads several times slower while HBM traffic was running).
+// The driver entry points are resolved at run time so that the library still loads on a
+// machine without a driver.
+namespace {
+struct VmmApi {
+  CUresult (*create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+  CUresult (*release)(CUmemGenericAllocationHandle) = nullptr;
+  CUresult (*reserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+  CUresult (*addr_free)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+  CUresult (*unmap)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*set_access)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+  CUresult (*granularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
+  CUresult (*export_handle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long) = nullptr;
+  CUresult (*import_handle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType) = nullptr;
+  bool ok = false;
+};
+struct VmmBlock {
+  CUmemGenericAllocationHandle handle;
+  size_t size;
+};
+std::mutex g_vmm_mu;
+std::map<void*, VmmBlock> g_vmm_blocks;
+
+template <typename F>
+bool resolve(const char* name, F* out) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult st;
+  if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &st) != cudaSuccess || !fn ||
+      st != cudaDriverEntryPointSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  *out = reinterpret_cast<F>(fn);
+  return true;
+}
+
+const VmmApi& vmm_api() {
+  static VmmApi api = [] {
+    VmmApi a;
+    a.ok = resolve("cuMemCreate", &a.create) && resolve("cuMemRelease", &a.release) &&
+           resolve("cuMemAddressReserve", &a.reserve) && resolve("cuMemAddressFree", &a.addr_free) &&
+           resolve("cuMemMap", &a.map) && resolve("cuMemUnmap", &a.unmap) &&
+           resolve("cuMemSetAccess", &a.set_access) &&
+           resolve("cuMemGetAllocationGranularity", &a.granularity) &&
+           resolve("cuMemExportToShareableHandle", &a.export_handle) &&
+           resolve("cuMemImportFromShareableHandle", &a.import_handle);
+    return a;
+  }();
+  return api;
+}
+
+// Returns nullptr if this route is not available; the caller falls back to cudaHostAlloc.
+void* vmm_host_alloc(size_t nbytes, size_t* mapped) {
+  const VmmApi& a = vmm_api();
+  if (!a.ok) return nullptr;
+  int dev = 0, supported = 0, n_dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceCount(&n_dev) != cudaSuccess) return nullptr;
+  if (cudaDeviceGetAttribute(&supported, static_cast<cudaDeviceAttr>(141) /* host-NUMA virtual memory management supported */, dev) != cudaSuccess ||
+      !supported) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  int numa = 0;
+  if (cudaDeviceGetAttribute(&numa, cudaDevAttrHostNumaId, dev) != cudaSuccess || numa < 0) {
+    cudaGetLastError();
+    numa = 0;
+  }
+  CUmemAllocationProp prop;
+  memset(&prop, 0, sizeof(prop));
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_HOST_NUMA;
+  prop.location.id = numa;
+  size_t gran = 0;
+  if (a.granularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS || !gran) return nullptr;
+  const size_t size = (nbytes + gran - 1) / gran * gran;
+  CUmemGenericAllocationHandle h;
+  if (a.create(&h, size, &prop, 0) != CUDA_SUCCESS) return nullptr;
+  CUdeviceptr va = 0;
+  if (a.reserve(&va, size, gran, 0, 0) != CUDA_SUCCESS) {
+    a.release(h);
+    return nullptr;
+  }
+  if (a.map(va, size, 0, h, 0) != CUDA_SUCCESS) {
+    a.addr_free(va, size);
+    a.release(h);
+    return nullptr;
+  }
+  std::vector<CUmemAccessDesc> acc;
+  for (int d = 0; d < n_dev; d++) {  // every GPU of this process may read the table
+    CUmemAccessDesc x;
+    memset(&x, 0, sizeof(x));
+    x.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    x.location.id = d;
+    x.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    acc.push_back(x);
+  }
+  CUmemAccessDesc hostacc;
+  memset(&hostacc, 0, sizeof(hostacc));
+  hostacc.location.type = CU_MEM_LOCATION_TYPE_HOST_NUMA;
+  hostacc.location.id = numa;
+  hostacc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  acc.push_back(hostacc);
+  if (a.set_access(va, size, acc.data(), acc.size()) != CUDA_SUCCESS) {
+    a.unmap(va, size);
+    a.addr_free(va, size);
+    a.release(h);
+    return nullptr;
+  }
+  void* p = reinterpret_cast<void*>(va);
+  std::lock_guard<std::mutex> lock(g_vmm_mu);
+  g_vmm_blocks[p] = VmmBlock{h, size};
+  *mapped = size;
+  return p;
+}
+
+bool vmm_host_free(void* p) {
+  VmmBlock b;
+  {
+    std::lock_guard<std::mutex> lock(g_vmm_mu);
+    auto it = g_vmm_blocks.find(p);
+    if (it == g_vmm_blocks.end()) return false;
+    b = it->second;
+    g_vmm_blocks.erase(it);
+  }
+  const VmmApi& a = vmm_api();
+  CUdeviceptr va = reinterpret_cast<CUdeviceptr>(p);
+  a.unmap(va, b.size);
+  a.addr_free(va, b.size);
+  a.release(b.handle);
+  return true;
+}
+
+// ---- device memory that other processes can map with large pages ---------------------------
+// The cache slice and the table are what peers read.  Memory from cudaMalloc can be shared
+// with cudaIpc* handles, but the importing process then reads it through a mapping whose
+// random-access behaviour was several times slower on the test machines (2000 peer rows cost
+// +55 us against +2 us in one process).  Allocations made through the virtual-memory API are
+// exported as POSIX file descriptors and mapped by the importer with the same 2 MiB
+// granularity as the owner.
+struct DevBlock {
+  CUmemGenericAllocationHandle handle;
+  size_t size;
+  int device;
+  int fd;         // exported descriptor, -1 until first export
+  bool imported;  // mapping of another process' allocation
+};
+std::map<void*, DevBlock> g_dev_blocks;
+
+bool dev_granularity(int device, size_t* gran, CUmemAllocationProp* prop) {
+  memset(prop, 0, sizeof(*prop));
+  prop->type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop->location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop->location.id = device;
+  prop->requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  return vmm_api().granularity(gran, prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && *gran;
+}
+
+bool dev_set_access(void* p, size_t size, int device) {
+  CUmemAccessDesc acc;
+  memset(&acc, 0, sizeof(acc));
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = device;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  return vmm_api().set_access(reinterpret_cast<CUdeviceptr>(p), size, &acc, 1) == CUDA_SUCCESS;
+}
+
+// Maps `handle` (size bytes) for `device`; registers the block.  nullptr on failure.
+void* dev_map(CUmemGenericAllocationHandle handle, size_t size, size_t gran, int device, bool imported) {
+  const VmmApi& a = vmm_api();
+  CUdeviceptr va = 0;
+  if (a.reserve(&va, size, gran, 0, 0) != CUDA_SUCCESS) return nullptr;
+  if (a.map(va, size, 0, handle, 0) != CUDA_SUCCESS) {
+    a.addr_free(va, size);
+    return nullptr;
+  }
+  void* p = reinterpret_cast<void*>(va);
+  if (!dev_set_access(p, size, device)) {
+    a.unmap(va, size);
+    a.addr_free(va, size);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_vmm_mu);
+  g_dev_blocks[p] = DevBlock{handle, size, device, -1, imported};
+  return p;
+}
+
+// Shareable device memory on the current device; nullptr if this route is unavailable.
+void* dev_shareable_alloc(size_t nbytes) {
+  const VmmApi& a = vmm_api();
+  if (!a.ok) return nullptr;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
+  CUmemAllocationProp prop;
+  size_t gran = 0;
+  if (!dev_granularity(device, &gran, &prop)) return nullptr;
+  const size_t size = (nbytes + gran - 1) / gran * gran;
+  CUmemGenericAllocationHandle h;
+  if (a.create(&h, size, &prop, 0) != CUDA_SUCCESS) return nullptr;
+  void* p = dev_map(h, size, gran, device, false);
+  if (!p) a.release(h);
+  return p;
+}
+
+bool dev_block_free(void* p) {
+  DevBlock b;
+  {
+    std::lock_guard<std::mutex> lock(g_vmm_mu);
+    auto it = g_dev_blocks.find(p);
+    if (it == g_dev_blocks.end()) return false;
+    b = it->second;
+    g_dev_blocks.erase(it);
+  }
+  const VmmApi& a = vmm_api();
+  CUdeviceptr va = reinterpret_cast<CUdeviceptr>(p);
+  a.unmap(va, b.size);
+  a.addr_free(va, b.size);
+  a.release(b.handle);
+  if (b.fd >= 0) close(b.fd);
+  return true;
+}
+
+bool dev_block_find(void* p, DevBlock* out) {
+  std::lock_guard<std::mutex> lock(g_vmm_mu);
+  auto it = g_dev_blocks.find(p);
+  if (it == g_dev_blocks.end()) return false;
+  *out = it->second;
+  return true;
+}
+
+// File descriptor under which other processes can import the block (created once).
+int dev_block_export_fd(void* p) {
+  std::lock_guard<std::mutex> lock(g_vmm_mu);
+  auto it = g_dev_blocks.find(p);
+  if (it == g_dev_blocks.end()) return -1;
+  if (it->second.fd < 0) {
+    int fd = -1;
+    if (vmm_api().export_handle(&fd, it->second.handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) != CUDA_SUCCESS)
+      return -1;
+    it->second.fd = fd;
+  }
+  return it->second.fd;
+}
+
+// Duplicates descriptor `fd` of process `pid` into this process (pidfd_open + pidfd_getfd).
+int steal_fd(int64_t pid, int fd) {
+#if defined(SYS_pidfd_open) && defined(SYS_pidfd_getfd)
+  int pidfd = (int)syscall(SYS_pidfd_open, (pid_t)pid, 0);
+  if (pidfd < 0) return -1;
+  int local = (int)syscall(SYS_pidfd_getfd, pidfd, fd, 0);
+  close(pidfd);
+  return local;
+#else
+  (void)pid;
+  (void)fd;
+  return -1;
+#endif
+}
+
+// Maps another process' exported block for `device`.
+void* dev_import(int64_t pid, int fd, size_t size, int device) {
+  const VmmApi& a = vmm_api();
+  if (!a.ok) return nullptr;
+  int local = steal_fd(pid, fd);
+  if (local < 0) return nullptr;
+  CUmemGenericAllocationHandle h;
+  CUresult rc = a.import_handle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(local)),
+                                CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+  close(local);
+  if (rc != CUDA_SUCCESS) return nullptr;
+  CUmemAllocationProp prop;
+  size_t gran = 0;
+  if (!dev_granularity(device, &gran, &prop)) {
+    a.release(h);
+    return nullptr;
+  }
+  void* p = dev_map(h, size, gran, device, true);
+  if (!p) a.release(h);
+  return p;
+}
+}  // namespace
+
+
+
+namespace {
 
 // A device buffer that grows on demand through the context's allocator.
 struct DevBuf {
@@ -149,6 +442,21 @@ void ctx_free(ugc_ctx* c, void* p) {
   } else if (!c->cfg.alloc) {
     cudaFree(p);
   }
+}
+
+// Memory that peers will read (slice, table): shareable large-page blocks when the built-in
+// allocator is in use and the driver offers them, the ordinary route otherwise.
+void* ctx_alloc_shared(ugc_ctx* c, size_t bytes) {
+  if (!c->cfg.alloc && !getenv("UGC_NO_VMM")) {
+    void* p = dev_shareable_alloc(std::max<size_t>(bytes, 256));
+    if (p) return p;
+  }
+  return ctx_alloc(c, bytes);
+}
+void ctx_free_shared(ugc_ctx* c, void* p) {
+  if (!p) return;
+  if (dev_block_free(p)) return;
+  ctx_free(c, p);
 }
 
 int ensure(ugc_ctx* c, DevBuf& b, size_t bytes) {
@@ -254,7 +562,7 @@ int alloc_table(ugc_ctx* c, Replica* r, uint64_t entries, uint64_t reserve, cuda
     r->table_bytes = (size_t)lines * kSlotsPerLine * sizeof(uint2);
     r->table_entry_cap = lines * 2;
   }
-  r->table_mem = ctx_alloc(c, r->table_bytes);
+  r->table_mem = ctx_alloc_shared(c, r->table_bytes);
   if (!r->table_mem) return fail(UGC_ERR_NOMEM, "table allocation of %zu bytes failed", r->table_bytes);
   if (r->table.kind == kTableFlat) {
     r->table.flat = static_cast<uint32_t*>(r->table_mem);
@@ -268,9 +576,10 @@ int alloc_table(ugc_ctx* c, Replica* r, uint64_t entries, uint64_t reserve, cuda
 void release_replica(ugc_ctx* c, Replica* r) {
   if (r->device >= 0) cudaSetDevice(r->device);
   for (cudaEvent_t e : r->prof_events) cudaEventDestroy(e);
-  for (int i = 0; i < r->n_ipc_opened; i++) cudaIpcCloseMemHandle(r->ipc_opened[i]);
-  ctx_free(c, r->slice);
-  ctx_free(c, r->table_mem);
+  for (int i = 0; i < r->n_ipc_opened; i++)
+    if (!dev_block_free(r->ipc_opened[i])) cudaIpcCloseMemHandle(r->ipc_opened[i]);
+  ctx_free_shared(c, r->slice);
+  ctx_free_shared(c, r->table_mem);
   for (auto& l : r->list) ctx_free(c, l);
   ctx_free(c, r->counters);
   ctx_free(c, r->stage_keys.ptr);
@@ -324,140 +633,6 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
 }
 
 }  // namespace
-
-// Host tables allocated through the virtual-memory API at a host NUMA location come in
-// 2 MiB physical chunks, which the GPU maps with large pages: random row reads over a table
-// of tens of GB then stop missing in the GPU's address translation (4 KiB mappings of
-// registered memory made those reads several times slower while HBM traffic was running).
-// The driver entry points are resolved at run time so that the library still loads on a
-// machine without a driver.
-namespace {
-struct VmmApi {
-  CUresult (*create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
-  CUresult (*release)(CUmemGenericAllocationHandle) = nullptr;
-  CUresult (*reserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
-  CUresult (*addr_free)(CUdeviceptr, size_t) = nullptr;
-  CUresult (*map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
-  CUresult (*unmap)(CUdeviceptr, size_t) = nullptr;
-  CUresult (*set_access)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
-  CUresult (*granularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
-  bool ok = false;
-};
-struct VmmBlock {
-  CUmemGenericAllocationHandle handle;
-  size_t size;
-};
-std::mutex g_vmm_mu;
-std::map<void*, VmmBlock> g_vmm_blocks;
-
-template <typename F>
-bool resolve(const char* name, F* out) {
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult st;
-  if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &st) != cudaSuccess || !fn ||
-      st != cudaDriverEntryPointSuccess) {
-    cudaGetLastError();
-    return false;
-  }
-  *out = reinterpret_cast<F>(fn);
-  return true;
-}
-
-const VmmApi& vmm_api() {
-  static VmmApi api = [] {
-    VmmApi a;
-    a.ok = resolve("cuMemCreate", &a.create) && resolve("cuMemRelease", &a.release) &&
-           resolve("cuMemAddressReserve", &a.reserve) && resolve("cuMemAddressFree", &a.addr_free) &&
-           resolve("cuMemMap", &a.map) && resolve("cuMemUnmap", &a.unmap) &&
-           resolve("cuMemSetAccess", &a.set_access) &&
-           resolve("cuMemGetAllocationGranularity", &a.granularity);
-    return a;
-  }();
-  return api;
-}
-
-// Returns nullptr if this route is not available; the caller falls back to cudaHostAlloc.
-void* vmm_host_alloc(size_t nbytes, size_t* mapped) {
-  const VmmApi& a = vmm_api();
-  if (!a.ok) return nullptr;
-  int dev = 0, supported = 0, n_dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceCount(&n_dev) != cudaSuccess) return nullptr;
-  if (cudaDeviceGetAttribute(&supported, static_cast<cudaDeviceAttr>(141) /* host-NUMA virtual memory management supported */, dev) != cudaSuccess ||
-      !supported) {
-    cudaGetLastError();
-    return nullptr;
-  }
-  int numa = 0;
-  if (cudaDeviceGetAttribute(&numa, cudaDevAttrHostNumaId, dev) != cudaSuccess || numa < 0) {
-    cudaGetLastError();
-    numa = 0;
-  }
-  CUmemAllocationProp prop;
-  memset(&prop, 0, sizeof(prop));
-  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
-  prop.location.type = CU_MEM_LOCATION_TYPE_HOST_NUMA;
-  prop.location.id = numa;
-  size_t gran = 0;
-  if (a.granularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS || !gran) return nullptr;
-  const size_t size = (nbytes + gran - 1) / gran * gran;
-  CUmemGenericAllocationHandle h;
-  if (a.create(&h, size, &prop, 0) != CUDA_SUCCESS) return nullptr;
-  CUdeviceptr va = 0;
-  if (a.reserve(&va, size, gran, 0, 0) != CUDA_SUCCESS) {
-    a.release(h);
-    return nullptr;
-  }
-  if (a.map(va, size, 0, h, 0) != CUDA_SUCCESS) {
-    a.addr_free(va, size);
-    a.release(h);
-    return nullptr;
-  }
-  std::vector<CUmemAccessDesc> acc;
-  for (int d = 0; d < n_dev; d++) {  // every GPU of this process may read the table
-    CUmemAccessDesc x;
-    memset(&x, 0, sizeof(x));
-    x.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
-    x.location.id = d;
-    x.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
-    acc.push_back(x);
-  }
-  CUmemAccessDesc hostacc;
-  memset(&hostacc, 0, sizeof(hostacc));
-  hostacc.location.type = CU_MEM_LOCATION_TYPE_HOST_NUMA;
-  hostacc.location.id = numa;
-  hostacc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
-  acc.push_back(hostacc);
-  if (a.set_access(va, size, acc.data(), acc.size()) != CUDA_SUCCESS) {
-    a.unmap(va, size);
-    a.addr_free(va, size);
-    a.release(h);
-    return nullptr;
-  }
-  void* p = reinterpret_cast<void*>(va);
-  std::lock_guard<std::mutex> lock(g_vmm_mu);
-  g_vmm_blocks[p] = VmmBlock{h, size};
-  *mapped = size;
-  return p;
-}
-
-bool vmm_host_free(void* p) {
-  VmmBlock b;
-  {
-    std::lock_guard<std::mutex> lock(g_vmm_mu);
-    auto it = g_vmm_blocks.find(p);
-    if (it == g_vmm_blocks.end()) return false;
-    b = it->second;
-    g_vmm_blocks.erase(it);
-  }
-  const VmmApi& a = vmm_api();
-  CUdeviceptr va = reinterpret_cast<CUdeviceptr>(p);
-  a.unmap(va, b.size);
-  a.addr_free(va, b.size);
-  a.release(b.handle);
-  return true;
-}
-}  // namespace
-
 
 // ---- lookup scratch that needs no allocation ------------------------------------------------
 // ugc_lookup_i64_static keeps its index lists and counters in this fixed device array instead
@@ -677,7 +852,7 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
     return rc;
   }
   r->slice_bytes = std::max<size_t>((size_t)r->capacity * c->cfg.row_bytes, 256);
-  r->slice = ctx_alloc(c, r->slice_bytes);
+  r->slice = ctx_alloc_shared(c, r->slice_bytes);
   if (!r->slice) {
     int rc = fail(UGC_ERR_NOMEM, "slice allocation of %zu bytes failed", r->slice_bytes);
     release_replica(c, r);
@@ -744,10 +919,23 @@ int ugc_export(ugc_ctx* c, int replica_id, ugc_peer_handle* out) {
   out->table_ptr = (uint64_t)(uintptr_t)r->table_mem;
   out->table_kind = r->table.kind;
   out->table_lines = r->table.kind == kTableFlat ? r->table.num_keys : (uint64_t)r->table.line_mask + 1;
-  // IPC handles only describe whole cudaMalloc allocations; with a caller-supplied allocator
-  // the pointers may sit inside a larger block, so cross-process export needs the built-in
-  // allocator.
-  if (!c->cfg.alloc) {
+  // Cross-process export needs the built-in allocator (IPC handles describe whole
+  // allocations; a caller's allocator may hand out pieces of a larger block).
+  DevBlock sb, tb;
+  if (!c->cfg.alloc && dev_block_find(r->slice, &sb) && dev_block_find(r->table_mem, &tb)) {
+    const int sfd = dev_block_export_fd(r->slice), tfd = dev_block_export_fd(r->table_mem);
+    if (sfd >= 0 && tfd >= 0) {
+      // other processes of this user may duplicate the two descriptors out of this process
+      prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0);
+      out->has_ipc = 2;
+      int64_t v[2] = {sfd, (int64_t)sb.size};
+      memcpy(out->slice_ipc, v, sizeof(v));
+      int64_t w[2] = {tfd, (int64_t)tb.size};
+      memcpy(out->table_ipc, w, sizeof(w));
+      return UGC_OK;
+    }
+  }
+  if (!c->cfg.alloc && !dev_block_find(r->slice, &sb)) {
     UGC_CUDA(cudaSetDevice(r->device));
     cudaIpcMemHandle_t h;
     static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
@@ -796,9 +984,32 @@ int ugc_import_peer(ugc_ctx* c, int replica_id, const ugc_peer_handle* peer) {
   void* slice = nullptr;
   void* table = nullptr;
   if (peer->pid == (int64_t)getpid()) {
-    UGC_TRY(enable_peer(r->device, peer->device_id));
     slice = (void*)(uintptr_t)peer->slice_ptr;
     table = (void*)(uintptr_t)peer->table_ptr;
+    DevBlock sb, tb;
+    if (dev_block_find(slice, &sb) && dev_block_find(table, &tb)) {
+      // virtual-memory blocks: access is granted per device, peer-access enabling does not apply
+      if (!dev_set_access(slice, sb.size, r->device) || !dev_set_access(table, tb.size, r->device))
+        return fail(UGC_ERR_CUDA, "cannot grant device %d access to replica %d's memory", r->device, p);
+      // keep the owner's own access
+      dev_set_access(slice, sb.size, sb.device);
+      dev_set_access(table, tb.size, tb.device);
+    } else {
+      UGC_TRY(enable_peer(r->device, peer->device_id));
+    }
+  } else if (peer->has_ipc == 2) {
+    UGC_CUDA(cudaSetDevice(r->device));
+    int64_t v[2], w[2];
+    memcpy(v, peer->slice_ipc, sizeof(v));
+    memcpy(w, peer->table_ipc, sizeof(w));
+    slice = dev_import(peer->pid, (int)v[0], (size_t)v[1], r->device);
+    if (!slice)
+      return fail(UGC_ERR_CUDA, "cannot import replica %d's slice (descriptor %d of process %lld)", p,
+                  (int)v[0], (long long)peer->pid);
+    r->ipc_opened[r->n_ipc_opened++] = slice;
+    table = dev_import(peer->pid, (int)w[0], (size_t)w[1], r->device);
+    if (!table) return fail(UGC_ERR_CUDA, "cannot import replica %d's table", p);
+    r->ipc_opened[r->n_ipc_opened++] = table;
   } else {
     if (!peer->has_ipc) return fail(UGC_ERR_INVALID, "peer handle from another process carries no IPC handles");
     UGC_CUDA(cudaSetDevice(r->device));
