@@ -458,6 +458,16 @@ def run_ours(a):
         step(i)
     lk_ms, ga_ms, nprof = cache.profile_end(rank)
     ga_all = all_list(ga_ms / max(nprof, 1) * 1e3)
+    # when each source group of the gather was done, sampled over a few single lookups
+    grp = np.zeros(3)
+    n_s = min(20, a.steps)
+    for i in range(n_s):
+        step(a.warmup + i)
+        torch.cuda.synchronize()
+        sg = cache.stats(rank)
+        grp += np.array([sg["last_local_ns"], sg["last_remote_ns"], sg["last_host_ns"]]) / 1e3
+    grp /= n_s
+    grp_all = [all_list(float(x)) for x in grp]
     t2 = time.time()
     sampler.stop()
     clocks = sampler.summary(t0, t2)
@@ -601,7 +611,8 @@ def run_ours(a):
                      "lookup_group_avg_us": lookup_ms_avg * 1e3},
         "cpu_baseline": cpu, "e2e": e2e, "e2e_device_consumer": e2e_dev, "clocks": clocks,
         "gpu_launches": 2 * a.steps * G,
-        "per_rank": {"step_us": [m / a.steps * 1e3 for m in ms_all], "gather_us": ga_all},
+        "per_rank": {"step_us": [m / a.steps * 1e3 for m in ms_all], "gather_us": ga_all,
+                     "group_done_us": {"local": grp_all[0], "remote": grp_all[1], "host": grp_all[2]}},
         "verified_vs_oracle": verified, "setup_s": setup_s, "tuning": cache.get_tuning(rank),
         "cache": {"local_rows": st["num_local_rows"], "remote_keys": st["num_remote_keys"],
                   "host_keys": st["num_host_keys"], "table_bytes": st["table_bytes"]},

@@ -119,6 +119,9 @@ typedef struct {
   uint64_t err_key_range;
   uint64_t err_table;
   uint64_t lookups;            /* lookups issued on this replica                       */
+  /* device-clock time (ns) from the start of the last gather kernel until the last CTA of
+     each source group was done; 0 for an empty group */
+  uint64_t last_local_ns, last_remote_ns, last_host_ns;
 } ugc_stats_t;
 
 const char* ugc_version(void);

@@ -73,6 +73,9 @@ class Stats(C.Structure):
         ("err_key_range", C.c_uint64),
         ("err_table", C.c_uint64),
         ("lookups", C.c_uint64),
+        ("last_local_ns", C.c_uint64),
+        ("last_remote_ns", C.c_uint64),
+        ("last_host_ns", C.c_uint64),
     ]
 
 

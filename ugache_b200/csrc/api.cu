@@ -1333,6 +1333,12 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   out->err_key_range = h.err_key_range;
   out->err_table = h.err_table;
   out->lookups = r->lookups;
+  auto span = [&](int g) -> uint64_t {
+    return (h.t_end[g] > h.t_start && h.t_start) ? (uint64_t)(h.t_end[g] - h.t_start) : 0;
+  };
+  out->last_local_ns = span(kGroupLocal);
+  out->last_remote_ns = span(kGroupRemote);
+  out->last_host_ns = span(kGroupHost);
   return UGC_OK;
 }
 

@@ -62,6 +62,9 @@ struct Counters {
   uint32_t last_keys;
   unsigned long long err_key_range;  // sticky
   unsigned long long err_table;      // sticky
+  // device clock (ns) of the last gather: earliest CTA start and, per group, latest CTA end
+  unsigned long long t_start;
+  unsigned long long t_end[kNumGroup];
 };
 
 // Everything the role-partitioned gather needs.

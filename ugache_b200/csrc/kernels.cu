@@ -226,6 +226,7 @@ __global__ void __launch_bounds__(kBlock)
   // was launched with programmatic stream serialization).
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (bad) atomicAdd(&counters->err_key_range, (unsigned long long)bad);
+  if (blockIdx.x == 0 && tid < kNumGroup) counters->t_end[tid] = 0;  // re-armed for the gather's timestamps
 
   // Group, count per warp with ballots.
   uint32_t group[kKeysPerThread], rank_in_warp[kKeysPerThread];
@@ -481,6 +482,8 @@ __global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // The next lookup's key loads and table probes may start while this grid drains.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  unsigned long long t0 = 0;
+  if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   uint32_t cnt[kNumGroup];
 #pragma unroll
   for (int g = 0; g < kNumGroup; g++) cnt[g] = p.counters->count[g];
@@ -533,6 +536,11 @@ __global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
   // The last CTA to finish publishes the counts of this lookup and re-arms the counters.
   __syncthreads();
   if (threadIdx.x == 0) {
+    // when each source group was done, for ugc_stats (one atomic per CTA)
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (b == 0) p.counters->t_start = t0;
+    if (cnt[g] != 0) atomicMax(&p.counters->t_end[g], t1);
     __threadfence();
     uint32_t done = atomicAdd(&p.counters->done_ctas, 1u);
     if (done == (uint32_t)grid - 1) {
