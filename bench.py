@@ -47,6 +47,11 @@ def parse_args():
     ap.add_argument("--cache-pct", type=float, default=0.10, help="fraction of rows per GPU")
     ap.add_argument("--alpha", type=float, default=1.2)
     ap.add_argument("--batch", type=int, default=8192 * 26)
+    ap.add_argument("--workload", default="dlr", choices=["dlr", "gnn"],
+                    help="dlr: Zipf key batches; gnn: R-MAT graph, 3-hop sampled unique node ids, "
+                         "cache ordered by degree")
+    ap.add_argument("--gnn-degree", type=int, default=15)
+    ap.add_argument("--gnn-seeds", type=int, default=8000)
     ap.add_argument("--policy", default="intuitive", choices=["intuitive", "rep", "clique_part"])
     ap.add_argument("--table-kind", type=int, default=0)
     ap.add_argument("--empty-feat", type=int, default=0,
@@ -253,6 +258,10 @@ def all_sum(x):
 
 
 def workload_name(a):
+    if a.workload == "gnn":
+        return ("gnn_rmat_%dMx%d%s_deg%d_3hop_15-10-5_seeds%d_cache%.0f%%" %
+                (a.rows // 1_000_000, a.dim, "f32" if a.dtype == "float32" else "f16", a.gnn_degree,
+                 a.gnn_seeds, a.cache_pct * 100))
     return ("dlr_zipf%.2f_%dMx%d%s_cache%.0f%%_batch%d" %
             (a.alpha, a.rows // 1_000_000, a.dim, "f32" if a.dtype == "float32" else "f16",
              a.cache_pct * 100, a.batch))
@@ -362,7 +371,13 @@ def run_ours(a):
     barrier()
 
     # ---- hotness, placement, build ---------------------------------------------------
-    ids, freqs = wl.analytic_hotness(a.rows, a.alpha)
+    gnn = None
+    if a.workload == "gnn":
+        from ugache_b200 import workload_gnn
+        gnn = workload_gnn.GnnWorkload(a.rows, a.gnn_degree, a.seed, device=dev)
+        ids, freqs = gnn.hotness()
+    else:
+        ids, freqs = wl.analytic_hotness(a.rows, a.alpha)
     placement = rt.solve_placement(a.policy, G, ids, freqs, a.cache_pct * 100.0)
     del ids, freqs
     cache = rt.Cache(G, a.rows, row_bytes, a.cache_pct, max_batch=a.batch,
@@ -403,12 +418,27 @@ def run_ours(a):
 
     # ---- keys ---------------------------------------------------------------------------
     total = a.warmup + a.steps
-    keys_np = make_keys(a, rank, total)
+    if gnn is not None:
+        # one deduplicated node-id set per step; sizes vary from step to step
+        keys_list = [gnn.batch(rank, i, a.gnn_seeds).contiguous() for i in range(total)]
+        sizes = [int(k.numel()) for k in keys_list]
+        a.batch = max(sizes)
+        cache.reserve_batch(rank, a.batch)
+        keys_np = np.zeros((total, a.batch), dtype=np.int64)
+        for i, k in enumerate(keys_list):
+            keys_np[i, :sizes[i]] = k.cpu().numpy()
+        gnn = None  # the graph is no longer needed
+        del keys_list
+        torch.cuda.empty_cache()
+    else:
+        keys_np = make_keys(a, rank, total)
+        sizes = [a.batch] * total
     keys_dev = torch.from_numpy(keys_np).to(dev)
     out = torch.empty((a.batch, row_bytes), dtype=torch.uint8, device=dev)
+    keys_timed = sum(sizes[a.warmup:total])
 
     def step(i):
-        cache.lookup_ptr(rank, keys_dev[i].data_ptr(), 8, a.batch, out.data_ptr(), stream)
+        cache.lookup_ptr(rank, keys_dev[i].data_ptr(), 8, sizes[i], out.data_ptr(), stream)
 
     # ---- optional verification of one batch against the oracle -------------------------
     verified = None
@@ -418,8 +448,8 @@ def run_ours(a):
         torch.cuda.synchronize()
         got = out.cpu().numpy()
         tv = table.np.reshape(host_rows, row_bytes)
-        want = orc.gather(tv, keys_np[0], empty_feat=a.empty_feat)
-        verified = bool(got.tobytes() == want.tobytes())
+        want = orc.gather(tv, keys_np[0][:sizes[0]], empty_feat=a.empty_feat)
+        verified = bool(got[:sizes[0]].tobytes() == want.tobytes())
         # the table itself against the oracle's generator on sampled rows
         rows = np.unique(keys_np[0][:64] % host_rows)
         want_rows = orc.gen_rows_for_keys(a.seed, rows, a.dim,
@@ -473,7 +503,9 @@ def run_ours(a):
     clocks = sampler.summary(t0, t2)
 
     # per-source bytes over the timed steps (host recount through the table words)
-    words = cache.table_words(rank, keys_dev[a.warmup:total].reshape(-1).to(torch.int32)).view(-1)
+    valid = (torch.arange(a.batch, device=dev)[None, :] <
+             torch.tensor(sizes[a.warmup:total], device=dev)[:, None]).reshape(-1)
+    words = cache.table_words(rank, keys_dev[a.warmup:total].reshape(-1)[valid].to(torch.int32)).view(-1)
     torch.cuda.synchronize()
     w = words.cpu().numpy().view(np.uint32)
     n_host = int((w == 0xFFFFFFFF).sum())
@@ -489,19 +521,20 @@ def run_ours(a):
         kpin = torch.from_numpy(keys_np[a.warmup:a.warmup + ke]).pin_memory()
         opin = torch.empty((a.batch, row_bytes), dtype=torch.uint8).pin_memory()
         for i in range(2):
-            cache.lookup_host_ptr(rank, kpin[i].data_ptr(), 8, a.batch, opin.data_ptr(), stream)
+            cache.lookup_host_ptr(rank, kpin[i].data_ptr(), 8, sizes[a.warmup + i], opin.data_ptr(), stream)
         barrier()
         torch.cuda.synchronize()
         ee0, ee1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ee0.record()
         for i in range(ke):
-            cache.lookup_host_ptr(rank, kpin[i].data_ptr(), 8, a.batch, opin.data_ptr(), stream)
+            cache.lookup_host_ptr(rank, kpin[i].data_ptr(), 8, sizes[a.warmup + i], opin.data_ptr(), stream)
         ee1.record()
         torch.cuda.synchronize()
         barrier()
         e2e_ms = all_max(ee0.elapsed_time(ee1))
-        e2e = {"value": G * ke * a.batch * row_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": a.batch * 8, "d2h_bytes_per_step": a.batch * row_bytes,
+        ke_keys = sum(sizes[a.warmup:a.warmup + ke])
+        e2e = {"value": G * ke_keys * row_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": ke_keys // ke * 8, "d2h_bytes_per_step": ke_keys // ke * row_bytes,
                "steps": ke, "ms_per_step": e2e_ms / ke,
                "note": "ugc_lookup_host: pinned host keys in, pinned host rows out, every step"}
 
@@ -519,13 +552,13 @@ def run_ours(a):
         ed0.record()
         for i in range(ke):
             kin.copy_(kpin[i], non_blocking=True)
-            cache.lookup_ptr(rank, kin.data_ptr(), 8, a.batch, out.data_ptr(), stream)
+            cache.lookup_ptr(rank, kin.data_ptr(), 8, sizes[a.warmup + i], out.data_ptr(), stream)
             res.copy_(o64, non_blocking=True)
         ed1.record()
         torch.cuda.synchronize()
         barrier()
         ed_ms = all_max(ed0.elapsed_time(ed1))
-        e2e_dev = {"value": G * ke * a.batch * row_bytes / (ed_ms * 1e-3) / 1e9, "unit": "GB/s",
+        e2e_dev = {"value": G * ke_keys * row_bytes / (ed_ms * 1e-3) / 1e9, "unit": "GB/s",
                    "h2d_bytes_per_step": a.batch * 8, "d2h_bytes_per_step": 8, "steps": ke,
                    "ms_per_step": ed_ms / ke,
                    "note": "pinned host keys in every step, rows left in HBM for a consumer on the "
@@ -539,31 +572,34 @@ def run_ours(a):
         threads = orc.max_threads()
         o = np.empty((a.batch, row_bytes), dtype=np.uint8)
         for i in range(3):
-            orc.gather(tv, keys_np[i % total], empty_feat=a.empty_feat, num_threads=threads, out=o)
+            orc.gather(tv, keys_np[i % total][:sizes[i % total]], empty_feat=a.empty_feat,
+                       num_threads=threads, out=o)
         c0 = time.perf_counter()
+        cpu_keys = 0
         for i in range(a.cpu_steps):
-            orc.gather(tv, keys_np[(3 + i) % total], empty_feat=a.empty_feat, num_threads=threads,
-                       out=o)
+            j = (3 + i) % total
+            orc.gather(tv, keys_np[j][:sizes[j]], empty_feat=a.empty_feat, num_threads=threads, out=o)
+            cpu_keys += sizes[j]
         cdt = time.perf_counter() - c0
-        cpu = {"value": a.cpu_steps * a.batch * row_bytes / cdt / 1e9, "unit": "GB/s",
+        cpu = {"value": cpu_keys * row_bytes / cdt / 1e9, "unit": "GB/s",
                "cores": threads, "kind": "port",
                "sample": "%d batches of %d keys over the same host table, after 3 warm-up "
                          "batches, all host threads" % (a.cpu_steps, a.batch)}
 
     # ---- the line -------------------------------------------------------------------------
     sec = ms_total * 1e-3
-    bytes_out_rank = a.steps * a.batch * row_bytes
+    bytes_out_rank = keys_timed * row_bytes
     value = G * bytes_out_rank / sec / 1e9
     hbm_peak, peak_kind = measured_peaks()
     gather_ms_avg = ga_ms / max(nprof, 1)
     lookup_ms_avg = lk_ms / max(nprof, 1)
-    algo_bytes = 2.0 * a.batch * row_bytes
+    algo_bytes = 2.0 * keys_timed / a.steps * row_bytes
     achieved = algo_bytes / (gather_ms_avg * 1e-3) / 1e9 if gather_ms_avg > 0 else 0.0
     # mixed-source roofline per step and GPU: max over sources of bytes / bandwidth
     b_loc = n_local / a.steps * row_bytes
     b_rem = n_remote / a.steps * row_bytes
     b_host = n_host / a.steps * row_bytes
-    b_out = a.batch * row_bytes
+    b_out = keys_timed / a.steps * row_bytes
 
     def tstar(hbm, nvl, pcie):
         return max((b_loc + b_out) / hbm, b_rem / nvl, b_host / pcie) / 1e9 * 1e6  # us
@@ -596,7 +632,8 @@ def run_ours(a):
                          "batch every step, no flush" % (st["slice_bytes"] / 1e9,
                                                          host_rows * row_bytes / 1e9),
                    **note},
-        "per_gpu_gbs": value / G, "mkeys_per_s_per_gpu": a.steps * a.batch / sec / 1e6,
+        "per_gpu_gbs": value / G, "mkeys_per_s_per_gpu": keys_timed / sec / 1e6,
+        "keys_per_step_avg": keys_timed / a.steps,
         "source_split": {"local": n_local / n_all, "remote": n_remote / n_all,
                          "host": n_host / n_all},
         "mixed_roofline": mixed,

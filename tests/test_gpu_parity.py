@@ -261,3 +261,30 @@ def test_refresh_keeps_results_identical(built_lib):
         cache.refresh_all_local(p_old, list(range(G)))
         check("after second refresh")
         cache.close()
+
+
+def test_gnn_shaped_batches(built_lib):
+    """Deduplicated, variable-size node-id batches from the sampled R-MAT graph, cache ordered
+    by degree (the GNN configuration at small scale)."""
+    from ugache_b200 import runtime as rt, workload as wl, workload_gnn as wg
+    N, dim, G = 50000, 128, 4
+    g = wg.GnnWorkload(N, 15, 9)
+    ids, freqs = g.hotness()
+    table = wl.table(13, N, dim)
+    cache = rt.Cache(G, N, dim * 4, 0.05, max_batch=1 << 12)
+    cache.set_placement(rt.solve_placement("intuitive", G, ids, freqs, 5.0))
+    host = pinned_table(table)
+    ndev = torch.cuda.device_count()
+    for r in range(G):
+        cache.build(r, r % ndev, host.data_ptr())
+    cache.connect_local()
+    for r in range(G):
+        cache.attach_peers(r)
+    for r in range(G):
+        for it in range(2):
+            keys = g.batch(r, it, num_seeds=200).numpy()
+            assert len(np.unique(keys)) == len(keys)
+            cache.reserve_batch(r, len(keys))
+            got = lookup_np(cache, r, keys)
+            assert got.tobytes() == orc.gather(table, keys).tobytes()
+    cache.close()
