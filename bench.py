@@ -71,6 +71,12 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--verify", type=int, default=1, help="check one batch against the oracle")
+    ap.add_argument("--refresh", type=float, default=0.0,
+                    help="after the timed region, drift the hotness order by this fraction of the "
+                         "key space and run one full cache refresh; its phase times are reported")
+    ap.add_argument("--variants", default="",
+                    help="extra tuning variants timed after the main run on the same cache, e.g. "
+                         "'programmatic_launch=3;host_ctas=32,remote_ctas=64'; reported under 'variants'")
     ap.add_argument("--sweep-out", default="", help="write extra per-phase numbers here (json)")
     return ap.parse_args()
 
@@ -482,6 +488,28 @@ def run_ours(a):
     ms_all = all_list(ms_rank)
     st_last = cache.stats(rank)
 
+    # ---- optional: the same timed loop under other launch shapes (tuning aid) --------------
+    variants = []
+    if a.variants:
+        base_tuning = cache.get_tuning(rank)
+        for spec in a.variants.split(";"):
+            kv = {k.strip(): int(v) for k, v in (item.split("=") for item in spec.split(",") if item)}
+            cache.tune(rank, **kv)
+            for i in range(a.warmup):
+                step(i)
+            barrier()
+            torch.cuda.synchronize()
+            v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            v0.record()
+            for i in range(a.warmup, total):
+                step(i)
+            v1.record()
+            torch.cuda.synchronize()
+            barrier()
+            variants.append({"tuning": kv, "step_us_per_rank": [m / a.steps * 1e3 for m in
+                                                                 all_list(v0.elapsed_time(v1))]})
+            cache.tune(rank, **base_tuning)
+
     # ---- same steps again with per-kernel events (for the roofline of the gather) ------
     cache.profile_begin(rank, a.steps)
     for i in range(a.warmup, total):
@@ -513,6 +541,42 @@ def run_ours(a):
     n_all = len(w)
     n_remote = n_all - n_host - n_local
     del words, w
+
+    # ---- optional: one full cache refresh (new placement from drifted hotness) -------------
+    refresh = None
+    if a.refresh > 0 and a.workload == "dlr":
+        ids, freqs = wl.analytic_hotness(a.rows, a.alpha)
+        ids = np.roll(ids, int(a.refresh * a.rows))       # the hot set moves
+        p_new = rt.solve_placement(a.policy, G, ids, freqs, a.cache_pct * 100.0)
+        del ids, freqs
+        before = cache.stats(rank)
+        barrier()
+        tr = [time.perf_counter()]
+        cache.refresh_set_placement(p_new)
+        cache.refresh_evict(rank, stream)
+        barrier(); tr.append(time.perf_counter())
+        cache.refresh_fill(rank, stream)
+        barrier(); tr.append(time.perf_counter())
+        cache.refresh_attach(rank, stream)
+        barrier(); tr.append(time.perf_counter())
+        cache.refresh_commit()
+        barrier(); tr.append(time.perf_counter())
+        after = cache.stats(rank)
+        ok = None
+        if a.verify and rank == 0:
+            from oracle import oracle as orc
+            step(0)
+            torch.cuda.synchronize()
+            tv = table.np.reshape(host_rows, row_bytes)
+            ok = bool(out.cpu().numpy()[:sizes[0]].tobytes() ==
+                      orc.gather(tv, keys_np[0][:sizes[0]], empty_feat=a.empty_feat).tobytes())
+        refresh = {"drift_fraction": a.refresh, "seconds": {"classify_evict": tr[1] - tr[0], "fill_insert": tr[2] - tr[1],
+                                                          "attach_peers": tr[3] - tr[2], "commit": tr[4] - tr[3],
+                                                          "total": tr[4] - tr[0]},
+                   "local_rows_before": before["num_local_rows"], "local_rows_after": after["num_local_rows"],
+                   "free_rows_after": after["free_rows"], "table_errors": after["err_table"],
+                   "lookup_exact_after_refresh": ok}
+        barrier()
 
     # ---- end to end with host buffers -------------------------------------------------
     e2e = None
@@ -650,6 +714,7 @@ def run_ours(a):
         "gpu_launches": 2 * a.steps * G,
         "per_rank": {"step_us": [m / a.steps * 1e3 for m in ms_all], "gather_us": ga_all,
                      "group_done_us": {"local": grp_all[0], "remote": grp_all[1], "host": grp_all[2]}},
+        "variants": variants, "refresh": refresh,
         "verified_vs_oracle": verified, "setup_s": setup_s, "tuning": cache.get_tuning(rank),
         "cache": {"local_rows": st["num_local_rows"], "remote_keys": st["num_remote_keys"],
                   "host_keys": st["num_host_keys"], "table_bytes": st["table_bytes"]},

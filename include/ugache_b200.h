@@ -257,6 +257,17 @@ int ugc_refresh_fill(ugc_ctx* ctx, int replica_id, void* stream);
 int ugc_refresh_attach(ugc_ctx* ctx, int replica_id, void* stream);
 int ugc_refresh_commit(ugc_ctx* ctx);
 
+/* -- hotness recording --------------------------------------------------------------------- */
+/* Counts key accesses on the GPU: counts[key] += 1 for every key of a device-resident batch
+ * (key_bytes 4 or 8).  The counter array (4 bytes per id of the key space) is allocated on
+ * the first call.  Replaces FreqRecorder::Record on host copies of the keys
+ * (coll_cache_lib/freq_recorder.cc, fed by python_tf2/.../lookup_manager.cc:290-312).
+ * ugc_hotness_read copies the counters to host memory (num_total_item uint32) after
+ * synchronising `stream`, and zeroes them on the device if `reset` is non-zero; ranking them
+ * (ids by descending count) gives the rank_ids / rank_freqs input of ugc_solve_placement. */
+int ugc_record(ugc_ctx* ctx, int replica_id, const void* keys, int key_bytes, size_t n, void* stream);
+int ugc_hotness_read(ugc_ctx* ctx, int replica_id, uint32_t* counts_out, int reset, void* stream);
+
 /* -- introspection --------------------------------------------------------------------- */
 int ugc_stats(ugc_ctx* ctx, int replica_id, ugc_stats_t* out);
 

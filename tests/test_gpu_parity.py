@@ -288,3 +288,36 @@ def test_gnn_shaped_batches(built_lib):
             got = lookup_np(cache, r, keys)
             assert got.tobytes() == orc.gather(table, keys).tobytes()
     cache.close()
+
+
+def test_device_hotness_recording_drives_a_refresh(built_lib):
+    """Access counts recorded on the GPU equal a host bincount; ranking them and refreshing
+    moves the cache to the recorded hot set, with lookups exact before and after."""
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim = 30000, 32
+    table = wl.table(3, N, dim)
+    ids, freqs = wl.analytic_hotness(N, 1.2)
+    cache = rt.Cache(1, N, dim * 4, 0.10, max_batch=1 << 14)
+    cache.set_placement(rt.solve_placement("rep", 1, ids, freqs, 10.0))
+    host = pinned_table(table)
+    cache.build(0, 0, host.data_ptr())
+    rng = np.random.default_rng(5)
+    perm = rng.permutation(N)                      # a different popularity order
+    want = np.zeros(N, dtype=np.int64)
+    for i in range(6):
+        keys = perm[wl.zipf_ranks(rng.random(12000), N, 1.2)].astype(np.int64)
+        k = torch.from_numpy(keys).cuda()
+        cache.record(0, k if i % 2 else k.to(torch.int32))
+        want += np.bincount(keys, minlength=N)
+    got = cache.hotness_read(0, reset=True)
+    assert np.array_equal(got.astype(np.int64), want)
+    assert cache.hotness_read(0).sum() == 0        # reset took effect
+    rank_ids, rank_freqs = rt.Cache.rank_hotness(got)
+    keys = perm[wl.zipf_ranks(rng.random(8000), N, 1.2)].astype(np.int64)
+    before = lookup_np(cache, 0, keys)
+    host_before = cache.stats(0)["last_host"]
+    cache.refresh_all_local(rt.solve_placement("rep", 1, rank_ids, rank_freqs, 10.0), [0])
+    after = lookup_np(cache, 0, keys)
+    assert before.tobytes() == after.tobytes() == orc.gather(table, keys).tobytes()
+    assert cache.stats(0)["last_host"] < host_before / 2      # the recorded hot set is cached now
+    cache.close()

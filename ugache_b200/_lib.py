@@ -130,6 +130,8 @@ SIGNATURES = {
     "ugc_refresh_fill": (_I, [_P, _I, _P]),
     "ugc_refresh_attach": (_I, [_P, _I, _P]),
     "ugc_refresh_commit": (_I, [_P]),
+    "ugc_record": (_I, [_P, _I, _P, _I, _SZ, _P]),
+    "ugc_hotness_read": (_I, [_P, _I, _P, _I, _P]),
     "ugc_stats": (_I, [_P, _I, C.POINTER(Stats)]),
     "ugc_get_tuning": (_I, [_P, _I, C.POINTER(Tuning)]),
     "ugc_set_tuning": (_I, [_P, _I, C.POINTER(Tuning)]),

@@ -385,6 +385,8 @@ struct Replica {
   uint32_t max_batch = 0;
   // host-buffer lookups
   DevBuf stage_keys, stage_out;
+  // hotness counters (one uint32 per id), allocated on first use
+  uint32_t* hot_counts = nullptr;
   // build / refresh staging
   DevBuf stage_a, stage_b;
   // bookkeeping mirrored from the reference's CacheEntryManager
@@ -582,6 +584,7 @@ void release_replica(ugc_ctx* c, Replica* r) {
   ctx_free_shared(c, r->table_mem);
   for (auto& l : r->list) ctx_free(c, l);
   ctx_free(c, r->counters);
+  ctx_free(c, r->hot_counts);
   ctx_free(c, r->stage_keys.ptr);
   ctx_free(c, r->stage_out.ptr);
   ctx_free(c, r->stage_a.ptr);
@@ -1308,6 +1311,41 @@ int ugc_refresh_commit(ugc_ctx* c) {
 }
 
 // --------------------------------------------------------------------------------------
+int ugc_record(ugc_ctx* c, int replica_id, const void* keys, int key_bytes, size_t n, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (key_bytes != 4 && key_bytes != 8) return fail(UGC_ERR_INVALID, "key_bytes must be 4 or 8");
+  if (n == 0) return UGC_OK;
+  if (!keys || n > 0xffffffffull) return fail(UGC_ERR_INVALID, "bad key batch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  UGC_CUDA(cudaSetDevice(r->device));
+  if (!r->hot_counts) {
+    const size_t bytes = (size_t)c->cfg.num_total_item * sizeof(uint32_t);
+    r->hot_counts = static_cast<uint32_t*>(ctx_alloc(c, bytes));
+    if (!r->hot_counts) return fail(UGC_ERR_NOMEM, "hotness counters (%zu bytes) could not be allocated", bytes);
+    UGC_CUDA(cudaMemsetAsync(r->hot_counts, 0, bytes, s));
+  }
+  UGC_CUDA(launch_record(keys, key_bytes, (uint32_t)n, r->hot_counts, c->cfg.num_total_item, s));
+  return UGC_OK;
+}
+
+int ugc_hotness_read(ugc_ctx* c, int replica_id, uint32_t* counts_out, int reset, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (!counts_out) return fail(UGC_ERR_INVALID, "null output");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  UGC_CUDA(cudaSetDevice(r->device));
+  const size_t bytes = (size_t)c->cfg.num_total_item * sizeof(uint32_t);
+  if (!r->hot_counts) {
+    memset(counts_out, 0, bytes);
+    return UGC_OK;
+  }
+  UGC_CUDA(cudaMemcpyAsync(counts_out, r->hot_counts, bytes, cudaMemcpyDeviceToHost, s));
+  if (reset) UGC_CUDA(cudaMemsetAsync(r->hot_counts, 0, bytes, s));
+  UGC_CUDA(cudaStreamSynchronize(s));
+  return UGC_OK;
+}
+
 int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   Replica* r;
   UGC_TRY(get_replica(c, replica_id, true, &r));

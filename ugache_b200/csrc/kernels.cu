@@ -673,6 +673,19 @@ __global__ void __launch_bounds__(kBlock)
 }
 
 // ------------------------------------------------------------------------------------
+// hotness recording: per-key access counts of a batch, kept on the device
+// ------------------------------------------------------------------------------------
+template <typename KeyT>
+__global__ void __launch_bounds__(kBlock)
+    record_kernel(const KeyT* __restrict__ keys, uint32_t n, uint32_t* __restrict__ counts,
+                  uint64_t num_keys) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint64_t k = (uint64_t)keys[i];
+  if (k < num_keys) atomicAdd(counts + k, 1u);  // fire-and-forget reduction in L2
+}
+
+// ------------------------------------------------------------------------------------
 // synthetic table rows
 // ------------------------------------------------------------------------------------
 __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
@@ -890,6 +903,19 @@ cudaError_t launch_table_resolve(const TableView& peer, const uint32_t* keys, ui
                                  cudaStream_t stream) {
   if (n == 0) return cudaSuccess;
   table_resolve_kernel<<<grid_for(n), kBlock, 0, stream>>>(peer, keys, n, expect_loc, offs, counters);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_record(const void* keys, int key_bytes, uint32_t n, uint32_t* counts,
+                          uint64_t num_keys, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  if (key_bytes == 8) {
+    record_kernel<long long><<<grid_for(n), kBlock, 0, stream>>>(static_cast<const long long*>(keys), n,
+                                                                counts, num_keys);
+  } else {
+    record_kernel<uint32_t><<<grid_for(n), kBlock, 0, stream>>>(static_cast<const uint32_t*>(keys), n,
+                                                               counts, num_keys);
+  }
   return cudaGetLastError();
 }
 

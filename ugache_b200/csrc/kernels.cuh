@@ -46,6 +46,10 @@ cudaError_t launch_table_resolve(const TableView& peer, const uint32_t* keys, ui
                                  uint32_t expect_loc, uint32_t* offs, Counters* counters,
                                  cudaStream_t stream);
 
+// counts[key] += 1 for every key of the batch (keys outside [0, num_keys) are ignored)
+cudaError_t launch_record(const void* keys, int key_bytes, uint32_t n, uint32_t* counts,
+                          uint64_t num_keys, cudaStream_t stream);
+
 cudaError_t launch_gen_table(void* dst, uint64_t seed, uint64_t row_begin, uint64_t n_rows,
                              uint64_t dim, int elem_bytes, cudaStream_t stream);
 

@@ -215,6 +215,27 @@ class Cache:
             self.refresh_attach(r, stream)
         self.refresh_commit()
 
+    # -- hotness ---------------------------------------------------------------------------
+    def record(self, replica_id, keys, stream=None):
+        """Count the accesses of a CUDA key tensor (int64 / int32) on the device."""
+        import torch
+        kb = 8 if keys.dtype == torch.int64 else 4
+        s = torch.cuda.current_stream(keys.device).cuda_stream if stream is None else stream
+        check(_lib.lib().ugc_record(self._h, replica_id, C.c_void_p(keys.data_ptr()), kb,
+                                    keys.numel(), C.c_void_p(s)))
+
+    def hotness_read(self, replica_id, reset=False, stream=0):
+        counts = np.empty(self.cfg.num_total_item, dtype=np.uint32)
+        check(_lib.lib().ugc_hotness_read(self._h, replica_id, _ptr(counts), 1 if reset else 0,
+                                          C.c_void_p(stream)))
+        return counts
+
+    @staticmethod
+    def rank_hotness(counts):
+        """(rank_ids, rank_freqs) for the placement solvers: ids by descending count, ties by id."""
+        order = np.argsort(-counts.astype(np.int64), kind="stable").astype(np.uint32)
+        return order, counts[order]
+
     # -- introspection ------------------------------------------------------------------
     def stats(self, replica_id):
         s = _lib.Stats()
