@@ -57,7 +57,7 @@ def parse_args():
     ap.add_argument("--empty-feat", type=int, default=0,
                     help="k>0: host table holds 2^k rows, host offsets wrap (mock)")
     ap.add_argument("--seed", type=int, default=2024)
-    ap.add_argument("--vec", type=int, default=16)
+    ap.add_argument("--vec", type=int, default=0)
     ap.add_argument("--ctas-per-sm", type=int, default=0)
     ap.add_argument("--host-ctas", type=int, default=0)
     ap.add_argument("--remote-ctas", type=int, default=0)

@@ -401,11 +401,11 @@ struct Replica {
   uint64_t lookups = 0;
   int gather_grid = 0;
   int host_ctas = 0, remote_ctas = 0;
-  int vec_bytes = 16;
+  int vec_bytes = 32;
   int block_threads = 256;
   int bulk_mask = 0;
   int lookup_kpt = 1;
-  int pdl = 1;  // bit 0: lookup kernel, bit 1: gather kernel launched with programmatic serialization
+  int pdl = 3;  // bit 0: lookup kernel, bit 1: gather kernel launched with programmatic serialization
   // per-kernel profiling (three events per lookup)
   std::vector<cudaEvent_t> prof_events;
   size_t prof_used = 0;
@@ -833,11 +833,14 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
   cudaDeviceProp prop;
   UGC_CUDA(cudaGetDeviceProperties(&prop, device_id));
   r->sm_count = prop.multiProcessorCount;
-  const int per_sm = c->cfg.gather_ctas_per_sm > 0 ? c->cfg.gather_ctas_per_sm : 4;
+  const int per_sm = c->cfg.gather_ctas_per_sm > 0 ? c->cfg.gather_ctas_per_sm : 8;
   r->gather_grid = r->sm_count * per_sm;
   r->host_ctas = c->cfg.host_ctas > 0 ? c->cfg.host_ctas : std::max(2, r->sm_count);
   r->remote_ctas = c->cfg.remote_ctas > 0 ? c->cfg.remote_ctas : std::max(2, r->sm_count * per_sm / 2);
-  r->vec_bytes = c->cfg.gather_vec_bytes == 32 ? 32 : 16;
+  // 32-byte loads win when almost every row comes from HBM (4+ GPUs cover the key space well:
+  // 36.5 vs 45 us per step on 8 GPUs); with many host rows per batch (1-2 GPUs) 16-byte loads
+  // were faster (113 vs 133 us on 1 GPU, 84 vs 110 us on 2).
+  r->vec_bytes = c->cfg.gather_vec_bytes ? (c->cfg.gather_vec_bytes == 32 ? 32 : 16) : (G >= 4 ? 32 : 16);
 
   // 1. which source serves each key (ascending key lists per GPU source)
   classify_keys(c->cur, replica_id, N, r->keys_by_src, r->counts);

@@ -526,6 +526,13 @@ __global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
       bool ok = copy_rows_bulk(ix, cnt[g], (uint32_t)(b - first) * warps_per_cta + warp,
                                (uint32_t)num * warps_per_cta, stage, bars);
       if (!ok && (threadIdx.x & 31) == 0) atomicAdd(&p.counters->err_table, 1ull);
+    } else if (VEC == 32 && g == kGroupHost) {
+      // host rows always move as 16-byte vectors, 4 rows in flight per lane group: 32-byte
+      // loads from pinned host memory were slower on every machine measured
+      constexpr int kHostLpr = LPR * 2 > 32 ? 32 : LPR * 2;
+      const uint32_t wpc = blockDim.x / kHostLpr;
+      copy_rows<16, kHostLpr, 4, true>(ix, cnt[g], (uint32_t)(b - first) * wpc + threadIdx.x / kHostLpr,
+                                       (uint32_t)num * wpc, threadIdx.x % kHostLpr, p.row_bytes / 16);
     } else {
       const uint32_t worker = (uint32_t)(b - first) * workers_per_cta + worker_in_cta;
       const uint32_t n_workers = (uint32_t)num * workers_per_cta;
