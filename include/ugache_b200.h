@@ -76,7 +76,7 @@ typedef struct {
   int32_t host_ctas;          /* CTA budget of the host-row group; 0 = default          */
   int32_t remote_ctas;        /* CTA budget of the peer-row group; 0 = default          */
   int32_t gather_vec_bytes;   /* 16 or 32 bytes per lane per load in the gather (host rows
-                                 always use 16); 0 = 32 with 4+ GPUs, else 16           */
+                                 always use 16); 0 = 32 with 8 GPUs, else 16            */
   ugc_alloc_fn alloc;
   ugc_free_fn free;
   void* alloc_user;

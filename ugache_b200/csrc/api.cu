@@ -837,10 +837,10 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
   r->gather_grid = r->sm_count * per_sm;
   r->host_ctas = c->cfg.host_ctas > 0 ? c->cfg.host_ctas : std::max(2, r->sm_count);
   r->remote_ctas = c->cfg.remote_ctas > 0 ? c->cfg.remote_ctas : std::max(2, r->sm_count * per_sm / 2);
-  // 32-byte loads win when almost every row comes from HBM (4+ GPUs cover the key space well:
-  // 36.5 vs 45 us per step on 8 GPUs); with many host rows per batch (1-2 GPUs) 16-byte loads
-  // were faster (113 vs 133 us on 1 GPU, 84 vs 110 us on 2).
-  r->vec_bytes = c->cfg.gather_vec_bytes ? (c->cfg.gather_vec_bytes == 32 ? 32 : 16) : (G >= 4 ? 32 : 16);
+  // 32-byte loads win when almost every row comes from HBM (8 GPUs, 458 host rows per batch:
+  // 36.5 us per step against 45); with more host rows per batch 16-byte loads were faster
+  // (1 GPU: 113 vs 133 us, 2 GPUs: 84 vs 110 us, 4 GPUs: 54 vs 61 us).
+  r->vec_bytes = c->cfg.gather_vec_bytes ? (c->cfg.gather_vec_bytes == 32 ? 32 : 16) : (G >= 8 ? 32 : 16);
 
   // 1. which source serves each key (ascending key lists per GPU source)
   classify_keys(c->cur, replica_id, N, r->keys_by_src, r->counts);
