@@ -111,13 +111,21 @@ WORKER = textwrap.dedent("""
 """)
 
 
-def test_collcache_processes_with_ipc(built_lib, tmp_path):
+@pytest.mark.parametrize("route", ["pidfd", "socket", "cuda_ipc"])
+def test_collcache_processes_with_ipc(built_lib, tmp_path, route):
     """One process per replica (both on GPU 0 when only one GPU is visible): peer slices and
-    peer tables are reached through CUDA IPC handles."""
+    peer tables are mapped from another process -- as exported virtual-memory blocks whose
+    descriptor is duplicated out of the owner (pidfd), or served over the descriptor socket,
+    or through cudaIpc handles of cudaMalloc memory."""
     script = tmp_path / "worker.py"
     script.write_text(WORKER % {"root": ROOT})
     G = 2
-    env = dict(os.environ, UGC_SESSION="pytest_ipc_%d" % os.getpid(), UGC_BARRIER_TIMEOUT_S="120")
+    env = dict(os.environ, UGC_SESSION="pytest_ipc_%s_%d" % (route, os.getpid()),
+               UGC_BARRIER_TIMEOUT_S="120")
+    if route == "socket":
+        env["UGC_NO_PIDFD"] = "1"
+    if route == "cuda_ipc":
+        env["UGC_NO_VMM"] = "1"
     procs = [subprocess.Popen([sys.executable, str(script), str(r), str(G)], env=env,
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
              for r in range(G)]
@@ -131,5 +139,5 @@ def test_collcache_processes_with_ipc(built_lib, tmp_path):
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, "replica %d failed:\n%s" % (r, o[-3000:])
     for name in os.listdir("/dev/shm"):
-        if name.startswith("ugc_%d_pytest_ipc_%d" % (os.getuid(), os.getpid())):
+        if name.startswith("ugc_%d_pytest_ipc_%s_%d" % (os.getuid(), route, os.getpid())):
             os.unlink(os.path.join("/dev/shm", name))

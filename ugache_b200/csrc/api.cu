@@ -4,18 +4,24 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <sys/prctl.h>
+#include <sys/socket.h>
+#include <sys/un.h>
 #include <sys/syscall.h>
 #include <unistd.h>
 
 #include <algorithm>
+#include <cerrno>
 #include <cstdarg>
+#include <cstddef>
 #include <cstdio>
 #include <cstring>
 #include <deque>
 #include <map>
 #include <mutex>
 #include <new>
+#include <set>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/ugache_b200.h"
@@ -310,19 +316,116 @@ int dev_block_export_fd(void* p) {
   return it->second.fd;
 }
 
-// Duplicates descriptor `fd` of process `pid` into this process (pidfd_open + pidfd_getfd).
+// ---- handing exported descriptors to other processes ----------------------------------------
+// First choice: the importer duplicates the descriptor straight out of the owner
+// (pidfd_open + pidfd_getfd).  Where the kernel's ptrace policy forbids that, the owner serves
+// its exported descriptors over an abstract-namespace Unix socket (SCM_RIGHTS).
+std::set<int> g_served_fds;
+bool g_fd_server_running = false;
+
+void fd_socket_name(int64_t pid, sockaddr_un* addr, socklen_t* len) {
+  memset(addr, 0, sizeof(*addr));
+  addr->sun_family = AF_UNIX;
+  int n = snprintf(addr->sun_path + 1, sizeof(addr->sun_path) - 1, "ugc_fd_%lld", (long long)pid);
+  *len = (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + n);
+}
+
+void fd_server_loop(int listen_fd) {
+  for (;;) {
+    int c = accept(listen_fd, nullptr, nullptr);
+    if (c < 0) {
+      if (errno == EINTR) continue;
+      return;
+    }
+    int wanted = -1;
+    if (read(c, &wanted, sizeof(wanted)) == (ssize_t)sizeof(wanted)) {
+      bool ok;
+      {
+        std::lock_guard<std::mutex> lock(g_vmm_mu);
+        ok = g_served_fds.count(wanted) != 0;
+      }
+      char byte = ok ? 1 : 0;
+      msghdr msg;
+      memset(&msg, 0, sizeof(msg));
+      iovec iov = {&byte, 1};
+      msg.msg_iov = &iov;
+      msg.msg_iovlen = 1;
+      char ctrl[CMSG_SPACE(sizeof(int))];
+      if (ok) {
+        memset(ctrl, 0, sizeof(ctrl));
+        msg.msg_control = ctrl;
+        msg.msg_controllen = sizeof(ctrl);
+        cmsghdr* cm = CMSG_FIRSTHDR(&msg);
+        cm->cmsg_level = SOL_SOCKET;
+        cm->cmsg_type = SCM_RIGHTS;
+        cm->cmsg_len = CMSG_LEN(sizeof(int));
+        memcpy(CMSG_DATA(cm), &wanted, sizeof(int));
+      }
+      sendmsg(c, &msg, 0);
+    }
+    close(c);
+  }
+}
+
+// Called by the owner when it exports descriptor `fd`.
+void fd_server_publish(int fd) {
+  std::lock_guard<std::mutex> lock(g_vmm_mu);
+  g_served_fds.insert(fd);
+  if (g_fd_server_running) return;
+  int s = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+  if (s < 0) return;
+  sockaddr_un addr;
+  socklen_t len;
+  fd_socket_name((int64_t)getpid(), &addr, &len);
+  if (bind(s, reinterpret_cast<sockaddr*>(&addr), len) != 0 || listen(s, 16) != 0) {
+    close(s);
+    return;
+  }
+  g_fd_server_running = true;
+  std::thread(fd_server_loop, s).detach();
+}
+
+int fd_from_socket(int64_t pid, int fd) {
+  int s = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+  if (s < 0) return -1;
+  sockaddr_un addr;
+  socklen_t len;
+  fd_socket_name(pid, &addr, &len);
+  int got = -1;
+  if (connect(s, reinterpret_cast<sockaddr*>(&addr), len) == 0 &&
+      write(s, &fd, sizeof(fd)) == (ssize_t)sizeof(fd)) {
+    char byte = 0;
+    msghdr msg;
+    memset(&msg, 0, sizeof(msg));
+    iovec iov = {&byte, 1};
+    msg.msg_iov = &iov;
+    msg.msg_iovlen = 1;
+    char ctrl[CMSG_SPACE(sizeof(int))];
+    memset(ctrl, 0, sizeof(ctrl));
+    msg.msg_control = ctrl;
+    msg.msg_controllen = sizeof(ctrl);
+    if (recvmsg(s, &msg, 0) == 1 && byte == 1) {
+      cmsghdr* cm = CMSG_FIRSTHDR(&msg);
+      if (cm && cm->cmsg_level == SOL_SOCKET && cm->cmsg_type == SCM_RIGHTS) memcpy(&got, CMSG_DATA(cm), sizeof(int));
+    }
+  }
+  close(s);
+  return got;
+}
+
+// A duplicate, in this process, of descriptor `fd` of process `pid`.
 int steal_fd(int64_t pid, int fd) {
+  if (!getenv("UGC_NO_PIDFD")) {
 #if defined(SYS_pidfd_open) && defined(SYS_pidfd_getfd)
-  int pidfd = (int)syscall(SYS_pidfd_open, (pid_t)pid, 0);
-  if (pidfd < 0) return -1;
-  int local = (int)syscall(SYS_pidfd_getfd, pidfd, fd, 0);
-  close(pidfd);
-  return local;
-#else
-  (void)pid;
-  (void)fd;
-  return -1;
+    int pidfd = (int)syscall(SYS_pidfd_open, (pid_t)pid, 0);
+    if (pidfd >= 0) {
+      int local = (int)syscall(SYS_pidfd_getfd, pidfd, fd, 0);
+      close(pidfd);
+      if (local >= 0) return local;
+    }
 #endif
+  }
+  return fd_from_socket(pid, fd);
 }
 
 // Maps another process' exported block for `device`.
@@ -931,8 +1034,11 @@ int ugc_export(ugc_ctx* c, int replica_id, ugc_peer_handle* out) {
   if (!c->cfg.alloc && dev_block_find(r->slice, &sb) && dev_block_find(r->table_mem, &tb)) {
     const int sfd = dev_block_export_fd(r->slice), tfd = dev_block_export_fd(r->table_mem);
     if (sfd >= 0 && tfd >= 0) {
-      // other processes of this user may duplicate the two descriptors out of this process
+      // other processes of this user may duplicate the two descriptors out of this process,
+      // or ask for them over the descriptor socket
       prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0);
+      fd_server_publish(sfd);
+      fd_server_publish(tfd);
       out->has_ipc = 2;
       int64_t v[2] = {sfd, (int64_t)sb.size};
       memcpy(out->slice_ipc, v, sizeof(v));
