@@ -321,3 +321,81 @@ def test_device_hotness_recording_drives_a_refresh(built_lib):
     assert before.tobytes() == after.tobytes() == orc.gather(table, keys).tobytes()
     assert cache.stats(0)["last_host"] < host_before / 2      # the recorded hot set is cached now
     cache.close()
+
+
+def test_full_batch_size_against_regenerated_rows(built_lib):
+    """The benchmark's batch size (212,992 keys, 512-byte rows) over a table too large to hold
+    twice: the table is written by the GPU generator into library-owned pinned memory and the
+    expected rows are regenerated key by key by the oracle's counter-based generator.  Also:
+    a second lookup of the same keys gives the same bytes (idempotence) and rows past the
+    batch stay untouched."""
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim, B = 8_000_000, 128, 8192 * 26
+    seed = 1234
+    hptr, dptr = rt.host_alloc(N * dim * 4)
+    try:
+        s = torch.cuda.current_stream().cuda_stream
+        rt.gen_table(dptr, seed, 0, N, dim, 4, s)
+        torch.cuda.synchronize()
+        ids, freqs = wl.analytic_hotness(N, 1.2)
+        for G, kind in ((1, 0), (4, 2)):
+            ndev = torch.cuda.device_count()
+            cache = rt.Cache(G, N, dim * 4, 0.10, max_batch=B, table_kind=kind, register_host=False)
+            cache.set_placement(rt.solve_placement("intuitive", G, ids, freqs, 10.0))
+            for r in range(G):
+                cache.build(r, r % ndev, hptr)
+            cache.connect_local()
+            for r in range(G):
+                cache.attach_peers(r)
+            r = G - 1
+            dev = torch.device("cuda", r % ndev)
+            keys = wl.zipf_keys(77 + G, B, N, 1.2)
+            want = orc.gen_rows_for_keys(seed, keys, dim).view(np.uint8).reshape(B, dim * 4)
+            with torch.cuda.device(dev):
+                k = torch.from_numpy(keys).to(dev)
+                out = torch.full((B + 64, dim * 4), 0x5A, dtype=torch.uint8, device=dev)
+                cache.lookup(r, k, out=out)
+                torch.cuda.synchronize(dev)
+                first = out.cpu().numpy()
+                cache.lookup(r, k, out=out)
+                torch.cuda.synchronize(dev)
+                second = out.cpu().numpy()
+            assert first[:B].tobytes() == want.tobytes()
+            assert second.tobytes() == first.tobytes()
+            assert (first[B:] == 0x5A).all()
+            st = cache.stats(r)
+            assert st["last_local"] + st["last_remote"] + st["last_host"] == B
+            assert st["err_table"] == 0 and st["err_key_range"] == 0
+            cache.close()
+    finally:
+        rt.host_free(hptr)
+
+
+def test_probing_table_churn(built_lib):
+    """Evict / re-insert cycles on the probing table (tombstones, slot reuse, chains that cross
+    lines): after every refresh the word of every key equals the model's source, every stored
+    row has its own slot, and lookups stay exact."""
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim = 20000, 8
+    table = wl.table(8, N, dim)
+    rng = np.random.default_rng(11)
+    cache = rt.Cache(1, N, dim * 4, 0.30, max_batch=1 << 13, table_kind=2)
+    order = rng.permutation(N).astype(np.uint32)
+    cache.set_placement(rt.solve_placement("rep", 1, order, None, 30.0))
+    host = pinned_table(table)
+    cache.build(0, 0, host.data_ptr())
+    allk = torch.arange(N, dtype=torch.int32, device="cuda")
+    for round_ in range(8):
+        order = np.roll(order, int(rng.integers(500, 5000)))
+        p = rt.solve_placement("rep", 1, order, None, 30.0)
+        cache.refresh_all_local(p, [0])
+        words = cache.table_words(0, allk).cpu().numpy().view(np.uint32)
+        stored = p.nid_to_block == 0
+        assert np.array_equal(words != 0xFFFFFFFF, stored), round_
+        slots = words[stored] & 0x0FFFFFFF
+        assert len(np.unique(slots)) == stored.sum()
+        keys = rng.integers(0, N, 5000).astype(np.int64)
+        assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
+        st = cache.stats(0)
+        assert st["err_table"] == 0 and st["free_rows"] == st["capacity_rows"] - stored.sum()
+    cache.close()

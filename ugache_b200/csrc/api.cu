@@ -494,11 +494,19 @@ struct Replica {
   DevBuf stage_a, stage_b;
   // bookkeeping mirrored from the reference's CacheEntryManager
   // (coll_cache_lib/cuda/cache_hashtable.cuh:548-557): keys per source, free slots
-  std::vector<uint32_t> keys_by_src[kMaxDevice];
   std::deque<uint32_t> free_slots;
-  // refresh in flight
-  std::vector<uint32_t> next_keys_by_src[kMaxDevice];
-  std::vector<uint32_t> pending_insert;
+  uint64_t n_local = 0;                    // rows stored here
+  uint64_t n_remote = 0;                   // keys read from peers
+  // Device-resident placement view of this reader and the key lists of the last
+  // classification (build: one list per source; refresh: evict / insert / drop / attach).
+  uint32_t* n2b_dev = nullptr;             // nid_to_block of the current placement
+  uint32_t* n2b_next = nullptr;            // same for the placement a refresh is moving to
+  DevBuf acc_dev;                          // [old row | new row] of block_access_from
+  DevBuf class_scratch;
+  DevBuf lists;                            // all lists back to back
+  uint64_t list_count[kMaxClassLists] = {0};
+  uint64_t list_base[kMaxClassLists] = {0};
+  uint64_t next_n_local = 0;
   bool refresh_open = false;
   uint64_t counts[kMaxLocation] = {0};
   uint64_t lookups = 0;
@@ -678,6 +686,63 @@ int alloc_table(ugc_ctx* c, Replica* r, uint64_t entries, uint64_t reserve, cuda
   return UGC_OK;
 }
 
+// Classifies the whole id space on the GPU (replaces the host OpenMP passes of the reference,
+// coll_cache_lib/cuda/cache_hashtable.cuh:693-835).  `old_p` == nullptr: build lists (one per
+// GPU source).  Otherwise the refresh lists.  Leaves counts / bases in the replica and the
+// keys in r->lists; returns after the stream is idle.
+int gpu_classify(ugc_ctx* c, Replica* r, const Placement* old_p, const Placement& new_p,
+                 const uint32_t* n2b_old_dev, const uint32_t* n2b_new_dev, cudaStream_t s) {
+  const uint64_t N = c->cfg.num_total_item;
+  const int G = c->cfg.num_device;
+  const size_t row_old = old_p ? (size_t)old_p->num_block : 0, row_new = (size_t)new_p.num_block;
+  UGC_TRY(ensure(c, r->acc_dev, row_old + row_new + 16));
+  uint8_t* acc = static_cast<uint8_t*>(r->acc_dev.ptr);
+  if (old_p)
+    UGC_CUDA(cudaMemcpyAsync(acc, &old_p->block_access_from[(size_t)r->id * row_old], row_old,
+                             cudaMemcpyHostToDevice, s));
+  UGC_CUDA(cudaMemcpyAsync(acc + row_old, &new_p.block_access_from[(size_t)r->id * row_new], row_new,
+                           cudaMemcpyHostToDevice, s));
+  ClassifyParams p;
+  memset(&p, 0, sizeof(p));
+  p.n2b_old = old_p ? n2b_old_dev : nullptr;
+  p.n2b_new = n2b_new_dev;
+  p.acc_old = acc;
+  p.acc_new = acc + row_old;
+  p.num_keys = N;
+  p.me = (uint32_t)r->id;
+  p.num_device = (uint32_t)G;
+  p.num_lists = old_p ? kListAttach0 + G : G;
+  UGC_TRY(ensure(c, r->class_scratch, classify_scratch_bytes(N)));
+  UGC_CUDA(launch_classify_count(p, r->class_scratch.ptr, s));
+  unsigned long long totals[kMaxClassLists];
+  UGC_CUDA(cudaMemcpyAsync(totals, classify_totals(r->class_scratch.ptr, N), sizeof(totals),
+                           cudaMemcpyDeviceToHost, s));
+  UGC_CUDA(cudaStreamSynchronize(s));
+  uint64_t sum = 0;
+  for (int l = 0; l < kMaxClassLists; l++) {
+    r->list_count[l] = l < p.num_lists ? totals[l] : 0;
+    r->list_base[l] = sum;
+    p.list_base[l] = sum;
+    sum += r->list_count[l];
+  }
+  UGC_TRY(ensure(c, r->lists, std::max<uint64_t>(sum, 1) * sizeof(uint32_t)));
+  UGC_CUDA(launch_classify_scatter(p, r->class_scratch.ptr, static_cast<uint32_t*>(r->lists.ptr), s));
+  UGC_CUDA(cudaStreamSynchronize(s));
+  return UGC_OK;
+}
+
+uint32_t* list_ptr(Replica* r, int l) { return static_cast<uint32_t*>(r->lists.ptr) + r->list_base[l]; }
+
+int upload_n2b(ugc_ctx* c, const Placement& p, uint32_t** dst, cudaStream_t s) {
+  const size_t bytes = (size_t)c->cfg.num_total_item * sizeof(uint32_t);
+  if (!*dst) {
+    *dst = static_cast<uint32_t*>(ctx_alloc(c, bytes));
+    if (!*dst) return fail(UGC_ERR_NOMEM, "placement copy (%zu bytes) could not be allocated", bytes);
+  }
+  UGC_CUDA(cudaMemcpyAsync(*dst, p.nid_to_block.data(), bytes, cudaMemcpyHostToDevice, s));
+  return UGC_OK;
+}
+
 void release_replica(ugc_ctx* c, Replica* r) {
   if (r->device >= 0) cudaSetDevice(r->device);
   for (cudaEvent_t e : r->prof_events) cudaEventDestroy(e);
@@ -688,6 +753,11 @@ void release_replica(ugc_ctx* c, Replica* r) {
   for (auto& l : r->list) ctx_free(c, l);
   ctx_free(c, r->counters);
   ctx_free(c, r->hot_counts);
+  ctx_free(c, r->n2b_dev);
+  ctx_free(c, r->n2b_next);
+  ctx_free(c, r->acc_dev.ptr);
+  ctx_free(c, r->class_scratch.ptr);
+  ctx_free(c, r->lists.ptr);
   ctx_free(c, r->stage_keys.ptr);
   ctx_free(c, r->stage_out.ptr);
   ctx_free(c, r->stage_a.ptr);
@@ -717,11 +787,8 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
   if (!keys || !out) return fail(UGC_ERR_INVALID, "keys and out must be non-null");
   if (n > r->max_batch)
     return fail(UGC_ERR_INVALID, "batch of %zu keys exceeds max_batch %u", n, r->max_batch);
-  if (c->cfg.num_device > 1 && !r->attached) {
-    for (int s2 = 0; s2 < c->cfg.num_device; s2++)
-      if (s2 != r->id && !r->keys_by_src[s2].empty())
-        return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
-  }
+  if (c->cfg.num_device > 1 && !r->attached)
+    return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
   const bool prof = r->prof_on && r->prof_used + 3 <= r->prof_events.size();
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used], s));
   UGC_CUDA(launch_lookup_group(keys, key_bytes, (uint32_t)n, r->table, (uint32_t)r->id,
@@ -945,12 +1012,23 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
   // (1 GPU: 113 vs 133 us, 2 GPUs: 84 vs 110 us, 4 GPUs: 54 vs 61 us).
   r->vec_bytes = c->cfg.gather_vec_bytes ? (c->cfg.gather_vec_bytes == 32 ? 32 : 16) : (G >= 8 ? 32 : 16);
 
-  // 1. which source serves each key (ascending key lists per GPU source)
-  classify_keys(c->cur, replica_id, N, r->keys_by_src, r->counts);
-  const uint64_t n_local = r->keys_by_src[replica_id].size();
+  // 1. which source serves each key: ascending key lists per GPU source, made on the GPU
+  {
+    int rc0 = upload_n2b(c, c->cur, &r->n2b_dev, s);
+    if (rc0 == UGC_OK) rc0 = gpu_classify(c, r, nullptr, c->cur, nullptr, r->n2b_dev, s);
+    if (rc0 != UGC_OK) {
+      std::string keep = g_last_error;
+      release_replica(c, r);
+      g_last_error = keep;
+      return rc0;
+    }
+  }
+  const uint64_t n_local = r->list_count[replica_id];
   uint64_t n_remote = 0;
   for (int s2 = 0; s2 < G; s2++)
-    if (s2 != replica_id) n_remote += r->keys_by_src[s2].size();
+    if (s2 != replica_id) n_remote += r->list_count[s2];
+  r->n_local = n_local;
+  r->n_remote = n_remote;
 
   // 2. the slice
   r->capacity = cache_capacity_rows(N, c->cfg.cache_percentage);
@@ -986,9 +1064,7 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
     return bail(fail(UGC_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(cudaGetLastError())));
 
   // 4. fill: slice[j] = host[local_keys[j]]
-  if ((rc = upload_u32(c, r->stage_a, r->keys_by_src[replica_id].data(), n_local, s)) != UGC_OK)
-    return bail(rc);
-  if (launch_fill_scatter(c->host_dev, r->slice, static_cast<uint32_t*>(r->stage_a.ptr), nullptr, 0,
+  if (launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, replica_id), nullptr, 0,
                           (uint32_t)n_local, c->cfg.row_bytes, c->cfg.empty_feat, r->sm_count * 2,
                           s) != cudaSuccess)
     return bail(fail(UGC_ERR_CUDA, "fill launch failed: %s", cudaGetErrorString(cudaGetLastError())));
@@ -1000,7 +1076,7 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
   const uint64_t max_entries = std::min<uint64_t>(N, (uint64_t)G * r->capacity);
   if ((rc = alloc_table(c, r, n_local + n_remote, std::max(n_local + n_remote, max_entries), s)) != UGC_OK)
     return bail(rc);
-  if (launch_table_insert(r->table, static_cast<uint32_t*>(r->stage_a.ptr), nullptr, 0,
+  if (launch_table_insert(r->table, list_ptr(r, replica_id), nullptr, 0,
                           (uint32_t)replica_id, (uint32_t)n_local, r->counters, s) != cudaSuccess)
     return bail(fail(UGC_ERR_CUDA, "insert launch failed: %s", cudaGetErrorString(cudaGetLastError())));
   if ((rc = check_table_errors(r, s, "build insert")) != UGC_OK) return bail(rc);
@@ -1012,6 +1088,10 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
   r->src_base[replica_id] = r->slice;
   r->src_base[G] = c->host_dev;
   r->attached = (n_remote == 0);
+  if (r->attached) {  // no peer lists to resolve later: the build lists can go now
+    ctx_free(c, r->lists.ptr);
+    r->lists = DevBuf{};
+  }
   r->built = true;
   return UGC_OK;
 }
@@ -1161,33 +1241,35 @@ int ugc_connect_local(ugc_ctx* c) {
 }
 
 // Resolve the slots of `keys` (all served by `src`) from src's table and insert them.
-static int attach_keys(ugc_ctx* c, Replica* r, int src, const std::vector<uint32_t>& keys,
-                       cudaStream_t s) {
-  if (keys.empty()) return UGC_OK;
+// Resolve the slots of `n` device-resident keys (all served by `src`) from src's table and
+// insert them into this replica's table.
+static int attach_keys(ugc_ctx* c, Replica* r, int src, const uint32_t* keys_dev, uint64_t n, cudaStream_t s) {
+  if (n == 0) return UGC_OK;
   if (!r->peer_known[src] || !r->src_base[src])
     return fail(UGC_ERR_STATE, "replica %d reads from replica %d, which has not been imported", r->id, src);
-  UGC_TRY(upload_u32(c, r->stage_a, keys.data(), keys.size(), s));
-  UGC_TRY(ensure(c, r->stage_b, keys.size() * sizeof(uint32_t)));
-  UGC_CUDA(launch_table_resolve(r->peer_table[src], static_cast<uint32_t*>(r->stage_a.ptr),
-                                (uint32_t)keys.size(), (uint32_t)src,
+  UGC_TRY(ensure(c, r->stage_b, n * sizeof(uint32_t)));
+  UGC_CUDA(launch_table_resolve(r->peer_table[src], keys_dev, (uint32_t)n, (uint32_t)src,
                                 static_cast<uint32_t*>(r->stage_b.ptr), r->counters, s));
-  UGC_CUDA(launch_table_insert(r->table, static_cast<uint32_t*>(r->stage_a.ptr),
-                               static_cast<uint32_t*>(r->stage_b.ptr), 0, (uint32_t)src,
-                               (uint32_t)keys.size(), r->counters, s));
-  // the staging buffers are reused by the next source
+  UGC_CUDA(launch_table_insert(r->table, keys_dev, static_cast<uint32_t*>(r->stage_b.ptr), 0, (uint32_t)src,
+                               (uint32_t)n, r->counters, s));
+  // the offset buffer is reused by the next source
   return check_table_errors(r, s, "peer attach");
 }
 
 int ugc_attach_peers(ugc_ctx* c, int replica_id, void* stream) {
   Replica* r;
   UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (r->attached) return UGC_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   UGC_CUDA(cudaSetDevice(r->device));
   for (int src = 0; src < c->cfg.num_device; src++) {
     if (src == replica_id) continue;
-    UGC_TRY(attach_keys(c, r, src, r->keys_by_src[src], s));
+    UGC_TRY(attach_keys(c, r, src, list_ptr(r, src), r->list_count[src], s));
   }
   r->attached = true;
+  // the build lists are not needed any more
+  ctx_free(c, r->lists.ptr);
+  r->lists = DevBuf{};
   return UGC_OK;
 }
 
@@ -1302,57 +1384,46 @@ int ugc_refresh_evict(ugc_ctx* c, int replica_id, void* stream) {
   const int G = c->cfg.num_device;
   const int me = replica_id;
   UGC_CUDA(cudaSetDevice(r->device));
-  const Placement& old_p = c->cur;
-  const Placement& new_p = c->next;
 
-  // step 1: sources under the new placement
-  uint64_t counts[kMaxLocation];
-  for (auto& v : r->next_keys_by_src) v.clear();
-  classify_keys(new_p, me, c->cfg.num_total_item, r->next_keys_by_src, counts);
-  const uint64_t n_new_local = r->next_keys_by_src[me].size();
+  // steps 1-4 of the reference's refresh in one pass over the id space on the GPU: keys whose
+  // source changed, as ascending lists (evict here / bring in here / drop a peer entry /
+  // point to a peer)
+  UGC_TRY(upload_n2b(c, c->next, &r->n2b_next, s));
+  UGC_TRY(gpu_classify(c, r, &c->cur, c->next, r->n2b_dev, r->n2b_next, s));
+  const uint64_t n_evict = r->list_count[kListEvict], n_insert = r->list_count[kListInsert];
+  const uint64_t n_drop = r->list_count[kListDropRemote];
+  const uint64_t n_new_local = r->n_local - n_evict + n_insert;
   if (n_new_local > r->capacity)
     return fail(UGC_ERR_CAPACITY, "new placement stores %llu rows on replica %d, slice holds %llu",
                 (unsigned long long)n_new_local, me, (unsigned long long)r->capacity);
-  uint64_t n_new_entries = n_new_local;
+  uint64_t n_attach = 0;
   for (int s2 = 0; s2 < G; s2++)
-    if (s2 != me) n_new_entries += r->next_keys_by_src[s2].size();
+    if (s2 != me) n_attach += r->list_count[kListAttach0 + s2];
+  const uint64_t n_new_entries = r->n_local + r->n_remote - n_evict - n_drop + n_insert + n_attach;
   if (r->table.kind == kTableHashed && n_new_entries > r->table_entry_cap)
     return fail(UGC_ERR_CAPACITY, "new placement needs %llu table entries, table is sized for %llu",
                 (unsigned long long)n_new_entries, (unsigned long long)r->table_entry_cap);
+  if (n_insert > r->free_slots.size() + n_evict)
+    return fail(UGC_ERR_CAPACITY, "refresh needs %llu free slots, %llu available",
+                (unsigned long long)n_insert, (unsigned long long)(r->free_slots.size() + n_evict));
 
-  // step 2: rows to bring in = stored here now, not before
-  r->pending_insert = select_keys(r->next_keys_by_src[me], [&](uint32_t k) { return !old_p.stored_on(me, k); });
-  // step 3: rows to drop = stored here before, not now; their slots return to the free list
-  std::vector<uint32_t> evict = select_keys(r->keys_by_src[me], [&](uint32_t k) { return !new_p.stored_on(me, k); });
-  if (!evict.empty()) {
-    UGC_TRY(upload_u32(c, r->stage_a, evict.data(), evict.size(), s));
-    UGC_TRY(ensure(c, r->stage_b, evict.size() * sizeof(uint32_t)));
-    UGC_CUDA(launch_table_resolve(r->table, static_cast<uint32_t*>(r->stage_a.ptr), (uint32_t)evict.size(),
-                                  (uint32_t)me, static_cast<uint32_t*>(r->stage_b.ptr), r->counters, s));
-    std::vector<uint32_t> slots(evict.size());
-    UGC_CUDA(cudaMemcpyAsync(slots.data(), r->stage_b.ptr, evict.size() * sizeof(uint32_t),
-                             cudaMemcpyDeviceToHost, s));
-    UGC_CUDA(launch_table_evict(r->table, static_cast<uint32_t*>(r->stage_a.ptr), (uint32_t)evict.size(),
-                                r->counters, s));
+  // step 3: evicted rows give their slots back (appended to the free list), then leave the table
+  if (n_evict) {
+    UGC_TRY(ensure(c, r->stage_b, n_evict * sizeof(uint32_t)));
+    UGC_CUDA(launch_table_resolve(r->table, list_ptr(r, kListEvict), (uint32_t)n_evict, (uint32_t)me,
+                                  static_cast<uint32_t*>(r->stage_b.ptr), r->counters, s));
+    std::vector<uint32_t> slots(n_evict);
+    UGC_CUDA(cudaMemcpyAsync(slots.data(), r->stage_b.ptr, n_evict * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    UGC_CUDA(launch_table_evict(r->table, list_ptr(r, kListEvict), (uint32_t)n_evict, r->counters, s));
     UGC_TRY(check_table_errors(r, s, "refresh evict"));
     for (uint32_t o : slots) r->free_slots.push_back(o);
   }
-  if (r->pending_insert.size() > r->free_slots.size())
-    return fail(UGC_ERR_CAPACITY, "refresh needs %zu free slots, %zu available", r->pending_insert.size(),
-                r->free_slots.size());
   // step 4: remote entries whose source changed (coll_cache_lib/cache_context.cu:3103-3136)
-  std::vector<uint32_t> drop_remote;
-  for (int src = 0; src < G; src++) {
-    if (src == me) continue;
-    for (uint32_t k : r->keys_by_src[src])
-      if (new_p.access(me, new_p.nid_to_block[k]) != src) drop_remote.push_back(k);
-  }
-  if (!drop_remote.empty()) {
-    UGC_TRY(upload_u32(c, r->stage_a, drop_remote.data(), drop_remote.size(), s));
-    UGC_CUDA(launch_table_evict(r->table, static_cast<uint32_t*>(r->stage_a.ptr),
-                                (uint32_t)drop_remote.size(), r->counters, s));
+  if (n_drop) {
+    UGC_CUDA(launch_table_evict(r->table, list_ptr(r, kListDropRemote), (uint32_t)n_drop, r->counters, s));
     UGC_TRY(check_table_errors(r, s, "refresh evict remote"));
   }
+  r->next_n_local = n_new_local;
   r->refresh_open = true;
   return UGC_OK;
 }
@@ -1363,7 +1434,7 @@ int ugc_refresh_fill(ugc_ctx* c, int replica_id, void* stream) {
   if (!r->refresh_open) return fail(UGC_ERR_STATE, "call ugc_refresh_evict first");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   UGC_CUDA(cudaSetDevice(r->device));
-  const size_t n = r->pending_insert.size();
+  const size_t n = (size_t)r->list_count[kListInsert];
   if (n) {
     // new rows take slots from the FRONT of the free list
     // (coll_cache_lib/cuda/cache_hashtable.cuh:637-645)
@@ -1372,16 +1443,14 @@ int ugc_refresh_fill(ugc_ctx* c, int replica_id, void* stream) {
       slots[i] = r->free_slots.front();
       r->free_slots.pop_front();
     }
-    UGC_TRY(upload_u32(c, r->stage_a, r->pending_insert.data(), n, s));
     UGC_TRY(upload_u32(c, r->stage_b, slots.data(), n, s));
     // A small grid keeps the refill from taking bandwidth from running lookups
     // (the reference limits it to 20 blocks, coll_cache_lib/cache_context.cu:4067).
-    UGC_CUDA(launch_fill_scatter(c->host_dev, r->slice, static_cast<uint32_t*>(r->stage_a.ptr),
+    UGC_CUDA(launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, kListInsert),
                                  static_cast<uint32_t*>(r->stage_b.ptr), 0, (uint32_t)n,
                                  c->cfg.row_bytes, c->cfg.empty_feat, 20, s));
-    UGC_CUDA(launch_table_insert(r->table, static_cast<uint32_t*>(r->stage_a.ptr),
-                                 static_cast<uint32_t*>(r->stage_b.ptr), 0, (uint32_t)replica_id,
-                                 (uint32_t)n, r->counters, s));
+    UGC_CUDA(launch_table_insert(r->table, list_ptr(r, kListInsert), static_cast<uint32_t*>(r->stage_b.ptr), 0,
+                                 (uint32_t)replica_id, (uint32_t)n, r->counters, s));
     UGC_TRY(check_table_errors(r, s, "refresh insert"));
   }
   return UGC_OK;
@@ -1394,16 +1463,20 @@ int ugc_refresh_attach(ugc_ctx* c, int replica_id, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   UGC_CUDA(cudaSetDevice(r->device));
   const int G = c->cfg.num_device;
-  const Placement& old_p = c->cur;
   for (int src = 0; src < G; src++) {
     if (src == replica_id) continue;
-    std::vector<uint32_t> fresh = select_keys(r->next_keys_by_src[src], [&](uint32_t k) {
-      return old_p.access(replica_id, old_p.nid_to_block[k]) != src;
-    });
-    UGC_TRY(attach_keys(c, r, src, fresh, s));
+    UGC_TRY(attach_keys(c, r, src, list_ptr(r, kListAttach0 + src), r->list_count[kListAttach0 + src], s));
   }
-  for (int src = 0; src < G; src++) r->keys_by_src[src] = std::move(r->next_keys_by_src[src]);
-  r->pending_insert.clear();
+  uint64_t attach_total = 0;
+  for (int src = 0; src < G; src++)
+    if (src != replica_id) attach_total += r->list_count[kListAttach0 + src];
+  r->n_remote = r->n_remote - r->list_count[kListDropRemote] + attach_total;
+  r->n_local = r->next_n_local;
+  std::swap(r->n2b_dev, r->n2b_next);
+  ctx_free(c, r->n2b_next);
+  r->n2b_next = nullptr;
+  ctx_free(c, r->lists.ptr);
+  r->lists = DevBuf{};
   r->refresh_open = false;
   return UGC_OK;
 }
@@ -1464,9 +1537,8 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   UGC_TRY(read_counters(r, &h));
   memset(out, 0, sizeof(*out));
   const int G = c->cfg.num_device;
-  out->num_local_rows = r->keys_by_src[replica_id].size();
-  for (int s = 0; s < G; s++)
-    if (s != replica_id) out->num_remote_keys += r->keys_by_src[s].size();
+  out->num_local_rows = r->n_local;
+  out->num_remote_keys = r->n_remote;
   out->num_host_keys = c->cfg.num_total_item - out->num_local_rows - out->num_remote_keys;
   out->capacity_rows = r->capacity;
   out->free_rows = r->free_slots.size();

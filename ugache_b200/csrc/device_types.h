@@ -82,4 +82,24 @@ struct GatherParams {
   int bulk_mask;        // bit 0: host rows, bit 1: peer rows go through bulk-async staging
 };
 
+// Classification of the whole id space into ascending key lists.
+//  build   (n2b_old == nullptr): list s = keys this reader fetches from GPU s, s in [0, G)
+//  refresh (n2b_old != nullptr): kListEvict  = stored here before, not now
+//                                kListInsert = stored here now, not before
+//                                kListDropRemote = read from a peer before, source changed
+//                                kListAttach0+s  = read from peer s now, not before
+constexpr int kListEvict = 0, kListInsert = 1, kListDropRemote = 2, kListAttach0 = 3;
+constexpr int kMaxClassLists = kListAttach0 + kMaxDevice;  // 11
+struct ClassifyParams {
+  const uint32_t* n2b_old;   // device, N entries, or nullptr
+  const uint32_t* n2b_new;   // device, N entries
+  const uint8_t* acc_old;    // device: this reader's source per block (old placement)
+  const uint8_t* acc_new;    // device: same for the new placement
+  uint64_t num_keys;
+  uint32_t me;
+  uint32_t num_device;
+  int num_lists;
+  uint64_t list_base[kMaxClassLists];  // start of each list in the output buffer (scatter pass)
+};
+
 }  // namespace ugc

@@ -680,6 +680,135 @@ __global__ void __launch_bounds__(kBlock)
 }
 
 // ------------------------------------------------------------------------------------
+// key classification over the whole id space (build and refresh), ordered compaction
+// ------------------------------------------------------------------------------------
+// For every key the placement gives the source that serves this reader.  Build wants one
+// ascending key list per GPU source; a refresh wants the ascending lists of keys whose
+// source changed (evict here, bring in here, drop a peer entry, point to a peer).  Three
+// passes over tiles of kClassTile keys: per-tile counts, a scan over tiles, a stable scatter.
+constexpr int kClassTile = 2048;
+constexpr int kClassRounds = kClassTile / kBlock;
+
+// Bit mask of the lists key k belongs to (see ClassifyParams in device_types.h).
+__device__ __forceinline__ uint32_t class_mask(const ClassifyParams& p, uint64_t k) {
+  const uint32_t src_new = p.acc_new[p.n2b_new[k]];
+  if (p.n2b_old == nullptr) return src_new < p.num_device ? (1u << src_new) : 0u;  // build
+  const uint32_t src_old = p.acc_old[p.n2b_old[k]];
+  if (src_old == src_new) return 0u;
+  uint32_t m = 0;
+  if (src_old == p.me) m |= 1u << kListEvict;
+  if (src_new == p.me) m |= 1u << kListInsert;
+  if (src_old < p.num_device && src_old != p.me) m |= 1u << kListDropRemote;
+  if (src_new < p.num_device && src_new != p.me) m |= 1u << (kListAttach0 + src_new);
+  return m;
+}
+
+__global__ void __launch_bounds__(kBlock) classify_count_kernel(ClassifyParams p, uint32_t* tile_counts) {
+  __shared__ uint32_t s_cnt[kMaxClassLists];
+  if (threadIdx.x < kMaxClassLists) s_cnt[threadIdx.x] = 0;
+  __syncthreads();
+  const uint64_t base = (uint64_t)blockIdx.x * kClassTile;
+  uint32_t masks[kClassRounds];
+#pragma unroll
+  for (int j = 0; j < kClassRounds; j++) {
+    uint64_t k = base + (uint64_t)j * kBlock + threadIdx.x;
+    masks[j] = k < p.num_keys ? class_mask(p, k) : 0u;
+  }
+  for (int l = 0; l < p.num_lists; l++) {
+    uint32_t c = 0;
+#pragma unroll
+    for (int j = 0; j < kClassRounds; j++) c += (masks[j] >> l) & 1u;
+    c = __reduce_add_sync(kFull, c);
+    if ((threadIdx.x & 31) == 0 && c) atomicAdd(&s_cnt[l], c);
+  }
+  __syncthreads();
+  if (threadIdx.x < kMaxClassLists)
+    tile_counts[(size_t)threadIdx.x * gridDim.x + blockIdx.x] = s_cnt[threadIdx.x];
+}
+
+// One CTA per list: exclusive scan of that list's per-tile counts, total to totals[list].
+__global__ void __launch_bounds__(1024) classify_scan_kernel(uint32_t* tile_counts, uint32_t n_tiles,
+                                                             unsigned long long* totals) {
+  __shared__ uint32_t s_warp[32];
+  __shared__ uint32_t s_carry;
+  uint32_t* row = tile_counts + (size_t)blockIdx.x * n_tiles;
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  unsigned long long total = 0;
+  for (uint32_t start = 0; start < n_tiles; start += 1024) {
+    const uint32_t i = start + threadIdx.x;
+    const uint32_t v = i < n_tiles ? row[i] : 0;
+    uint32_t x = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t y = __shfl_up_sync(kFull, x, d);
+      if (lane >= (uint32_t)d) x += y;
+    }
+    if (lane == 31) s_warp[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t w = s_warp[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        uint32_t y = __shfl_up_sync(kFull, w, d);
+        if (lane >= (uint32_t)d) w += y;
+      }
+      s_warp[lane] = w;  // inclusive over warps
+    }
+    __syncthreads();
+    const uint32_t carry = s_carry;
+    const uint32_t before = carry + (warp ? s_warp[warp - 1] : 0) + x - v;  // exclusive prefix
+    if (i < n_tiles) row[i] = before;
+    __syncthreads();
+    if (threadIdx.x == 1023) {
+      s_carry = carry + s_warp[31];
+    }
+    __syncthreads();
+    total = s_carry;
+  }
+  // per-tile offsets are 32-bit: a list holds fewer than 2^32 keys (the id space is < 2^31)
+  if (threadIdx.x == 0) totals[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(kBlock)
+    classify_scatter_kernel(ClassifyParams p, const uint32_t* __restrict__ tile_offsets,
+                            uint32_t* __restrict__ out) {
+  __shared__ uint32_t s_warp_cnt[kWarpsPerBlock][kMaxClassLists];
+  __shared__ uint32_t s_running[kMaxClassLists];
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < kMaxClassLists)
+    s_running[threadIdx.x] = tile_offsets[(size_t)threadIdx.x * gridDim.x + blockIdx.x];
+  __syncthreads();
+  const uint64_t base = (uint64_t)blockIdx.x * kClassTile;
+  for (int j = 0; j < kClassRounds; j++) {
+    const uint64_t k = base + (uint64_t)j * kBlock + threadIdx.x;
+    const uint32_t m = k < p.num_keys ? class_mask(p, k) : 0u;
+    uint32_t rank[kMaxClassLists];
+    for (int l = 0; l < p.num_lists; l++) {
+      const unsigned b = __ballot_sync(kFull, (m >> l) & 1u);
+      rank[l] = __popc(b & ((1u << lane) - 1));
+      if (lane == 0) s_warp_cnt[warp][l] = __popc(b);
+    }
+    __syncthreads();
+    for (int l = 0; l < p.num_lists; l++) {
+      if ((m >> l) & 1u) {
+        uint32_t pos = s_running[l] + rank[l];
+        for (uint32_t w = 0; w < warp; w++) pos += s_warp_cnt[w][l];
+        out[p.list_base[l] + pos] = (uint32_t)k;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < (uint32_t)p.num_lists) {
+      uint32_t add = 0;
+      for (int w = 0; w < kWarpsPerBlock; w++) add += s_warp_cnt[w][threadIdx.x];
+      s_running[threadIdx.x] += add;
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // hotness recording: per-key access counts of a batch, kept on the device
 // ------------------------------------------------------------------------------------
 template <typename KeyT>
@@ -910,6 +1039,35 @@ cudaError_t launch_table_resolve(const TableView& peer, const uint32_t* keys, ui
                                  cudaStream_t stream) {
   if (n == 0) return cudaSuccess;
   table_resolve_kernel<<<grid_for(n), kBlock, 0, stream>>>(peer, keys, n, expect_loc, offs, counters);
+  return cudaGetLastError();
+}
+
+size_t classify_scratch_bytes(uint64_t num_keys) {
+  const size_t n_tiles = (size_t)((num_keys + kClassTile - 1) / kClassTile);
+  return n_tiles * kMaxClassLists * sizeof(uint32_t) + kMaxClassLists * sizeof(unsigned long long) + 256;
+}
+
+// scratch layout: tile counts [kMaxClassLists][n_tiles] u32, then totals [kMaxClassLists] u64
+cudaError_t launch_classify_count(const ClassifyParams& p, void* scratch, cudaStream_t stream) {
+  const uint32_t n_tiles = (uint32_t)((p.num_keys + kClassTile - 1) / kClassTile);
+  uint32_t* tile_counts = static_cast<uint32_t*>(scratch);
+  size_t off = ((size_t)n_tiles * kMaxClassLists * sizeof(uint32_t) + 255) / 256 * 256;
+  unsigned long long* totals = reinterpret_cast<unsigned long long*>(static_cast<char*>(scratch) + off);
+  classify_count_kernel<<<n_tiles, kBlock, 0, stream>>>(p, tile_counts);
+  classify_scan_kernel<<<kMaxClassLists, 1024, 0, stream>>>(tile_counts, n_tiles, totals);
+  return cudaGetLastError();
+}
+
+const unsigned long long* classify_totals(void* scratch, uint64_t num_keys) {
+  const size_t n_tiles = (size_t)((num_keys + kClassTile - 1) / kClassTile);
+  size_t off = (n_tiles * kMaxClassLists * sizeof(uint32_t) + 255) / 256 * 256;
+  return reinterpret_cast<const unsigned long long*>(static_cast<char*>(scratch) + off);
+}
+
+cudaError_t launch_classify_scatter(const ClassifyParams& p, const void* scratch, uint32_t* out,
+                                    cudaStream_t stream) {
+  const uint32_t n_tiles = (uint32_t)((p.num_keys + kClassTile - 1) / kClassTile);
+  classify_scatter_kernel<<<n_tiles, kBlock, 0, stream>>>(p, static_cast<const uint32_t*>(scratch), out);
   return cudaGetLastError();
 }
 

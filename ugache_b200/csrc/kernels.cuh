@@ -46,6 +46,16 @@ cudaError_t launch_table_resolve(const TableView& peer, const uint32_t* keys, ui
                                  uint32_t expect_loc, uint32_t* offs, Counters* counters,
                                  cudaStream_t stream);
 
+// Whole-id-space classification into ascending key lists (see ClassifyParams).  Pass 1+2
+// (launch_classify_count) leave per-tile offsets and per-list totals in `scratch`
+// (classify_scratch_bytes(N) bytes); after reading the totals (classify_totals) the caller
+// fills p.list_base and runs the scatter pass into `out`.
+size_t classify_scratch_bytes(uint64_t num_keys);
+cudaError_t launch_classify_count(const ClassifyParams& p, void* scratch, cudaStream_t stream);
+const unsigned long long* classify_totals(void* scratch, uint64_t num_keys);
+cudaError_t launch_classify_scatter(const ClassifyParams& p, const void* scratch, uint32_t* out,
+                                    cudaStream_t stream);
+
 // counts[key] += 1 for every key of the batch (keys outside [0, num_keys) are ignored)
 cudaError_t launch_record(const void* keys, int key_bytes, uint32_t n, uint32_t* counts,
                           uint64_t num_keys, cudaStream_t stream);
