@@ -52,16 +52,6 @@ std::string solve_placement(int policy, int num_device, uint64_t num_total_item,
 void classify_keys(const Placement& p, int reader, uint64_t num_total_item,
                    std::vector<uint32_t> keys_by_src[], uint64_t* counts);
 
-// Keys of `input` for which pred(key) holds, order preserved
-// (replaces DetectKeysWithCond, coll_cache_lib/cuda/cache_hashtable.cuh:693-740).
-template <typename Pred>
-std::vector<uint32_t> select_keys(const std::vector<uint32_t>& input, Pred pred) {
-  std::vector<uint32_t> out;
-  for (uint32_t k : input)
-    if (pred(k)) out.push_back(k);
-  return out;
-}
-
 // Rule of the reference for choosing the direct-index table over the probing one
 // (coll_cache_lib/cache_context.cu:2489-2497 with cuda/cache_hashtable.cu:222-225).
 bool reference_prefers_flat_table(uint64_t cached_plus_remote, uint64_t num_total_item);
