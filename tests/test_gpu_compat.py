@@ -141,3 +141,21 @@ def test_collcache_processes_with_ipc(built_lib, tmp_path, route):
     for name in os.listdir("/dev/shm"):
         if name.startswith("ugc_%d_pytest_ipc_%s_%d" % (os.getuid(), route, os.getpid())):
             os.unlink(os.path.join("/dev/shm", name))
+
+
+def test_cpp_facade_program(built_lib, tmp_path):
+    """A C++ program written against coll_cache_lib::CollCache (the reference's facade
+    signatures) builds against include/coll_cache_lib/facade.h, links the library, and gets
+    exact rows before and after a refresh."""
+    import shutil
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    exe = tmp_path / "facade_demo"
+    libdir = os.path.dirname(built_lib)
+    cmd = [nvcc, "-std=c++17", "-O1", "-I", os.path.join(ROOT, "include"),
+           os.path.join(ROOT, "tests", "cpp", "facade_demo.cc"), "-o", str(exe),
+           "-L" + libdir, "-lugache_b200", "-Xlinker", "-rpath=" + libdir, "-Xcompiler", "-pthread",
+           "-Wno-deprecated-gpu-targets"]
+    c = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert c.returncode == 0, c.stderr
+    p = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "facade ok" in p.stdout, p.stdout + p.stderr
