@@ -10,8 +10,12 @@
  * for this path, and it has no CPU extraction routine.  The integer helpers below
  * (murmur3 hash, packed location/offset word, table sizing) ARE pinned: they are checked
  * against values printed by the reference's own headers compiled in place (see
- * ref_pin.cu and tests/golden/ref_pin.json).  The rest (gather, placement heuristics,
- * slot bookkeeping) is pinned only by reading: "parity unpinned" by reference tests.
+ * ref_pin.cu and tests/golden/ref_pin.json).  The probing table and the direct-index table
+ * (insert, evict, re-insert, lookup with the host fallback) ARE pinned too: against the
+ * words the reference's own SimpleHashTable / FlatHashTable kernels returned on a B200
+ * (ref_pin.cu --gpu; tests/golden/ref_tables.npz, tests/test_gpu_refpin.py).  The rest
+ * (gather, placement heuristics, slot bookkeeping) is pinned only by reading: "parity
+ * unpinned" by reference tests.
  *
  * Every function cites the reference file:line it follows (paths relative to the
  * reference project root).

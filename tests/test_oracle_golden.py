@@ -128,3 +128,20 @@ def test_empty_and_ragged_gather():
         k = np.arange(n, dtype=np.int64) * 3 % 100
         assert (orc.gather(t, k) == t[k]).all()
     assert (orc.gather(t, np.array([5, 69]), empty_feat=6) == t[[5, 5]]).all()
+
+
+def test_oracle_tables_match_reference_gpu_kernels():
+    """tests/golden/ref_tables.npz holds what the reference's own SimpleHashTable and
+    FlatHashTable kernels returned on a B200 (tests/golden/make_ref_tables.py): insert per
+    location, evict, re-insert, then a lookup of every id with its EmbedVal helper."""
+    import os
+    from tests.helpers import oracle_table_words, ref_table_scenario
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_tables.npz"))
+    N, fb = int(z["N"]), int(z["fallback"])
+    sc = ref_table_scenario(int(z["seed"]), N, int(z["n_ins"]), int(z["n_ev"]), int(z["n_re"]))
+    simple, flat = oracle_table_words(orc, N, fb, sc)
+    assert np.array_equal(simple, z["simple"])
+    assert np.array_equal(flat, z["flat"])
+    # the fixture is not trivial: hits at three locations, evicted ids and misses all occur
+    loc = z["simple"] >> 28
+    assert {0, 1, 2, fb} <= set(np.unique(loc).tolist())
