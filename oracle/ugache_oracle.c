@@ -7,15 +7,20 @@
  * only the test-suite, the smoke check and the CPU-baseline leg of the benchmark do.
  *
  * Parity status: the reference holds no tests, golden vectors or known-answer fixtures
- * for this path, and it has no CPU extraction routine.  The integer helpers below
- * (murmur3 hash, packed location/offset word, table sizing) ARE pinned: they are checked
- * against values printed by the reference's own headers compiled in place (see
- * ref_pin.cu and tests/golden/ref_pin.json).  The probing table and the direct-index table
- * (insert, evict, re-insert, lookup with the host fallback) ARE pinned too: against the
- * words the reference's own SimpleHashTable / FlatHashTable kernels returned on a B200
- * (ref_pin.cu --gpu; tests/golden/ref_tables.npz, tests/test_gpu_refpin.py).  The rest
- * (gather, placement heuristics, slot bookkeeping) is pinned only by reading: "parity
- * unpinned" by reference tests.
+ * for this path, and it has no CPU extraction routine.  The oracle is pinned against the
+ * reference's OWN code instead, compiled in place from the reference tree into oracle/_ref/:
+ *   - integer helpers (murmur3 hash, packed location/offset word, table sizing): values
+ *     printed by the reference's headers (ref_pin.cu, tests/golden/ref_pin.json);
+ *   - both key tables (insert, evict, re-insert, lookup with the host fallback): the words the
+ *     reference's SimpleHashTable / FlatHashTable kernels returned on a B200 (ref_pin.cu --gpu,
+ *     tests/golden/ref_tables.npz, tests/test_gpu_refpin.py);
+ *   - lookup records, grouping, group boundaries, the per-location row copy, the build fill and
+ *     the refresh scatter: the reference's LookupHelper, radix-sort dispatcher, find_boundary
+ *     and extract_data device code run on a B200 (ref_extract_pin.cu,
+ *     tests/golden/ref_extract.json, tests/test_gpu_refpin.py).
+ * Still pinned only by reading ("parity unpinned"): the placement heuristics (the reference's
+ * solver file does not compile without the commercial solver's headers) and the host-side
+ * slot bookkeeping of a refresh.
  *
  * Every function cites the reference file:line it follows (paths relative to the
  * reference project root).

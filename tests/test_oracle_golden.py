@@ -145,3 +145,25 @@ def test_oracle_tables_match_reference_gpu_kernels():
     # the fixture is not trivial: hits at three locations, evicted ids and misses all occur
     loc = z["simple"] >> 28
     assert {0, 1, 2, fb} <= set(np.unique(loc).tolist())
+
+
+def test_oracle_extraction_matches_reference_gpu_kernels():
+    """tests/golden/ref_extract.json: digests of what the reference's own lookup-helper, sort,
+    boundary and extract_data kernels produced on a B200 for REF_EXTRACT_CASES
+    (tests/golden/make_ref_extract.py)."""
+    import json
+    import os
+    from tests.helpers import REF_EXTRACT_CASES, ref_extract_case
+    with open(os.path.join(os.path.dirname(__file__), "golden", "ref_extract.json")) as f:
+        gold = json.load(f)
+    from tests.helpers import REF_FILL_CASES, ref_fill_case
+    assert set(gold) == {c["name"] for c in REF_EXTRACT_CASES} | {"fill_" + c["name"] for c in REF_FILL_CASES}
+    for case in REF_FILL_CASES:
+        _, want = ref_fill_case(orc, case)
+        assert digest(want) == gold["fill_" + case["name"]]["slice"], case["name"]
+    for case in REF_EXTRACT_CASES:
+        _, want = ref_extract_case(orc, oracle_solver, case)
+        g = gold[case["name"]]
+        assert [int(x) for x in want["groups"]] == g["groups"], case["name"]
+        assert digest(want["records"]) == g["records"], case["name"]
+        assert digest(want["out"]) == g["out"], case["name"]
