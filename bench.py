@@ -12,6 +12,7 @@ Data are synthetic (seeded generators of ugache_b200.workload).
     python bench.py --gpus 1 --steps 100 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference ...     # the CPU restatement on the box's host cores
+    python bench.py --impl reference-gpu ... # extra: the reference's own device code, one GPU
 
 Prints ONE JSON line on rank 0.
 """
@@ -40,7 +41,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--rows", type=int, default=100_000_000)
     ap.add_argument("--dim", type=int, default=128)
     ap.add_argument("--dtype", default="float32", choices=["float32", "float16"])
@@ -334,6 +335,68 @@ def run_reference(a):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------
+def run_reference_gpu(a):
+    """Extra arm (one GPU): the reference's OWN device code — table lookup with its record
+    helper, radix-sort grouping, boundary kernel, extract_data row copy per source — compiled in
+    place for this GPU into oracle/_ref/ref_extract_pin and sequenced as its extraction session
+    does, timed on the same table shape, cache share and key batches as our arm.  Its host
+    threads, sleeps and SM partitioning are left out, so this is the reference's best case."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    import subprocess
+    import tempfile
+    binary = os.path.join(ROOT, "oracle", "_ref", "ref_extract_pin")
+    base = {"impl": "reference-gpu", "metric": "extracted_embedding_throughput", "unit": "GB/s",
+            "n_gpus": 1, "steps": a.steps, "warmup": a.warmup}
+    if not os.path.exists(binary) or a.workload != "dlr" or a.empty_feat:
+        base["unavailable"] = "oracle/_ref/ref_extract_pin not built (needs the reference tree)" \
+            if not os.path.exists(binary) else "only the plain dlr workload is wired to this arm"
+        print(json.dumps(base), flush=True)
+        return
+    from ugache_b200 import build as ubuild
+    ubuild.build()
+    from ugache_b200 import runtime as rt, workload as wl
+    elem = 4 if a.dtype == "float32" else 2
+    row_bytes = a.dim * elem
+    ids, freqs = wl.analytic_hotness(a.rows, a.alpha)
+    placement = rt.solve_placement(a.policy, 1, ids, freqs, a.cache_pct * 100.0)
+    del ids, freqs
+    src = np.asarray(placement.block_access_from).reshape(1, -1)[0][placement.nid_to_block]
+    cached = np.nonzero(src == 0)[0].astype(np.uint32)
+    total = a.warmup + a.steps
+    keys = make_keys(a, 0, total).astype(np.uint32)
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "time.bin"), "wb") as f:
+            np.array([a.rows, cached.size, a.batch, a.steps, a.warmup, row_bytes],
+                     dtype=np.uint32).tofile(f)
+            cached.tofile(f)
+            keys.tofile(f)
+        env = dict(os.environ, USER=os.environ.get("USER", "root"))
+        p = subprocess.run([binary, "--time", d], env=env, capture_output=True, text=True)
+    if p.returncode != 0:
+        base["unavailable"] = "pin binary failed: " + (p.stdout + p.stderr)[-300:].replace("\n", " ")
+        print(json.dumps(base), flush=True)
+        return
+    r = json.loads(p.stdout.strip().splitlines()[-1])
+    us = r["device_us"]
+    base.update({
+        "value": a.batch * row_bytes / us / 1e3, "ms_per_step": us / 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": workload_name(a), "rows": a.rows, "dim": a.dim,
+                   "keys_per_step": a.batch, "alpha": a.alpha, "cached_rows": int(cached.size),
+                   "note": "reference device code compiled for sm_100a; device-timed per "
+                           "synchronous lookup; no SM partitioning, host threads or sleeps"},
+        "mkeys_per_s": a.batch / us,
+        "index_us": r["index_us"], "wall_us": r["wall_us"],
+        "local_rows": r["local_rows"], "host_rows": r["host_rows"],
+        "e2e": {"value": a.batch * row_bytes / r["wall_us"] / 1e3, "unit": "GB/s",
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    })
+    print(json.dumps(base), flush=True)
 
 
 # ---------------------------------------------------------------------------------------
@@ -738,6 +801,8 @@ def main():
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.impl == "reference-gpu":
+        run_reference_gpu(a)
     else:
         run_ours(a)
 

@@ -35,10 +35,27 @@
  * Input  <dir>/fill.bin : u32 header {N, n_build, row_bytes, slice_rows, n_scatter}, build keys,
  *        scatter keys, scatter destinations, then the host table (N x row_bytes bytes).
  * Output <dir>/slice.bin (slice_rows x row_bytes; rows nothing wrote stay zero).
+ *
+ * With "--time <dir>" it TIMES the same device code on a one-GPU cache (local slice + host
+ * table), as the baseline a recompiled reference would give on this GPU:
+ *   per lookup: records (+ sync), radix sort (+ sync), find_boundary (+ sync, host fix-up), then
+ *   the host group and the local group copied by extract_data on two streams, then both synced
+ *   - the order and the synchronisations of ExtractSession::GetMissCacheIndex / SplitGroup /
+ *   ExtractFeat (cache_context.cu:702-761, :825-847, :1330-1440).  Left out, all in the
+ *   reference's favour: its per-source host threads and their semaphore hand-off, the 60 us
+ *   sleep, and the SM-mask / MPS partitioning of the copy kernels (the mask interface addresses
+ *   the SM count of older GPUs only).  Device memory comes from a size-keyed pool, standing in
+ *   for the caching allocator of the framework the reference runs under.
+ * Input  <dir>/time.bin : u32 header {N, n_cached, n_keys, n_steps, warmup, row_bytes}, the
+ *        cached keys in slot order, then (warmup + n_steps) key batches of n_keys u32 each.
+ *        Host row r is filled with the 32-bit value r, so the output can be checked from the keys.
+ * Output one JSON line on stdout.
  */
 #include "coll_cache_lib/cache_context.cu"
 
+#include <chrono>
 #include <cstdio>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -56,10 +73,21 @@ using namespace coll_cache_lib::common;
 
 namespace {
 
+// freed blocks are kept by size and handed out again (time mode only)
+bool g_pool_blocks = false;
+std::multimap<size_t, void*> g_pool;
+
 class PinDeviceBlock : public ExternelGPUMemoryHandler {
  public:
-  explicit PinDeviceBlock(size_t n) : n_(n) { PIN_CUDA(cudaMalloc(&p_, n ? n : 1)); }
-  ~PinDeviceBlock() override { cudaFree(p_); }
+  explicit PinDeviceBlock(size_t n) : n_(n ? n : 1) {
+    auto it = g_pool.find(n_);
+    if (it != g_pool.end()) { p_ = it->second; g_pool.erase(it); return; }
+    PIN_CUDA(cudaMalloc(&p_, n_));
+  }
+  ~PinDeviceBlock() override {
+    if (g_pool_blocks) g_pool.emplace(n_, p_);
+    else cudaFree(p_);
+  }
   void* ptr() override { return p_; }
   size_t nbytes() override { return n_; }
 
@@ -155,9 +183,151 @@ static int fill_mode(const std::string& dir) {
   return 0;
 }
 
+static int time_mode(const std::string& dir) {
+  FILE* f = fopen((dir + "/time.bin").c_str(), "rb");
+  if (!f) { fprintf(stderr, "no time.bin in %s\n", dir.c_str()); return 3; }
+  auto hdr = read_u32(f, 6);
+  const uint32_t N = hdr[0], n_cached = hdr[1], n_keys = hdr[2], n_steps = hdr[3], warmup = hdr[4];
+  const uint32_t row_bytes = hdr[5];
+  auto cached = read_u32(f, n_cached);
+  auto batches = read_u32(f, (size_t)(n_steps + warmup) * n_keys);
+  fclose(f);
+  PIN_CUDA(cudaSetDevice(0));
+  RunConfig::option_empty_feat = 0;
+  g_pool_blocks = true;
+  Context gpu = GPU(0);
+  cudaStream_t s = nullptr, s_host = nullptr, s_local = nullptr;
+  PIN_CUDA(cudaStreamCreate(&s));
+  PIN_CUDA(cudaStreamCreate(&s_host));
+  PIN_CUDA(cudaStreamCreate(&s_local));
+  std::function<MemHandle(size_t)> alloc = [](size_t n) -> MemHandle {
+    return std::make_shared<PinDeviceBlock>(n);
+  };
+  const size_t words_per_row = row_bytes / 4;
+  uint32_t* host = nullptr;
+  PIN_CUDA(cudaHostAlloc(&host, (size_t)N * row_bytes, cudaHostAllocMapped));
+#pragma omp parallel for schedule(static)
+  for (long long r = 0; r < (long long)N; r++)
+    for (size_t w = 0; w < words_per_row; w++) host[(size_t)r * words_per_row + w] = (uint32_t)r;
+  DataType dtype = kF32;
+  IdType dim = row_bytes / 4;
+  if (row_bytes % 16 == 0) { dtype = kF64_2; dim = row_bytes / 16; }
+
+  // build: slice[j] = host[cached[j]], table entry cached[j] -> (location 0, j)
+  void* slice = nullptr;
+  PIN_CUDA(cudaMalloc(&slice, (size_t)n_cached * row_bytes + 16));
+  uint32_t* d_cached = to_dev(cached);
+  {
+    IdxStoreDirect<false> idx_store(d_cached);
+    DataIterPerLoc<decltype(idx_store)> it(idx_store, host, slice, dim);
+    Combine(it, n_cached, gpu, dtype, dim, s);
+  }
+  FlatHashTable table(alloc, (size_t)N, gpu, s);
+  {
+    std::vector<uint32_t> offs(n_cached);
+    for (uint32_t j = 0; j < n_cached; j++) offs[j] = j;
+    uint32_t* d_offs = to_dev(offs);
+    table.InsertUnique<HashTableInsertHelper::SingleLoc>(d_cached, HashTableInsertHelper::SingleLoc(d_offs, 0),
+                                                        n_cached, s);
+    PIN_CUDA(cudaStreamSynchronize(s));
+    cudaFree(d_offs);
+  }
+  uint32_t* d_batches = to_dev(batches);
+  void* out = nullptr;
+  PIN_CUDA(cudaMalloc(&out, (size_t)n_keys * row_bytes + 16));
+  const int host_loc = 1, n_loc = 2;
+  void* src[2] = {slice, host};
+  IdType* group_offset = nullptr;
+  PIN_CUDA(cudaHostAlloc(&group_offset, sizeof(IdType) * (n_loc + 1), cudaHostAllocMapped));
+  MemHandle idx_mem, alter_mem;
+  cudaEvent_t e0, e1, e_idx, e_host, e_local;
+  PIN_CUDA(cudaEventCreate(&e0));
+  PIN_CUDA(cudaEventCreate(&e1));
+  PIN_CUDA(cudaEventCreate(&e_idx));
+  PIN_CUDA(cudaEventCreateWithFlags(&e_host, cudaEventDisableTiming));
+  PIN_CUDA(cudaEventCreateWithFlags(&e_local, cudaEventDisableTiming));
+  double sum_dev = 0, sum_idx = 0, sum_wall = 0;
+  uint64_t n_host_rows = 0, n_local_rows = 0;
+  for (uint32_t step = 0; step < n_steps + warmup; step++) {
+    const uint32_t* d_keys = d_batches + (size_t)step * n_keys;
+    PIN_CUDA(cudaDeviceSynchronize());
+    auto w0 = std::chrono::steady_clock::now();
+    PIN_CUDA(cudaEventRecord(e0, s));
+    IdxStoreCompact idx, idx_alter;
+    if (idx_mem == nullptr || idx_mem->nbytes() < idx.required_mem(n_keys)) {
+      idx_mem = alloc(idx.required_mem(n_keys));
+      alter_mem = alloc(idx.required_mem(n_keys));
+    }
+    idx.prepare_mem(idx_mem->ptr<uint8_t>(), n_keys);
+    {
+      auto helper = HashTableLookupHelper::LookupHelper<false, IdxStoreCompact>(host_loc);
+      helper.idx_store = idx;
+      table.LookupValCustom(d_keys, n_keys, helper, s);
+      PIN_CUDA(cudaStreamSynchronize(s));
+    }
+    idx_alter.prepare_mem(alter_mem->ptr<uint8_t>(), n_keys);
+    common::cuda::CubSortDispatcher(idx.keys_for_sort(), idx_alter.keys_for_sort(), idx.vals_for_sort(),
+                                    idx_alter.vals_for_sort(), n_keys, gpu, alloc, false, s);
+    memset(group_offset, 0, sizeof(IdType) * (n_loc + 1));
+    PIN_CUDA(cudaStreamSynchronize(s));
+    group_offset[n_loc] = n_keys;
+    {
+      const dim3 grid(RoundUpDiv((size_t)n_keys, Constant::kCudaTileSize));
+      const dim3 block(Constant::kCudaBlockSize);
+      find_boundary<><<<grid, block, 0, s>>>(idx, n_keys, group_offset);
+      PIN_CUDA(cudaEventRecord(e_idx, s));
+      PIN_CUDA(cudaStreamSynchronize(s));
+      for (int i = 1; i < n_loc; i++)
+        if (group_offset[i + 1] == 0) group_offset[i + 1] = group_offset[i];
+    }
+    // host group first, then the local group, each on its own stream
+    PIN_CUDA(cudaStreamWaitEvent(s_host, e_idx, 0));
+    PIN_CUDA(cudaStreamWaitEvent(s_local, e_idx, 0));
+    for (int l = n_loc - 1; l >= 0; l--) {
+      const size_t cnt = group_offset[l + 1] - group_offset[l];
+      DataIterPerLoc<IdxStoreCompact> it(idx.sub_array(group_offset[l]), src[l], out, dim);
+      Combine(it, cnt, gpu, dtype, dim, l == host_loc ? s_host : s_local, 0, true);
+    }
+    PIN_CUDA(cudaEventRecord(e_host, s_host));
+    PIN_CUDA(cudaEventRecord(e_local, s_local));
+    PIN_CUDA(cudaStreamWaitEvent(s, e_host, 0));
+    PIN_CUDA(cudaStreamWaitEvent(s, e_local, 0));
+    PIN_CUDA(cudaEventRecord(e1, s));
+    PIN_CUDA(cudaStreamSynchronize(s_host));
+    PIN_CUDA(cudaStreamSynchronize(s_local));
+    PIN_CUDA(cudaStreamSynchronize(s));
+    auto w1 = std::chrono::steady_clock::now();
+    // the swap of the sort's double buffer moved the records: keep the handles in step
+    if (idx.src_dst_idx != (SrcKeyDstVal*)idx_mem->ptr()) std::swap(idx_mem, alter_mem);
+    if (step >= warmup) {
+      float ms = 0, ms_idx = 0;
+      PIN_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+      PIN_CUDA(cudaEventElapsedTime(&ms_idx, e0, e_idx));
+      sum_dev += ms * 1e3;
+      sum_idx += ms_idx * 1e3;
+      sum_wall += std::chrono::duration<double, std::micro>(w1 - w0).count();
+      n_local_rows += group_offset[1];
+      n_host_rows += group_offset[2] - group_offset[1];
+    }
+  }
+  // check the last batch: every word of output row i is the key of that row
+  std::vector<uint32_t> h_out((size_t)n_keys * words_per_row);
+  PIN_CUDA(cudaMemcpy(h_out.data(), out, h_out.size() * 4, cudaMemcpyDeviceToHost));
+  const uint32_t* last = batches.data() + (size_t)(n_steps + warmup - 1) * n_keys;
+  size_t bad = 0;
+  for (size_t i = 0; i < n_keys; i++)
+    for (size_t w = 0; w < words_per_row; w++) bad += h_out[i * words_per_row + w] != last[i];
+  printf("{\"steps\": %u, \"keys\": %u, \"row_bytes\": %u, \"device_us\": %.2f, \"index_us\": %.2f, "
+         "\"wall_us\": %.2f, \"local_rows\": %.1f, \"host_rows\": %.1f, \"mismatched_words\": %zu}\n",
+         n_steps, n_keys, row_bytes, sum_dev / n_steps, sum_idx / n_steps, sum_wall / n_steps,
+         (double)n_local_rows / n_steps, (double)n_host_rows / n_steps, bad);
+  return bad ? 4 : 0;
+}
+
 int main(int argc, char** argv) {
-  if (argc < 2) { fprintf(stderr, "usage: %s [--fill] <dir>\n", argv[0]); return 1; }
+  if (argc < 2) { fprintf(stderr, "usage: %s [--fill|--time] <dir>\n", argv[0]); return 1; }
   if (argc >= 3 && std::string(argv[1]) == "--fill") return fill_mode(argv[2]);
+  if (argc >= 3 && std::string(argv[1]) == "--time") return time_mode(argv[2]);
   const std::string dir = argv[1];
   FILE* f = fopen((dir + "/extract.bin").c_str(), "rb");
   if (!f) { fprintf(stderr, "no extract.bin in %s\n", dir.c_str()); return 3; }

@@ -28,3 +28,12 @@ def test_reference_arm_other_ranks_stay_silent():
                         "--rows", "100000", "--batch", "1024", "--steps", "1", "--warmup", "0"],
                        capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert p.returncode == 0 and p.stdout.strip() == ""
+
+
+def test_reference_gpu_arm_reports_unavailable_without_a_gpu():
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference-gpu",
+                        "--rows", "20000", "--batch", "512", "--steps", "2", "--warmup", "1"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    line = json.loads(p.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference-gpu" and "unavailable" in line
