@@ -78,6 +78,9 @@ def parse_args():
     ap.add_argument("--variants", default="",
                     help="extra tuning variants timed after the main run on the same cache, e.g. "
                          "'programmatic_launch=3;host_ctas=32,remote_ctas=64'; reported under 'variants'")
+    ap.add_argument("--sorted-batches", action="store_true",
+                    help="ascending key order inside each batch (what a caller that deduplicates "
+                         "by sorting hands over); the default keeps the generator's random order")
     ap.add_argument("--sweep-out", default="", help="write extra per-phase numbers here (json)")
     return ap.parse_args()
 
@@ -279,6 +282,8 @@ def make_keys(a, rank, count):
     out = np.empty((count, a.batch), dtype=np.int64)
     for i in range(count):
         out[i] = wl.zipf_keys(a.seed * 1000003 + rank * 1009 + i, a.batch, a.rows, a.alpha)
+    if a.sorted_batches:
+        out.sort(axis=1)
     return out
 
 
@@ -352,9 +357,14 @@ def run_reference_gpu(a):
     binary = os.path.join(ROOT, "oracle", "_ref", "ref_extract_pin")
     base = {"impl": "reference-gpu", "metric": "extracted_embedding_throughput", "unit": "GB/s",
             "n_gpus": 1, "steps": a.steps, "warmup": a.warmup}
-    if not os.path.exists(binary) or a.workload != "dlr" or a.empty_feat:
-        base["unavailable"] = "oracle/_ref/ref_extract_pin not built (needs the reference tree)" \
-            if not os.path.exists(binary) else "only the plain dlr workload is wired to this arm"
+    host_rows = (1 << a.empty_feat) if a.empty_feat else a.rows
+    if not os.path.exists(binary) or a.workload != "dlr" or host_rows > (1 << 28):
+        base["unavailable"] = (
+            "oracle/_ref/ref_extract_pin not built (needs the reference tree)"
+            if not os.path.exists(binary) else
+            "only the dlr workload is wired to this arm" if a.workload != "dlr" else
+            "the reference packs a host row index into 28 bits: more than 2^28 host rows need "
+            "its mock host table (--empty-feat <= 28)")
         print(json.dumps(base), flush=True)
         return
     from ugache_b200 import build as ubuild
@@ -371,7 +381,7 @@ def run_reference_gpu(a):
     keys = make_keys(a, 0, total).astype(np.uint32)
     with tempfile.TemporaryDirectory() as d:
         with open(os.path.join(d, "time.bin"), "wb") as f:
-            np.array([a.rows, cached.size, a.batch, a.steps, a.warmup, row_bytes],
+            np.array([a.rows, cached.size, a.batch, a.steps, a.warmup, row_bytes, a.empty_feat],
                      dtype=np.uint32).tofile(f)
             cached.tofile(f)
             keys.tofile(f)
@@ -388,6 +398,7 @@ def run_reference_gpu(a):
         "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": workload_name(a), "rows": a.rows, "dim": a.dim,
                    "keys_per_step": a.batch, "alpha": a.alpha, "cached_rows": int(cached.size),
+                   "empty_feat": a.empty_feat,
                    "note": "reference device code compiled for sm_100a; device-timed per "
                            "synchronous lookup; no SM partitioning, host threads or sleeps"},
         "mkeys_per_s": a.batch / us,

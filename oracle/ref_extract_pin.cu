@@ -46,8 +46,11 @@
  *   sleep, and the SM-mask / MPS partitioning of the copy kernels (the mask interface addresses
  *   the SM count of older GPUs only).  Device memory comes from a size-keyed pool, standing in
  *   for the caching allocator of the framework the reference runs under.
- * Input  <dir>/time.bin : u32 header {N, n_cached, n_keys, n_steps, warmup, row_bytes}, the
+ * Input  <dir>/time.bin : u32 header {N, n_cached, n_keys, n_steps, warmup, row_bytes, k}, the
  *        cached keys in slot order, then (warmup + n_steps) key batches of n_keys u32 each.
+ *        k != 0 selects the reference's mock host table of 2^k rows (host row = key mod 2^k,
+ *        RunConfig::option_empty_feat); the reference packs a host row index into 28 bits, so
+ *        without it N may not exceed 2^28 and the program refuses such a case.
  *        Host row r is filled with the 32-bit value r, so the output can be checked from the keys.
  * Output one JSON line on stdout.
  */
@@ -96,6 +99,15 @@ class PinDeviceBlock : public ExternelGPUMemoryHandler {
   size_t n_;
 };
 
+// The reference packs (location, row index) into 4 + 28 bits (cuda/cache_hashtable.h:22-25): a
+// host row index of 2^28 or more would spill into the location bits and send find_boundary past
+// the end of the boundary array.  Such a case is refused before anything runs.
+bool offsets_overflow(unsigned long long host_rows) {
+  if (host_rows <= (1ull << 28)) return false;
+  fprintf(stderr, "refused: %llu host rows do not fit the reference's 28-bit row index\n", host_rows);
+  return true;
+}
+
 std::vector<uint32_t> read_u32(FILE* f, size_t n) {
   std::vector<uint32_t> v(n);
   if (n && fread(v.data(), 4, n, f) != n) { fprintf(stderr, "short read\n"); exit(3); }
@@ -143,6 +155,10 @@ static int fill_mode(const std::string& dir) {
   auto hdr = read_u32(f, 5);
   const uint32_t N = hdr[0], n_build = hdr[1], row_bytes = hdr[2], slice_rows = hdr[3], n_sc = hdr[4];
   auto bkeys = read_u32(f, n_build), skeys = read_u32(f, n_sc), sdst = read_u32(f, n_sc);
+  if (n_build > slice_rows) { fprintf(stderr, "build list longer than the slice\n"); return 5; }
+  for (uint32_t k : bkeys) if (k >= N) { fprintf(stderr, "build key out of range\n"); return 5; }
+  for (size_t i = 0; i < n_sc; i++)
+    if (skeys[i] >= N || sdst[i] >= slice_rows) { fprintf(stderr, "scatter %zu out of range\n", i); return 5; }
   PIN_CUDA(cudaSetDevice(0));
   RunConfig::option_empty_feat = 0;
   Context gpu = GPU(0);
@@ -186,14 +202,18 @@ static int fill_mode(const std::string& dir) {
 static int time_mode(const std::string& dir) {
   FILE* f = fopen((dir + "/time.bin").c_str(), "rb");
   if (!f) { fprintf(stderr, "no time.bin in %s\n", dir.c_str()); return 3; }
-  auto hdr = read_u32(f, 6);
+  auto hdr = read_u32(f, 7);
   const uint32_t N = hdr[0], n_cached = hdr[1], n_keys = hdr[2], n_steps = hdr[3], warmup = hdr[4];
-  const uint32_t row_bytes = hdr[5];
+  const uint32_t row_bytes = hdr[5], mock_bits = hdr[6];
+  if (offsets_overflow(mock_bits ? (1ull << mock_bits) : N) || mock_bits > 28) { fclose(f); return 5; }
+  const size_t host_rows = mock_bits ? ((size_t)1 << mock_bits) : N;
   auto cached = read_u32(f, n_cached);
   auto batches = read_u32(f, (size_t)(n_steps + warmup) * n_keys);
   fclose(f);
+  for (uint32_t k : cached) if (k >= N) { fprintf(stderr, "cached key out of range\n"); return 5; }
+  for (uint32_t k : batches) if (k >= N) { fprintf(stderr, "key out of range\n"); return 5; }
   PIN_CUDA(cudaSetDevice(0));
-  RunConfig::option_empty_feat = 0;
+  RunConfig::option_empty_feat = mock_bits;
   g_pool_blocks = true;
   Context gpu = GPU(0);
   cudaStream_t s = nullptr, s_host = nullptr, s_local = nullptr;
@@ -205,9 +225,9 @@ static int time_mode(const std::string& dir) {
   };
   const size_t words_per_row = row_bytes / 4;
   uint32_t* host = nullptr;
-  PIN_CUDA(cudaHostAlloc(&host, (size_t)N * row_bytes, cudaHostAllocMapped));
+  PIN_CUDA(cudaHostAlloc(&host, host_rows * row_bytes, cudaHostAllocMapped));
 #pragma omp parallel for schedule(static)
-  for (long long r = 0; r < (long long)N; r++)
+  for (long long r = 0; r < (long long)host_rows; r++)
     for (size_t w = 0; w < words_per_row; w++) host[(size_t)r * words_per_row + w] = (uint32_t)r;
   DataType dtype = kF32;
   IdType dim = row_bytes / 4;
@@ -217,7 +237,11 @@ static int time_mode(const std::string& dir) {
   void* slice = nullptr;
   PIN_CUDA(cudaMalloc(&slice, (size_t)n_cached * row_bytes + 16));
   uint32_t* d_cached = to_dev(cached);
-  {
+  if (mock_bits) {
+    IdxStoreDirect<true> idx_store(d_cached);
+    DataIterPerLoc<decltype(idx_store)> it(idx_store, host, slice, dim);
+    Combine(it, n_cached, gpu, dtype, dim, s);
+  } else {
     IdxStoreDirect<false> idx_store(d_cached);
     DataIterPerLoc<decltype(idx_store)> it(idx_store, host, slice, dim);
     Combine(it, n_cached, gpu, dtype, dim, s);
@@ -259,7 +283,12 @@ static int time_mode(const std::string& dir) {
       alter_mem = alloc(idx.required_mem(n_keys));
     }
     idx.prepare_mem(idx_mem->ptr<uint8_t>(), n_keys);
-    {
+    if (mock_bits) {
+      auto helper = HashTableLookupHelper::LookupHelper<true, IdxStoreCompact>(host_loc);
+      helper.idx_store = idx;
+      table.LookupValCustom(d_keys, n_keys, helper, s);
+      PIN_CUDA(cudaStreamSynchronize(s));
+    } else {
       auto helper = HashTableLookupHelper::LookupHelper<false, IdxStoreCompact>(host_loc);
       helper.idx_store = idx;
       table.LookupValCustom(d_keys, n_keys, helper, s);
@@ -316,7 +345,8 @@ static int time_mode(const std::string& dir) {
   const uint32_t* last = batches.data() + (size_t)(n_steps + warmup - 1) * n_keys;
   size_t bad = 0;
   for (size_t i = 0; i < n_keys; i++)
-    for (size_t w = 0; w < words_per_row; w++) bad += h_out[i * words_per_row + w] != last[i];
+    for (size_t w = 0; w < words_per_row; w++)
+      bad += h_out[i * words_per_row + w] != (mock_bits ? last[i] % (1u << mock_bits) : last[i]);
   printf("{\"steps\": %u, \"keys\": %u, \"row_bytes\": %u, \"device_us\": %.2f, \"index_us\": %.2f, "
          "\"wall_us\": %.2f, \"local_rows\": %.1f, \"host_rows\": %.1f, \"mismatched_words\": %zu}\n",
          n_steps, n_keys, row_bytes, sum_dev / n_steps, sum_idx / n_steps, sum_wall / n_steps,
@@ -334,10 +364,20 @@ int main(int argc, char** argv) {
   auto hdr = read_u32(f, 6);
   const uint32_t N = hdr[0], n_ent = hdr[1], n_keys = hdr[2], n_loc = hdr[3], row_bytes = hdr[4];
   const bool use_flat = hdr[5] != 0;
+  if (offsets_overflow(N) || n_loc > 9) { fclose(f); return 5; }
   const int host_loc = (int)n_loc - 1;
   auto ekeys = read_u32(f, n_ent), elocs = read_u32(f, n_ent), eoffs = read_u32(f, n_ent);
   auto rows = read_u32(f, n_loc);
   auto batch = read_u32(f, n_keys);
+  // every index the kernels will dereference is checked here, on the host
+  if (rows[host_loc] < N) { fprintf(stderr, "host source shorter than the id space\n"); return 5; }
+  for (size_t i = 0; i < n_ent; i++)
+    if (ekeys[i] >= N || elocs[i] >= n_loc || eoffs[i] >= rows[elocs[i]]) {
+      fprintf(stderr, "entry %zu out of range\n", i);
+      return 5;
+    }
+  for (size_t i = 0; i < n_keys; i++)
+    if (batch[i] >= N) { fprintf(stderr, "key %zu out of range\n", i); return 5; }
 
   PIN_CUDA(cudaSetDevice(0));
   RunConfig::option_empty_feat = 0;

@@ -87,7 +87,7 @@ def ref_extract_case(orc, solver, case):
     words, cnt, slot_of = orc.model_build(w.placement, rank, w.capacity)
     loc = (words >> 28).astype(np.uint32)
     off = (words & ((1 << 28) - 1)).astype(np.uint32)
-    cached = np.nonzero(loc != G)[0].astype(np.uint32)
+    cached = np.nonzero(words != 0xFFFFFFFF)[0].astype(np.uint32)   # host keys have no entry
     tab = w.table.view(np.uint8).reshape(w.N, w.row_bytes)
     sources, rows = [], []
     for g in range(G):
@@ -106,8 +106,7 @@ def ref_extract_case(orc, solver, case):
     blob = b"".join(np.ascontiguousarray(p).tobytes() for p in parts)
 
     if case["flat"]:
-        rec = orc.lookup_flat(np.where(loc != G, words, 0xFFFFFFFF).astype(np.uint32), keys,
-                              fallback_loc=G)
+        rec = orc.lookup_flat(words, keys, fallback_loc=G)
     else:
         t = orc.SimpleTable(cached.size)
         for g in range(G):          # the pin inserts location by location, in list order
