@@ -53,7 +53,9 @@ def parse_args():
                          "cache ordered by degree")
     ap.add_argument("--gnn-degree", type=int, default=15)
     ap.add_argument("--gnn-seeds", type=int, default=8000)
-    ap.add_argument("--policy", default="intuitive", choices=["intuitive", "rep", "clique_part"])
+    ap.add_argument("--policy", default="intuitive", choices=["intuitive", "rep", "clique_part", "split_search"],
+                    help="split_search costs every replicate/partition split with the link model "
+                         "whose host term follows the measured host-row rate")
     ap.add_argument("--table-kind", type=int, default=0)
     ap.add_argument("--empty-feat", type=int, default=0,
                     help="k>0: host table holds 2^k rows, host offsets wrap (mock)")
@@ -458,7 +460,11 @@ def run_ours(a):
         ids, freqs = gnn.hotness()
     else:
         ids, freqs = wl.analytic_hotness(a.rows, a.alpha)
-    placement = rt.solve_placement(a.policy, G, ids, freqs, a.cache_pct * 100.0)
+    if a.policy == "split_search":
+        tl, tr, tc = rt.link_model(G, row_bytes)
+        placement = rt.solve_placement(a.policy, G, ids, freqs, a.cache_pct * 100.0, tl, tr, tc)
+    else:
+        placement = rt.solve_placement(a.policy, G, ids, freqs, a.cache_pct * 100.0)
     del ids, freqs
     cache = rt.Cache(G, a.rows, row_bytes, a.cache_pct, max_batch=a.batch,
                      empty_feat=a.empty_feat, table_kind=a.table_kind,

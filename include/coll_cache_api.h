@@ -25,7 +25,8 @@ extern "C" {
 
 /* operation.h:34-35, operation.cc:160-173.  Keys: cache_percentage, _cache_policy, num_device,
  * num_global_step_per_epoch, num_epoch, num_total_item, omp_thread_num (operation.cc:72-78).
- * Policies that need the MILP solver (8, 13, 18) fall back to the intuitive heuristic (9). */
+ * Policies that need the MILP solver (8, 13, 18) are served by the library's split search
+ * (UGC_POLICY_SPLIT_SEARCH in ugache_b200.h), which costs every replicate/partition split. */
 int coll_cache_config(const char** config_keys, const char** config_values, size_t num_config_items);
 
 size_t coll_cache_num_epoch(void); /* operation.h:37 */

@@ -43,7 +43,16 @@ typedef enum {
 typedef enum {
   UGC_POLICY_INTUITIVE = 9, /* coll_intuitive: replicate hottest, partition next      */
   UGC_POLICY_REP = 12,      /* rep: replicate hottest on every GPU                    */
-  UGC_POLICY_CLIQUE_PART = 14 /* clique_part: partition hottest round-robin           */
+  UGC_POLICY_CLIQUE_PART = 14, /* clique_part: partition hottest round-robin          */
+  UGC_POLICY_SPLIT_SEARCH = 100 /* no reference number: stands in for the reference's MILP
+                                   policies (coll_cache_asymm_link and relatives,
+                                   coll_cache_lib/coll_cache/optimal_solver_class.cc:957-1112) on a
+                                   switch-connected box, where the optimum is a replicate /
+                                   partition / host split: every split is costed against the
+                                   recorded hotness with max((local + served + 1) * t_local,
+                                   peers * t_remote, host * t_cpu), where "served" is what the
+                                   peers read from this GPU, and the cheapest kept; among equals
+                                   the most replicated                                     */
 } ugc_policy;
 
 typedef enum { UGC_TABLE_AUTO = 0, UGC_TABLE_FLAT = 1, UGC_TABLE_HASHED = 2 } ugc_table_kind;
@@ -154,6 +163,15 @@ int ugc_solve_placement(int policy, int num_device, uint64_t num_total_item,
 /* Default B200 time-per-byte ratios (local : remote : host) for the solvers, the
  * counterpart of coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289. */
 int ugc_link_model(int num_device, double* t_local, double* t_remote, double* t_cpu);
+
+/* Modelled cost per reader of a placement under the concurrent-source model above (shares of
+ * the recorded hotness served from the local slice, from peers and from the host).  No
+ * reference counterpart; lets a caller compare policies before building.  cost has num_device
+ * entries. */
+int ugc_placement_cost(int num_device, uint64_t num_total_item, const uint32_t* rank_ids,
+                       const uint32_t* rank_freqs, const uint32_t* nid_to_block,
+                       const uint8_t* block_access_from, int num_block, double t_local,
+                       double t_remote, double t_cpu, double* cost);
 
 /* Hands the placement to the context (arrays are copied).  Corresponds to the four shm
  * tensors the reference publishes (coll_cache_lib/facade.cc:238-261). */

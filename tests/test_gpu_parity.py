@@ -399,3 +399,28 @@ def test_probing_table_churn(built_lib):
         st = cache.stats(0)
         assert st["err_table"] == 0 and st["free_rows"] == st["capacity_rows"] - stored.sum()
     cache.close()
+
+
+@pytest.mark.parametrize("G,row_bytes_model", [(4, None), (2, 512), (8, 128)])
+def test_split_search_placement_serves_exact_rows(built_lib, G, row_bytes_model):
+    """Build and look up under the split-search policy: every reader gets exactly the host
+    table's rows, and the per-source counts follow the placement."""
+    from ugache_b200 import runtime as rt, workload as wl
+
+    def solver(policy, G_, ids, freqs, pct):
+        tl, tr, tc = rt.link_model(G_, row_bytes_model)
+        return rt.solve_placement(policy, G_, ids, freqs, pct, tl, tr, tc)
+
+    w = wl.Workload(N=60_000, dim=32, dtype="float32", G=G, pct=0.08, alpha=1.1, n_keys=20_000,
+                    policy="split_search", seed=41, dedup=False, solver=solver)
+    cache = make_cache(w)
+    for r in range(G):
+        keys = w.keys(rank=r)
+        got = lookup_np(cache, r, keys)
+        assert np.array_equal(got, orc.gather(w.table, keys).view(np.uint8).reshape(len(keys), -1)), r
+        st = cache.stats(r)
+        src = w.placement.block_access_from[r][w.placement.nid_to_block[keys]]
+        assert st["last_local"] == int((src == r).sum())
+        assert st["last_host"] == int((src == G).sum())
+        assert st["last_remote"] == int(((src != r) & (src != G)).sum())
+    cache.close()

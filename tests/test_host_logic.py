@@ -148,3 +148,50 @@ def test_workload_generators_match_oracle():
         assert np.array_equal(wl.rank_to_id(r, N), orc.rank_to_id(r, N, A, B))
         ids = wl.rank_to_id(np.arange(1000), N)
         assert len(np.unique(ids)) == 1000
+
+
+@pytest.mark.parametrize("G,alpha,pct", [(1, 1.2, 10.0), (2, 1.2, 10.0), (4, 1.2, 10.0), (8, 1.2, 10.0),
+                                         (8, 1.05, 5.0), (4, 1.01, 2.0), (2, 1.5, 20.0), (3, 1.1, 30.0)])
+def test_split_search_is_never_costlier_than_the_heuristics(built_lib, G, alpha, pct):
+    """The split-search policy (the stand-in for the reference's MILP on a switch-connected
+    box) yields a placement the runtime accepts, within the cache capacity, whose modelled cost
+    is at most that of every heuristic policy, under the nominal link model and under the one
+    with the measured host-row rate."""
+    from ugache_b200 import runtime as rt, workload as wl
+    N = 400_000
+    ids, freqs = wl.analytic_hotness(N, alpha)
+    cache = rt.Cache(G, N, 512, pct / 100.0)
+    for row_bytes in (None, 512, 128):
+        tl, tr, tc = rt.link_model(G, row_bytes)
+        costs = {}
+        for pol in ("rep", "clique_part", "intuitive", "split_search"):
+            p = rt.solve_placement(pol, G, ids, freqs, pct, tl, tr, tc)
+            costs[pol] = float(rt.placement_cost(p, ids, freqs, tl, tr, tc).max())
+            if pol == "split_search":
+                cache.set_placement(p)                      # validated by the runtime
+                stored = (p.block_placement[p.nid_to_block][:, None] >> np.arange(G)) & 1
+                assert stored.sum(axis=0).max() <= int(N * (pct / 100.0 + 0.001))
+                # hotter ids are never placed worse than colder ones: replicated, then
+                # partitioned, then host, along the hotness order
+                kind = np.where(p.block_placement[p.nid_to_block[ids]] == (1 << G) - 1, 0,
+                                np.where(p.block_placement[p.nid_to_block[ids]] != 0, 1, 2))
+                assert (np.diff(kind) >= 0).all()
+        best_other = min(v for k, v in costs.items() if k != "split_search")
+        assert costs["split_search"] <= best_other * (1 + 1e-6), (row_bytes, costs)
+    cache.close()
+
+
+def test_placement_cost_rejects_bad_arrays(built_lib):
+    from ugache_b200 import _lib, runtime as rt
+    ids = np.arange(1000, dtype=np.uint32)
+    freqs = np.arange(1000, 0, -1).astype(np.uint32)
+    p = rt.solve_placement("rep", 2, ids, None, 10.0)
+    c = rt.placement_cost(p, ids, freqs)
+    assert c.shape == (2,) and c[0] == c[1] and c[0] > 0
+    bad = rt.PlacementArrays(p.nid_to_block.copy(), p.block_placement, p.block_access_from,
+                             p.block_density)
+    bad.nid_to_block[3] = 77
+    with pytest.raises(_lib.UgcError):
+        rt.placement_cost(bad, ids, freqs)
+    with pytest.raises(_lib.UgcError):
+        rt.solve_placement("split_search", 2, ids, None, 10.0)   # needs frequencies

@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(HERE, "libugache_b200.so")
 
 UGC_MAX_DEVICE = 8
 UGC_OK = 0
-POLICY_INTUITIVE, POLICY_REP, POLICY_CLIQUE_PART = 9, 12, 14
+POLICY_INTUITIVE, POLICY_REP, POLICY_CLIQUE_PART, POLICY_SPLIT_SEARCH = 9, 12, 14, 100
 TABLE_AUTO, TABLE_FLAT, TABLE_HASHED = 0, 1, 2
 
 ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_size_t, C.c_void_p)
@@ -113,6 +113,7 @@ SIGNATURES = {
     "ugc_solve_placement": (_I, [_I, _I, _U64, _P, _P, _D, _D, _D, _D, _P, _P, _P, _P,
                                  C.POINTER(_I)]),
     "ugc_link_model": (_I, [_I, C.POINTER(_D), C.POINTER(_D), C.POINTER(_D)]),
+    "ugc_placement_cost": (_I, [_I, _U64, _P, _P, _P, _P, _I, _D, _D, _D, _P]),
     "ugc_set_placement": (_I, [_P, _P, _P, _P, _P, _I]),
     "ugc_classify_keys": (_I, [_P, _I, _P, _P]),
     "ugc_build": (_I, [_P, _I, _I, _P, _P]),

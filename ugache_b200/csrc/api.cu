@@ -933,6 +933,25 @@ int ugc_solve_placement(int policy, int num_device, uint64_t N, const uint32_t* 
   return UGC_OK;
 }
 
+int ugc_placement_cost(int num_device, uint64_t N, const uint32_t* rank_ids, const uint32_t* rank_freqs,
+                       const uint32_t* nid_to_block, const uint8_t* block_access_from, int num_block,
+                       double t_local, double t_remote, double t_cpu, double* cost) {
+  if (num_device < 1 || num_device > UGC_MAX_DEVICE || num_block < 1 || !nid_to_block || !block_access_from)
+    return fail(UGC_ERR_INVALID, "bad placement arguments");
+  Placement p;
+  p.num_device = num_device;
+  p.num_block = num_block;
+  p.nid_to_block.assign(nid_to_block, nid_to_block + N);
+  p.block_access_from.assign(block_access_from, block_access_from + (size_t)num_device * num_block);
+  for (uint64_t k = 0; k < N; k++)
+    if (p.nid_to_block[k] >= (uint32_t)num_block) return fail(UGC_ERR_INVALID, "block id out of range");
+  for (uint8_t a : p.block_access_from)
+    if (a > num_device) return fail(UGC_ERR_INVALID, "source location out of range");
+  std::string err = placement_cost(p, N, rank_ids, rank_freqs, t_local, t_remote, t_cpu, cost);
+  if (!err.empty()) return fail(UGC_ERR_INVALID, "%s", err.c_str());
+  return UGC_OK;
+}
+
 int ugc_link_model(int num_device, double* t_local, double* t_remote, double* t_cpu) {
   if (!t_local || !t_remote || !t_cpu) return fail(UGC_ERR_INVALID, "null output");
   b200_link_model(num_device, t_local, t_remote, t_cpu);

@@ -303,8 +303,10 @@ int coll_cache_config(const char** keys, const char** values, size_t n) {
   std::lock_guard<std::mutex> lock(g_mu);
   g_cfg.cache_percentage = atof(m["cache_percentage"].c_str());
   int pol = atoi(m["_cache_policy"].c_str());
-  if (pol == 8 || pol == 13 || pol == 18) pol = UGC_POLICY_INTUITIVE;  // MILP policies: no solver here
-  if (pol != UGC_POLICY_INTUITIVE && pol != UGC_POLICY_REP && pol != UGC_POLICY_CLIQUE_PART)
+  // the MILP policies have no solver here: the split search stands in for them
+  if (pol == 8 || pol == 13 || pol == 18) pol = UGC_POLICY_SPLIT_SEARCH;
+  if (pol != UGC_POLICY_INTUITIVE && pol != UGC_POLICY_REP && pol != UGC_POLICY_CLIQUE_PART &&
+      pol != UGC_POLICY_SPLIT_SEARCH)
     return fail(UGC_ERR_UNSUPPORTED, "cache policy " + m["_cache_policy"] + " is not supported");
   g_cfg.policy = pol;
   g_cfg.num_device = atoi(m["num_device"].c_str());

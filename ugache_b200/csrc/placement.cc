@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <omp.h>
 #include <cstring>
 
 #include "../../include/ugache_b200.h"
@@ -58,6 +59,32 @@ void alloc_out(Placement* out, int G, uint64_t N, int B) {
   out->num_device = G;
 }
 
+// Blocks of a replicate / partition / host split: ranks < L on every GPU (block 0), ranks
+// L..R dealt round-robin (block 1 + rank % G), ranks > R on the host (block G + 1).
+void emit_split(int G, uint32_t N, const uint32_t* ids, uint32_t L, uint32_t R, uint32_t part,
+                Placement* out) {
+#pragma omp parallel for
+  for (int64_t rank = 0; rank < (int64_t)N; rank++) {
+    uint32_t b;
+    if ((uint32_t)rank < L) b = 0;
+    else if ((uint32_t)rank <= R) b = (uint32_t)rank % (uint32_t)G + 1;
+    else b = (uint32_t)G + 1;
+    out->nid_to_block[ids[rank]] = b;
+  }
+  const int B = G + 2;
+  out->block_placement[0] = (uint8_t)((1 << G) - 1);
+  for (int g = 0; g < G; g++) out->block_placement[g + 1] = (uint8_t)(1 << g);
+  for (int g = 0; g < G; g++) {
+    uint8_t* row = &out->block_access_from[(size_t)g * B];
+    row[0] = (uint8_t)g;
+    for (int b = 1; b <= G; b++) row[b] = (uint8_t)(b - 1);
+    row[G + 1] = (uint8_t)G;
+  }
+  out->block_density[0] = (double)L * 100 / (double)N;
+  for (int b = 1; b <= G; b++) out->block_density[b] = part * 100.0 / (double)N;
+  out->block_density[G + 1] = 100 - (R / (double)N) * 100;
+}
+
 std::string solve_intuitive(int G, uint32_t N, const uint32_t* ids, const uint32_t* freq, double pct,
                             double T_local, double T_remote, double T_cpu, Placement* out) {
   if (!freq) return "the intuitive policy needs rank_freqs";
@@ -81,27 +108,86 @@ std::string solve_intuitive(int G, uint32_t N, const uint32_t* ids, const uint32
     }
     part = hi;
   }
-  const uint32_t L = lb(part), R = rb(part);
-#pragma omp parallel for
-  for (int64_t rank = 0; rank < (int64_t)N; rank++) {
-    uint32_t b;
-    if ((uint32_t)rank < L) b = 0;
-    else if ((uint32_t)rank <= R) b = (uint32_t)rank % (uint32_t)G + 1;
-    else b = (uint32_t)G + 1;
-    out->nid_to_block[ids[rank]] = b;
+  emit_split(G, N, ids, lb(part), rb(part), part, out);
+  return "";
+}
+
+// Hotness mass below a rank, from coarse prefix sums with linear interpolation inside a step.
+struct HotnessPrefix {
+  std::vector<double> sum;  // sum[j] = total frequency of ranks < j * step
+  uint64_t step = 1, n = 0;
+  void build(uint32_t N, const uint32_t* freq) {
+    n = N;
+    step = std::max<uint64_t>(1, N / 16384);
+    const int64_t J = (int64_t)((N + step - 1) / step);
+    std::vector<double> part((size_t)J, 0.0);
+#pragma omp parallel for schedule(static)
+    for (int64_t j = 0; j < J; j++) {
+      const uint64_t end = std::min<uint64_t>(N, (uint64_t)(j + 1) * step);
+      double a = 0;
+      for (uint64_t r = (uint64_t)j * step; r < end; r++) a += (double)freq[r];
+      part[(size_t)j] = a;
+    }
+    sum.assign((size_t)J + 1, 0.0);
+    for (int64_t j = 0; j < J; j++) sum[(size_t)j + 1] = sum[(size_t)j] + part[(size_t)j];
   }
-  const int B = G + 2;
-  out->block_placement[0] = (uint8_t)((1 << G) - 1);
-  for (int g = 0; g < G; g++) out->block_placement[g + 1] = (uint8_t)(1 << g);
-  for (int g = 0; g < G; g++) {
-    uint8_t* row = &out->block_access_from[(size_t)g * B];
-    row[0] = (uint8_t)g;
-    for (int b = 1; b <= G; b++) row[b] = (uint8_t)(b - 1);
-    row[G + 1] = (uint8_t)G;
+  double below(uint64_t rank) const {
+    if (rank >= n) return sum.back();
+    const uint64_t j = rank / step;
+    const uint64_t width = std::min<uint64_t>(step, n - j * step);
+    return sum[j] + (sum[j + 1] - sum[j]) * (double)(rank - j * step) / (double)width;
   }
-  out->block_density[0] = (double)L * 100 / (double)N;
-  for (int b = 1; b <= G; b++) out->block_density[b] = part * 100.0 / (double)N;
-  out->block_density[G + 1] = 100 - (R / (double)N) * 100;
+};
+
+// Modelled time of one GPU per unit of looked-up bytes when its sources are read concurrently
+// (one launch, role-partitioned): the slowest of
+//   HBM   : (bytes it reads from its own slice + bytes its peers read from its slice + every
+//            output byte it writes) * t_local
+//   links : bytes it reads from peers * t_remote
+//   host  : bytes it reads from the host table * t_cpu
+double concurrent_cost(double f_local, double f_remote, double f_host, double f_served,
+                       double t_local, double t_remote, double t_cpu) {
+  return std::max((f_local + f_served + 1.0) * t_local, std::max(f_remote * t_remote, f_host * t_cpu));
+}
+
+// Split search for a switch-connected box.  On a uniform topology the optimum of the reference's
+// MILP (OptimalAsymmLinkSolver, coll_cache_lib/coll_cache/optimal_solver_class.cc:957-1112) has
+// the shape the intuitive policy assumes: the hottest L ranks on every GPU, the next ranks dealt
+// round-robin, the rest on the host, with L + part = capacity.  The only free variable is `part`,
+// so every feasible value (in 4096 steps) is costed with the concurrent-source model against the
+// recorded hotness and the cheapest kept; among equals the one with more replication wins
+// (fewer rows cross the links).
+std::string solve_split_search(int G, uint32_t N, const uint32_t* ids, const uint32_t* freq, double pct,
+                               double T_local, double T_remote, double T_cpu, Placement* out) {
+  if (!freq) return "the split-search policy needs rank_freqs";
+  alloc_out(out, G, N, G + 2);
+  const uint32_t cached = (uint32_t)(N * (pct / 100.0));
+  uint32_t hi = 0;
+  if (G > 1) hi = std::min<uint32_t>(cached, (N - cached) / (uint32_t)(G - 1));
+  HotnessPrefix hp;
+  hp.build(N, freq);
+  const double total = std::max(hp.sum.back(), 1.0);
+  uint32_t best_part = 0;
+  double best = 0;
+  const uint32_t kSteps = 4096;
+  for (uint32_t i = 0; i <= kSteps; i++) {
+    const uint32_t part = (uint32_t)((uint64_t)hi * i / kSteps);
+    if (i && part == (uint32_t)((uint64_t)hi * (i - 1) / kSteps)) continue;
+    const uint64_t L = cached - part, R = (uint64_t)cached + (uint64_t)part * (G - 1);
+    const double f_rep = hp.below(L) / total, f_cov = hp.below(R) / total;
+    const double f_part = f_cov - f_rep;
+    // every GPU serves as much to its peers as it reads from them (same hotness on every reader)
+    const double f_remote = f_part * (G - 1) / G;
+    const double cost =
+        concurrent_cost(f_rep + f_part / G, f_remote, 1.0 - f_cov, f_remote, T_local, T_remote, T_cpu);
+    if (i == 0 || cost < best * (1 - 1e-9)) {
+      best = cost;
+      best_part = part;
+    }
+  }
+  const uint32_t L = cached - best_part;
+  const uint32_t R = std::max<uint32_t>(cached + best_part * (uint32_t)(G - 1), 1u) - 1u;
+  emit_split(G, N, ids, L, R, best_part, out);
   return "";
 }
 
@@ -155,10 +241,49 @@ std::string solve_placement(int policy, int G, uint64_t N, const uint32_t* ids, 
       break;
     case UGC_POLICY_REP: err = solve_rep(G, (uint32_t)N, ids, pct, out); break;
     case UGC_POLICY_CLIQUE_PART: err = solve_clique(G, (uint32_t)N, ids, pct, out); break;
-    default: return "unknown policy (supported: 9 intuitive, 12 rep, 14 clique_part)";
+    case UGC_POLICY_SPLIT_SEARCH:
+      err = solve_split_search(G, (uint32_t)N, ids, freq, pct, T_local, T_remote, T_cpu, out);
+      break;
+    default: return "unknown policy (supported: 9 intuitive, 12 rep, 14 clique_part, 100 split search)";
   }
   out->valid = err.empty();
   return err;
+}
+
+std::string placement_cost(const Placement& p, uint64_t N, const uint32_t* ids, const uint32_t* freq,
+                           double T_local, double T_remote, double T_cpu, double* cost_per_reader) {
+  const int G = p.num_device, B = p.num_block;
+  if (!ids || !freq || !cost_per_reader) return "rank_ids, rank_freqs and the output are required";
+  if (p.nid_to_block.size() < N) return "placement is smaller than the id space";
+  std::vector<double> mass((size_t)B, 0.0);
+  {
+    const int T = omp_get_max_threads();
+    std::vector<double> priv((size_t)T * B, 0.0);
+#pragma omp parallel
+    {
+      double* mine = &priv[(size_t)omp_get_thread_num() * B];
+#pragma omp for schedule(static)
+      for (int64_t r = 0; r < (int64_t)N; r++) mine[p.nid_to_block[ids[r]]] += (double)freq[r];
+    }
+    for (int t = 0; t < T; t++)
+      for (int b = 0; b < B; b++) mass[(size_t)b] += priv[(size_t)t * B + b];
+  }
+  double total = 0;
+  for (double m : mass) total += m;
+  total = std::max(total, 1.0);
+  for (int g = 0; g < G; g++) {
+    double f[3] = {0, 0, 0};  // local, peers, host
+    double served = 0;        // read from this GPU's slice by the other readers
+    for (int b = 0; b < B; b++) {
+      const double m = mass[(size_t)b] / total;
+      const int src = p.access(g, (uint32_t)b);
+      f[src == g ? 0 : (src == G ? 2 : 1)] += m;
+      for (int r = 0; r < G; r++)
+        if (r != g && p.access(r, (uint32_t)b) == g) served += m;
+    }
+    cost_per_reader[g] = concurrent_cost(f[0], f[1], f[2], served, T_local, T_remote, T_cpu);
+  }
+  return "";
 }
 
 void classify_keys(const Placement& p, int reader, uint64_t N, std::vector<uint32_t> keys_by_src[],

@@ -40,11 +40,21 @@ void b200_link_model(int num_device, double* t_local, double* t_remote, double* 
 
 // IntuitiveSolver / RepSolver / CliquePartSolver of the reference
 // (coll_cache_lib/coll_cache/optimal_solver_class.cc:1251-1404, :1869-1924, :1926-2058).
+// plus UGC_POLICY_SPLIT_SEARCH, which has no counterpart among them: it stands in for the
+// reference's MILP (optimal_solver_class.cc:957-1112) on a switch-connected box by costing every
+// replicate/partition split against the recorded hotness.
 // cache_percent in percent.  Returns an empty string or the reason for failure.
 std::string solve_placement(int policy, int num_device, uint64_t num_total_item,
                             const uint32_t* rank_ids, const uint32_t* rank_freqs,
                             double cache_percent, double t_local, double t_remote, double t_cpu,
                             Placement* out);
+
+// Modelled cost of a placement per reader under the concurrent-source model the split-search
+// policy minimises: max((local + served to peers + 1) * t_local, peers * t_remote, host * t_cpu),
+// the fractions being shares of the recorded hotness.  Lets callers compare policies before building.
+std::string placement_cost(const Placement& p, uint64_t num_total_item, const uint32_t* rank_ids,
+                           const uint32_t* rank_freqs, double t_local, double t_remote, double t_cpu,
+                           double* cost_per_reader);
 
 // Keys served to `reader` by each GPU source, ascending key order
 // (replaces coll_cache_lib/cuda/cache_hashtable.cuh:741-835).  counts has G+1 entries

@@ -8,11 +8,12 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import (POLICY_CLIQUE_PART, POLICY_INTUITIVE, POLICY_REP, TABLE_AUTO, TABLE_FLAT,
+from ._lib import (POLICY_CLIQUE_PART, POLICY_INTUITIVE, POLICY_REP, POLICY_SPLIT_SEARCH, TABLE_AUTO, TABLE_FLAT,
                    TABLE_HASHED, UgcError, check)
 
 POLICIES = {"intuitive": POLICY_INTUITIVE, "coll_intuitive": POLICY_INTUITIVE,
-            "rep": POLICY_REP, "clique_part": POLICY_CLIQUE_PART}
+            "rep": POLICY_REP, "clique_part": POLICY_CLIQUE_PART,
+            "split_search": POLICY_SPLIT_SEARCH}
 
 
 class PlacementArrays:
@@ -37,10 +38,21 @@ def _ptr(a):
     return a.ctypes.data_as(C.c_void_p)
 
 
-def link_model(num_device):
+# Scattered rows of pinned host memory arrive at about this rate on the B200 machines measured,
+# whatever the row size up to 512 B; the host link is then slower than its bandwidth says.
+HOST_ROWS_PER_S = 30e6
+
+
+def link_model(num_device, row_bytes=None):
+    """(t_local, t_remote, t_cpu) time-per-byte ratios of the library's B200 link model.  With
+    ``row_bytes`` the host term is raised to what scattered row reads really cost
+    (``HOST_ROWS_PER_S`` rows per second) when that is slower than the link bandwidth."""
     tl, tr, tc = C.c_double(), C.c_double(), C.c_double()
     check(_lib.lib().ugc_link_model(num_device, C.byref(tl), C.byref(tr), C.byref(tc)))
-    return tl.value, tr.value, tc.value
+    t_cpu = tc.value
+    if row_bytes:
+        t_cpu = max(t_cpu, tl.value * 8000e9 / (HOST_ROWS_PER_S * row_bytes))
+    return tl.value, tr.value, t_cpu
 
 
 def solve_placement(policy, num_device, rank_ids, rank_freqs, cache_percent, t_local=None,
@@ -67,6 +79,22 @@ def solve_placement(policy, num_device, rank_ids, rank_freqs, cache_percent, t_l
     b = nb.value
     return PlacementArrays(n2b, bp[:b].copy(), ba[:num_device * b].reshape(num_device, b).copy(),
                            bd[:b].copy())
+
+
+def placement_cost(placement, rank_ids, rank_freqs, t_local=None, t_remote=None, t_cpu=None):
+    """Modelled cost per reader (concurrent sources: the slowest of HBM, peer links and host
+    link, in units of t_local per looked-up byte) of a placement against a hotness record."""
+    G = placement.num_device
+    rank_ids = np.ascontiguousarray(rank_ids, dtype=np.uint32)
+    freqs = np.ascontiguousarray(rank_freqs, dtype=np.uint32)
+    dl, dr, dc = link_model(G)
+    cost = np.zeros(G, dtype=np.float64)
+    ba = np.ascontiguousarray(placement.block_access_from, dtype=np.uint8)
+    check(_lib.lib().ugc_placement_cost(
+        G, len(rank_ids), _ptr(rank_ids), _ptr(freqs), _ptr(placement.nid_to_block), _ptr(ba),
+        placement.num_block, dl if t_local is None else t_local,
+        dr if t_remote is None else t_remote, dc if t_cpu is None else t_cpu, _ptr(cost)))
+    return cost
 
 
 class Cache:
