@@ -267,6 +267,12 @@ int ugc_lookup_host(ugc_ctx* ctx, int replica_id, const void* keys, int key_byte
  *   ugc_refresh_fill           step 6: scatter new rows into freed slots, insert them
  *   ugc_refresh_attach         step 7: resolve and insert the new remote keys
  *   ugc_refresh_commit         once per process: new placement becomes current
+ * Lookups of the same replica may be issued from another thread (on another stream) during all
+ * of it, as the reference's background refresh allows: an evicted key is served from the host
+ * table until it is cached again, a slot is reused only after every lookup that could still
+ * name it has drained (ugc_refresh_evict ends with a device-wide wait), and a new entry becomes
+ * visible only after its row has been written (same stream, one 64-bit publish).  The phase
+ * calls of one replica must come from one thread at a time.
  */
 int ugc_refresh_set_placement(ugc_ctx* ctx, const uint32_t* nid_to_block,
                               const uint8_t* block_placement, const uint8_t* block_access_from,

@@ -424,3 +424,70 @@ def test_split_search_placement_serves_exact_rows(built_lib, G, row_bytes_model)
         assert st["last_host"] == int((src == G).sum())
         assert st["last_remote"] == int(((src != r) & (src != G)).sum())
     cache.close()
+
+
+@pytest.mark.parametrize("kind", [1, 2])
+def test_lookups_stay_exact_while_a_refresh_runs(built_lib, kind):
+    """Lookups issued from other threads, on their own streams, while a background thread takes
+    the cache through whole refreshes back and forth: every batch must still be the host
+    table's rows (evicted keys come from the host, reused slots are never read by an older
+    lookup, new entries appear only with their rows)."""
+    import threading
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim, G = 120_000, 32, 2
+    table = wl.table(51, N, dim)
+    ids, freqs = wl.analytic_hotness(N, 1.1)
+    p_a = rt.solve_placement("intuitive", G, ids, freqs, 10.0)
+    p_b = rt.solve_placement("intuitive", G, np.roll(ids, 9000), freqs, 10.0)
+    cache = rt.Cache(G, N, dim * 4, 0.10, max_batch=1 << 15, table_kind=kind)
+    cache.set_placement(p_a)
+    host = pinned_table(table)
+    ndev = torch.cuda.device_count()
+    for r in range(G):
+        cache.build(r, r % ndev, host.data_ptr())
+    cache.connect_local()
+    for r in range(G):
+        cache.attach_peers(r)
+    stop = threading.Event()
+    failures, done = [], [0] * G
+
+    def reader(r):
+        dev = torch.device("cuda", r % ndev)
+        try:
+            with torch.cuda.device(dev):
+                stream = torch.cuda.Stream(dev)
+                out = torch.empty((20_000, dim * 4), dtype=torch.uint8, device=dev)
+                it = 0
+                while not stop.is_set() or it < 4:
+                    keys = wl.zipf_keys(1000 * r + it, 20_000, N, 1.1)
+                    with torch.cuda.stream(stream):
+                        k = torch.from_numpy(keys).to(dev, non_blocking=False)
+                        out.fill_(0xEE)
+                        cache.lookup(r, k, out=out)
+                        stream.synchronize()
+                        got = out.cpu().numpy()
+                    if got.tobytes() != orc.gather(table, keys).tobytes():
+                        failures.append((r, it))
+                        return
+                    it += 1
+                    done[r] = it
+        except Exception as e:  # surfaces in the main thread's assert
+            failures.append((r, repr(e)))
+
+    threads = [threading.Thread(target=reader, args=(r,)) for r in range(G)]
+    for t in threads:
+        t.start()
+    try:
+        # the refresh runs on each device's default stream; the readers' streams do not
+        # synchronise with it (torch creates non-blocking streams)
+        for round_ in range(6):
+            cache.refresh_all_local(p_b if round_ % 2 == 0 else p_a, list(range(G)))
+    finally:
+        stop.set()
+        for t in threads:
+            t.join(timeout=120)
+    assert not failures, failures
+    assert min(done) >= 4
+    for r in range(G):
+        assert cache.stats(r)["err_table"] == 0
+    cache.close()

@@ -1442,6 +1442,14 @@ int ugc_refresh_evict(ugc_ctx* c, int replica_id, void* stream) {
     UGC_CUDA(launch_table_evict(r->table, list_ptr(r, kListDropRemote), (uint32_t)n_drop, r->counters, s));
     UGC_TRY(check_table_errors(r, s, "refresh evict remote"));
   }
+  // Grace period.  A lookup that was enqueued before the evictions above completed may hold a
+  // record naming a slot that is about to be given to another key (here, or on a peer that this
+  // replica just stopped reading from).  Everything enqueued on this device so far is drained
+  // before the call returns; the caller's barrier between the evict and fill phases then keeps
+  // every replica's fill behind every replica's drain.  Lookups enqueued from now on see only
+  // the tables without the evicted entries.  (The reference waits for the trainer's step
+  // counter to advance instead, coll_cache_lib/cache_context.cu:4050-4052.)
+  UGC_CUDA(cudaDeviceSynchronize());
   r->next_n_local = n_new_local;
   r->refresh_open = true;
   return UGC_OK;
