@@ -54,6 +54,18 @@ def test_collcache_torch_api_threads(built_lib):
                 out = co.coll_torch_lookup_key_t_val_ret(r, torch.from_numpy(k).to(dev).to(torch.int32),
                                                          pad_to_8=False)
                 assert out.cpu().numpy().tobytes() == orc.gather(table, k).tobytes()
+            # a second refresh in the background while this thread keeps looking up
+            for i in range(3):
+                co.coll_torch_record(r, torch.from_numpy(wl.zipf_keys(950 + i, 20000, N, 1.3)))
+            job = co.coll_torch_refresh_async(r)
+            rounds = 0
+            while rounds < 3 or not job.done():
+                for k in batches[r]:
+                    out = co.coll_torch_lookup_key_t_val_ret(r, torch.from_numpy(k).to(dev).to(torch.int64),
+                                                             pad_to_8=False)
+                    assert out.cpu().numpy().tobytes() == orc.gather(table, k).tobytes()
+                rounds += 1
+            job.wait(timeout=120)
             # a batch larger than anything recorded grows the scratch
             big = wl.zipf_keys(7, 90000, N, 1.2)
             out = co.coll_torch_lookup_key_t_val_ret(r, torch.from_numpy(big).to(dev).to(torch.int32), False)

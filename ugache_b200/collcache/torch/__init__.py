@@ -148,6 +148,45 @@ def coll_torch_refresh(local_id):
     _basics._ok(_L().coll_cache_refresh(local_id, ctypes.c_void_p(stream)), "coll_cache_refresh")
 
 
+class _RefreshJob:
+    """Handle of a background refresh: ``wait()`` joins it and re-raises its failure."""
+
+    def __init__(self, local_id, dev):
+        import threading
+        self.error = None
+
+        def work():
+            try:
+                with torch.cuda.device(dev):
+                    stream = torch.cuda.Stream(dev)
+                    _basics._ok(_L().coll_cache_refresh(local_id, ctypes.c_void_p(stream.cuda_stream)),
+                                "coll_cache_refresh")
+                    stream.synchronize()
+            except Exception as e:  # handed to wait()
+                self.error = e
+
+        self._t = threading.Thread(target=work, name="collcache-refresh-%d" % local_id, daemon=True)
+        self._t.start()
+
+    def done(self):
+        return not self._t.is_alive()
+
+    def wait(self, timeout=None):
+        self._t.join(timeout)
+        if self._t.is_alive():
+            raise TimeoutError("background refresh still running")
+        if self.error is not None:
+            raise self.error
+
+
+def coll_torch_refresh_async(local_id):
+    """Starts ``coll_torch_refresh`` on a background thread with a stream of its own and returns
+    a handle; lookups of the replica may go on meanwhile (the reference's TensorFlow binding
+    refreshes this way, from a helper thread, ``CollCache::refresh(..., foreground=false)``).
+    Every replica must start one, as with the blocking form."""
+    return _RefreshJob(local_id, _state["dev"][local_id])
+
+
 def coll_torch_shutdown():
     _basics.shutdown()
     _state["out"].clear()
