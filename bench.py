@@ -727,8 +727,10 @@ def run_ours(a):
         cdt = time.perf_counter() - c0
         cpu = {"value": cpu_keys * row_bytes / cdt / 1e9, "unit": "GB/s",
                "cores": threads, "kind": "port",
-               "sample": "%d batches of %d keys over the same host table, after 3 warm-up "
-                         "batches, all host threads" % (a.cpu_steps, a.batch)}
+               "sample": "%d batches of %d keys over the same host table (the GPU-visible pinned "
+                         "allocation, which the CPU reads more slowly than the private anonymous "
+                         "table of --impl reference), after 3 warm-up batches, all host threads"
+                         % (a.cpu_steps, a.batch)}
 
     # ---- the line -------------------------------------------------------------------------
     sec = ms_total * 1e-3
