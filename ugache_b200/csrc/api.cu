@@ -70,11 +70,11 @@ uint64_t pow2_ceil(uint64_t v) {
 }  // namespace
 
 // Host tables allocated through the virtual-memory API at a host NUMA location come in
-// 2 MiB physical chunks, which the GPU maps with large pages: random row reads over a table
-// of tens of GB then stop missing in the GPU's address translation (4 KiB mappings of
-// registered memory made those reads several times slower while HBM traffic was running).
-// The driver entry points are resolved at run time so that the library still loads on a
-// machine without a driver.
+// 2 MiB physical chunks, which the GPU can map with large pages, so random row reads over a
+// table of tens of GB need far fewer GPU-side translations than 4 KiB mappings of registered
+// memory.  (On the machines measured so far the host-row rate came out the same either way:
+// the limit sat on the far side of PCIe.)  The driver entry points are resolved at run time
+// so that the library still loads on a machine without a driver.
 namespace {
 struct VmmApi {
   CUresult (*create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
@@ -319,7 +319,8 @@ int dev_block_export_fd(void* p) {
 // ---- handing exported descriptors to other processes ----------------------------------------
 // First choice: the importer duplicates the descriptor straight out of the owner
 // (pidfd_open + pidfd_getfd).  Where the kernel's ptrace policy forbids that, the owner serves
-// its exported descriptors over an abstract-namespace Unix socket (SCM_RIGHTS).
+// its exported descriptors over an abstract-namespace Unix socket (SCM_RIGHTS), to processes of
+// the same user only.
 std::set<int> g_served_fds;
 bool g_fd_server_running = false;
 
@@ -336,6 +337,13 @@ void fd_server_loop(int listen_fd) {
     if (c < 0) {
       if (errno == EINTR) continue;
       return;
+    }
+    // only processes of the same user are served (the descriptors give access to the cache memory)
+    ucred peer;
+    socklen_t peer_len = sizeof(peer);
+    if (getsockopt(c, SOL_SOCKET, SO_PEERCRED, &peer, &peer_len) != 0 || peer.uid != geteuid()) {
+      close(c);
+      continue;
     }
     int wanted = -1;
     if (read(c, &wanted, sizeof(wanted)) == (ssize_t)sizeof(wanted)) {
