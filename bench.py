@@ -83,6 +83,10 @@ def parse_args():
     ap.add_argument("--sorted-batches", action="store_true",
                     help="ascending key order inside each batch (what a caller that deduplicates "
                          "by sorting hands over); the default keeps the generator's random order")
+    ap.add_argument("--sweep", default="",
+                    help="one GPU: 'alphas;ratios', e.g. '0.8,1.0,1.2,1.4;0.02,0.05,0.10,0.20' — the "
+                         "skew and capacity sweep over one host table; prints one JSON line with a "
+                         "point per (alpha, ratio) instead of the benchmark line")
     ap.add_argument("--sweep-out", default="", help="write extra per-phase numbers here (json)")
     return ap.parse_args()
 
@@ -410,6 +414,96 @@ def run_reference_gpu(a):
                 "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     })
     print(json.dumps(base), flush=True)
+
+
+# ---------------------------------------------------------------------------------------
+def run_sweep(a):
+    """Skew and capacity sweep on one GPU: for every (alpha, cache ratio) a fresh cache is
+    built over the same host table and `--steps` lookups of `--batch` keys are timed."""
+    import torch
+    from ugache_b200 import build as ubuild
+    ubuild.build()
+    from ugache_b200 import runtime as rt, workload as wl
+    alphas, ratios = [[float(x) for x in part.split(",") if x] for part in a.sweep.split(";")]
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    elem = 4 if a.dtype == "float32" else 2
+    row_bytes = a.dim * elem
+    table = HostTable(a.rows, row_bytes, 0, 1, "sweep", library_owned=True)
+    stream = torch.cuda.current_stream().cuda_stream
+    rt.gen_table(table.map_for_gpu(), a.seed, 0, a.rows, a.dim, elem, stream)
+    torch.cuda.synchronize()
+    hbm_peak, peak_kind = measured_peaks()
+    out = torch.empty((a.batch, row_bytes), dtype=torch.uint8, device=dev)
+    total = a.warmup + a.steps
+    points = []
+    for alpha in alphas:
+        ids, freqs = wl.analytic_hotness(a.rows, alpha)
+        a.alpha = alpha
+        keys_np = make_keys(a, 0, total)
+        keys_dev = torch.from_numpy(keys_np).to(dev)
+        for ratio in ratios:
+            placement = rt.solve_placement(a.policy, 1, ids, freqs, ratio * 100.0)
+            cache = rt.Cache(1, a.rows, row_bytes, ratio, max_batch=a.batch, register_host=False)
+            cache.set_placement(placement)
+            cache.build(0, 0, table.ptr, stream)
+            for i in range(a.warmup):
+                cache.lookup(0, keys_dev[i], out=out)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(a.warmup, total):
+                cache.lookup(0, keys_dev[i], out=out)
+            e1.record()
+            torch.cuda.synchronize()
+            step_us = e0.elapsed_time(e1) / a.steps * 1e3
+            # per-source split of the timed batches, and one batch checked against the oracle
+            words = cache.table_words(0, keys_dev[a.warmup:total].reshape(-1).to(torch.int32)).view(-1)
+            torch.cuda.synchronize()
+            host_share = float((words == -1).sum().item()) / words.numel()
+            ok = None
+            if a.verify:
+                from oracle import oracle as orc
+                j = total - 1
+                cache.lookup(0, keys_dev[j], out=out)
+                torch.cuda.synchronize()
+                want = orc.gen_rows_for_keys(a.seed, keys_np[j], a.dim,
+                                             np.float32 if elem == 4 else np.float16)
+                ok = bool(out.cpu().numpy().tobytes() == want.tobytes())
+            st = cache.stats(0)
+            b_out = a.batch * row_bytes
+            b_host = host_share * b_out
+            b_loc = b_out - b_host
+
+            def tstar(hbm, pcie):
+                return max((b_loc + b_out) / hbm, b_host / pcie) / 1e9 * 1e6
+
+            points.append({
+                "alpha": alpha, "cache_ratio": ratio, "step_us": step_us,
+                "gbs": b_out / step_us / 1e3, "mkeys_per_s": a.batch / step_us,
+                "split": {"local": 1.0 - host_share, "remote": 0.0, "host": host_share},
+                "hit_rate": 1.0 - host_share, "global_miss_rate": host_share,
+                "table": "flat" if st["table_kind"] == 1 else "hashed",
+                "t_star_us_nominal": tstar(NOMINAL["hbm"], NOMINAL["pcie"]),
+                "frac_nominal": tstar(NOMINAL["hbm"], NOMINAL["pcie"]) / step_us,
+                "frac_measured_hbm": tstar(hbm_peak, NOMINAL["pcie"]) / step_us,
+                "verified_vs_oracle": ok,
+            })
+            print("point " + json.dumps(points[-1]), file=sys.stderr, flush=True)
+            cache.close()
+            del cache
+        del keys_dev
+    line = {"metric": "extracted_embedding_throughput", "unit": "GB/s", "n_gpus": 1,
+            "steps": a.steps, "warmup": a.warmup, "data": "synthetic",
+            "config": {"workload": "dlr_sweep_%dMx%d%s_batch%d" %
+                       (a.rows // 1_000_000, a.dim, "f32" if elem == 4 else "f16", a.batch),
+                       "policy": a.policy, "hbm_peak": hbm_peak, "peak_kind": peak_kind},
+            "sweep": points}
+    print(json.dumps(line), flush=True)
+    if a.sweep_out:
+        with open(a.sweep_out, "w") as f:
+            json.dump(line, f)
+    table.release()
 
 
 # ---------------------------------------------------------------------------------------
@@ -822,6 +916,8 @@ def main():
         run_reference(a)
     elif a.impl == "reference-gpu":
         run_reference_gpu(a)
+    elif a.sweep:
+        run_sweep(a)
     else:
         run_ours(a)
 
