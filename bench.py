@@ -881,7 +881,9 @@ def run_ours(a):
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "peak_kind": "of " + peak_kind, "traffic": traffic,
                      "traffic_note": "dram read+write per launch from the ncu capture of a 20 M-row "
-                                     "case, same batch and kernel (profiles/gather_roles_dlr.md)"
+                                     "case, same batch and kernel (profiles/gather_roles_dlr.md); "
+                                     "captured before the row loads allocated in L1, which moves "
+                                     "former L2 hits into L1 and leaves DRAM traffic as it was"
                                      if traffic else None,
                      "algorithmic_bytes_per_launch": algo_bytes,
                      "avg_launch_us": gather_ms_avg * 1e3,
