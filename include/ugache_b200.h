@@ -82,8 +82,8 @@ typedef struct {
    * counterpart of coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289).  0 = default. */
   double bw_local_gbs, bw_remote_gbs, bw_host_gbs;
   int32_t gather_ctas_per_sm; /* CTAs of the gather kernel per SM; 0 = default          */
-  int32_t host_ctas;          /* CTA budget of the host-row group; 0 = default          */
-  int32_t remote_ctas;        /* CTA budget of the peer-row group; 0 = default          */
+  int32_t host_ctas;          /* most CTAs the host-row group may take; 0 = default          */
+  int32_t remote_ctas;        /* most CTAs the peer-row group may take; 0 = default          */
   int32_t gather_vec_bytes;   /* 16 or 32 bytes per lane per load in the gather (host rows
                                  always use 16); 0 = 32 with 8 GPUs, else 16            */
   ugc_alloc_fn alloc;
@@ -306,8 +306,8 @@ typedef struct {
   int32_t gather_ctas_per_sm;     /* CTAs of the gather kernel per SM                       */
   int32_t gather_block_threads;   /* 256, 512 or 1024                                       */
   int32_t gather_vec_bytes;       /* 16 or 32 bytes per lane per load                       */
-  int32_t host_ctas;              /* CTA budget of the host-row group                       */
-  int32_t remote_ctas;            /* CTA budget of the peer-row group                       */
+  int32_t host_ctas;              /* most CTAs the host-row group may take                       */
+  int32_t remote_ctas;            /* most CTAs the peer-row group may take                       */
   int32_t bulk_mask;              /* far sources staged through shared memory by the
                                      bulk-async copy engine: bit 0 host rows, bit 1 peer rows */
   int32_t lookup_keys_per_thread; /* 1, 2 or 4                                              */

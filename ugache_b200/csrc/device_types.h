@@ -75,8 +75,8 @@ struct GatherParams {
   Counters* counters;
   uint32_t row_bytes;
   uint32_t n_keys;
-  int remote_cta_cap;   // CTA budget of the peer group
-  int host_cta_cap;     // CTA budget of the host group
+  int remote_cta_cap;   // most CTAs of the peer group
+  int host_cta_cap;     // most CTAs of the host group
   int rows_per_cta_min; // do not give a group more CTAs than count / this
   int pdl;              // launched with programmatic stream serialization
   int bulk_mask;        // bit 0: host rows, bit 1: peer rows go through bulk-async staging

@@ -466,7 +466,7 @@ __device__ __forceinline__ bool copy_rows_bulk(const RecordIndex& ix, uint32_t c
         bulk_s2g(dst[u], smem_u32(stage + (size_t)u * ix.row_bytes), ix.row_bytes);
       }
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-      // the slots are reused by the next round: wait until the stores have read them
+      // the slots are reused by the next pass: wait until the stores have read them
       asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
       if (!ok_all) break;
       parity ^= 1;

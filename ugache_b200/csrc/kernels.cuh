@@ -2,9 +2,9 @@
 //
 //   lookup_group   keys -> (location, offset) through the replica's table, grouped by
 //                  source into three record lists (local / peers / host) with the counts
-//                  left in device memory: no sort, no host round trip.
+//                  left in device memory: no sort, nothing goes through the host.
 //   gather_roles   one launch whose CTAs split into per-source groups sized from those
-//                  counts and the link budgets; each group copies its rows with vector
+//                  counts and the per-link CTA caps; each group copies its rows with vector
 //                  loads (local HBM, peer HBM over NVLink P2P, zero-copy host over PCIe).
 //   fill_scatter   host rows -> cache slots (build and refresh).
 //   table_*        insert / evict / word lookup / peer-table resolve.
