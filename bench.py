@@ -887,7 +887,13 @@ def run_ours(a):
                                      if traffic else None,
                      "algorithmic_bytes_per_launch": algo_bytes,
                      "avg_launch_us": gather_ms_avg * 1e3,
-                     "lookup_group_avg_us": lookup_ms_avg * 1e3},
+                     "lookup_group_avg_us": lookup_ms_avg * 1e3,
+                     # the same kernel by its own device clock (first CTA start to last CTA end,
+                     # sampled over single lookups): the event interval above also holds the
+                     # launch gap that the event records put between the two kernels
+                     "device_clock_span_us": float(max(grp)),
+                     "achieved_by_device_clock": (algo_bytes / (float(max(grp)) * 1e-6) / 1e9
+                                                  if max(grp) > 0 else None)},
         "cpu_baseline": cpu, "e2e": e2e, "e2e_device_consumer": e2e_dev, "clocks": clocks,
         "gpu_launches": 2 * a.steps * G,
         "per_rank": {"step_us": [m / a.steps * 1e3 for m in ms_all], "gather_us": ga_all,
