@@ -195,3 +195,28 @@ def test_placement_cost_rejects_bad_arrays(built_lib):
         rt.placement_cost(bad, ids, freqs)
     with pytest.raises(_lib.UgcError):
         rt.solve_placement("split_search", 2, ids, None, 10.0)   # needs frequencies
+
+
+def test_lookup_unique_helper_reassembles_the_batch(built_lib):
+    """The dedup-aware adapter on CPU tensors with a stand-in lookup: the distinct keys are
+    looked up once, in ascending order, and rows_unique[inverse] is the per-key result."""
+    torch = pytest.importorskip("torch")
+    from ugache_b200.collcache.torch import lookup_unique
+    from ugache_b200 import workload as wl
+    N, dim = 5000, 8
+    table = torch.from_numpy(wl.table(3, N, dim))
+    calls = []
+
+    def fake_lookup(u):
+        calls.append(u.clone())
+        out = torch.zeros((u.numel() + 5, dim))       # a larger reusable buffer, as the real one
+        out[:u.numel()] = table[u]
+        return out
+
+    for keys in (torch.from_numpy(wl.zipf_keys(9, 4000, N, 1.3)), torch.tensor([7, 7, 7], dtype=torch.int64),
+                 torch.zeros(0, dtype=torch.int64)):
+        rows, inverse = lookup_unique(keys, fake_lookup)
+        u = calls[-1]
+        assert rows.shape == (u.numel(), dim)
+        assert torch.equal(u, torch.unique(keys)) and (u.numel() < 2 or bool((u[1:] > u[:-1]).all()))
+        assert torch.equal(rows[inverse], table[keys])

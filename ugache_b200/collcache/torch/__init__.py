@@ -2,8 +2,9 @@
 the pybind module behind it, python/collcache/torch/adapter.cc:124-281), implemented with
 ctypes calls into libugache_b200.so.  PyTorch only owns tensors here.
 
-Extensions beyond the reference: int64 key tensors are accepted, ``coll_torch_refresh``
-exposes the refresh path (the reference reaches it only from its TF2 binding), and
+Extensions beyond the reference: int64 key tensors are accepted, ``coll_torch_refresh`` /
+``coll_torch_refresh_async`` expose the refresh path (the reference reaches it only from its
+TF2 binding), ``coll_torch_lookup_unique`` looks every distinct key of a batch up once, and
 ``coll_torch_shutdown`` releases everything.
 """
 import ctypes
@@ -146,6 +147,28 @@ def coll_torch_refresh(local_id):
     dev = _state["dev"][local_id]
     stream = torch.cuda.current_stream(dev).cuda_stream
     _basics._ok(_L().coll_cache_refresh(local_id, ctypes.c_void_p(stream)), "coll_cache_refresh")
+
+
+def lookup_unique(keys, lookup_fn):
+    """Dedup-aware lookup: the distinct keys of a batch are looked up once.
+
+    ``lookup_fn(unique_keys)`` returns the rows of ``unique_keys`` ([u, dim]); the result is
+    ``(rows_unique, inverse)`` with ``rows_unique[inverse]`` equal to the rows of ``keys`` in
+    batch order.  Returns views of whatever ``lookup_fn`` returns, so the aliasing rules of the
+    underlying lookup apply.  The distinct keys come out ascending, which also makes the table
+    probes of the lookup coalesce."""
+    unique, inverse = torch.unique(keys.reshape(-1), sorted=True, return_inverse=True)
+    rows = lookup_fn(unique)
+    return rows[:unique.numel()], inverse
+
+
+def coll_torch_lookup_unique(local_id, keys):
+    """``(rows_unique, inverse)`` for a key batch with duplicates (a recommendation batch under a
+    skewed distribution repeats its hottest ids thousands of times): consumers that pool or
+    scatter by ``inverse`` anyway (embedding-bag forward, sparse-gradient backward) need every
+    distinct row once.  ``rows_unique[inverse]`` is what ``coll_torch_lookup_key_t_val_ret``
+    returns for the same keys.  No counterpart in the reference."""
+    return lookup_unique(keys, lambda u: coll_torch_lookup_key_t_val_ret(local_id, u, pad_to_8=False))
 
 
 class _RefreshJob:
