@@ -67,6 +67,11 @@ def parse_args():
     ap.add_argument("--block-threads", type=int, default=0)
     ap.add_argument("--bulk-mask", type=int, default=-1)
     ap.add_argument("--lookup-kpt", type=int, default=0)
+    ap.add_argument("--extract-mode", default="", choices=["", "auto", "grouped", "direct"],
+                    help="ugc_tuning.extract_mode; default: the library's (auto)")
+    ap.add_argument("--direct-ctas-per-sm", type=int, default=0)
+    ap.add_argument("--cpu-threads", type=int, default=0,
+                    help="threads of the CPU arms; 0 = every core this process may run on")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--pdl", type=int, default=-1)
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 30)")
@@ -283,6 +288,29 @@ def workload_name(a):
              a.cache_pct * 100, a.batch))
 
 
+def recorded_traffic(kernel, batch, row_bytes, alpha, G):
+    """(bytes, source) of DRAM read+write per launch of `kernel`, from the ncu summaries kept
+    under profiles/ (profiles/dram_traffic.json: a list of captures with the workload each
+    one was taken on); (None, None) when no capture matches this run's shape."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            rows = json.load(f)["captures"]
+    except Exception:
+        return None, None
+    for r in rows:
+        if (r["kernel"] == kernel and r["keys_per_launch"] == batch and r["row_bytes"] == row_bytes
+                and abs(r["alpha"] - alpha) < 1e-9 and r["n_gpus"] == G):
+            return float(r["dram_bytes_per_launch"]), r["source"]
+    return None, None
+
+
+def config_block(a, row_bytes):
+    """The workload description both arms print (kept identical so the lines compare)."""
+    return {"workload": workload_name(a), "rows": a.rows, "dim": a.dim, "row_bytes": row_bytes,
+            "keys_per_gpu_per_step": a.batch, "alpha": a.alpha,
+            "cache_fraction_per_gpu": a.cache_pct, "policy": a.policy, "empty_feat": a.empty_feat}
+
+
 def make_keys(a, rank, count):
     from ugache_b200 import workload as wl
     out = np.empty((count, a.batch), dtype=np.int64)
@@ -294,23 +322,43 @@ def make_keys(a, rank, count):
 
 
 # ---------------------------------------------------------------------------------------
+def cpu_thread_count(a):
+    """Threads for the CPU arms: every core this process may run on, whatever OMP_NUM_THREADS
+    says (launchers such as torch.distributed.run export OMP_NUM_THREADS=1)."""
+    if a.cpu_threads > 0:
+        return a.cpu_threads
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def private_table(host_rows, row_bytes, elem, dim):
+    """A private anonymous mapping for the CPU arms (the kernel backs it with large pages): the
+    table a CPU-only deployment would hold.  Both CPU figures of this file read such a table."""
+    mm = mmap.mmap(-1, host_rows * row_bytes, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
+    return mm, np.frombuffer(mm, dtype=np.float32 if elem == 4 else np.float16).reshape(host_rows, dim)
+
+
 def run_reference(a):
     """The reference has no CPU extraction routine; its gather (extract_data) restated on the
-    CPU is timed here on the box's host cores, all threads, over the same table and keys."""
+    CPU is timed here on the box's host cores, all of them, over the same table and keys.  With
+    --gpus N a step is N batches, one from each rank's key stream, so that `value` is the same
+    whole-job aggregate the GPU arm reports."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
     from oracle import oracle as orc
+    G = max(1, a.gpus if world == 1 else world)
     elem = 4 if a.dtype == "float32" else 2
     row_bytes = a.dim * elem
     host_rows = (1 << a.empty_feat) if a.empty_feat else a.rows
     try:
-        mm = mmap.mmap(-1, host_rows * row_bytes, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
+        mm, table = private_table(host_rows, row_bytes, elem, a.dim)
     except (OSError, MemoryError, ValueError):
         a.empty_feat = 24
         host_rows = 1 << 24
-        mm = mmap.mmap(-1, host_rows * row_bytes, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
-    table = np.frombuffer(mm, dtype=np.float32 if elem == 4 else np.float16).reshape(host_rows, a.dim)
+        mm, table = private_table(host_rows, row_bytes, elem, a.dim)
     chunk = 1 << 20
     lib = orc.lib()
     import ctypes as C
@@ -319,29 +367,35 @@ def run_reference(a):
         fn = lib.orc_gen_rows_f32 if elem == 4 else lib.orc_gen_rows_f16
         fn(C.c_uint64(a.seed), C.c_uint64(r0), C.c_uint64(n), C.c_uint64(a.dim),
            C.c_void_p(table[r0:r0 + n].ctypes.data))
-    threads = orc.max_threads()
+    threads = cpu_thread_count(a)
     total = a.warmup + a.steps
-    keys = make_keys(a, 0, total)
+    keys = [make_keys(a, r, total) for r in range(G)]
     out = np.empty((a.batch, a.dim), dtype=table.dtype)
+
+    def step(i):
+        for r in range(G):
+            orc.gather(table, keys[r][i], empty_feat=a.empty_feat, num_threads=threads, out=out)
+
     for i in range(a.warmup):
-        orc.gather(table, keys[i], empty_feat=a.empty_feat, num_threads=threads, out=out)
+        step(i)
     t0 = time.perf_counter()
     for i in range(a.warmup, total):
-        orc.gather(table, keys[i], empty_feat=a.empty_feat, num_threads=threads, out=out)
+        step(i)
     dt = time.perf_counter() - t0
-    gbs = a.steps * a.batch * row_bytes / dt / 1e9
+    gbs = a.steps * G * a.batch * row_bytes / dt / 1e9
     line = {
         "impl": "reference", "metric": "extracted_embedding_throughput", "value": gbs,
         "unit": "GB/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": dt / a.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": workload_name(a), "rows": a.rows, "dim": a.dim,
-                   "keys_per_step": a.batch, "alpha": a.alpha, "empty_feat": a.empty_feat,
-                   "note": "CPU restatement of the reference gather; the reference itself has "
-                           "no CPU extraction routine"},
-        "mkeys_per_s": a.steps * a.batch / dt / 1e6,
+        "config": config_block(a, row_bytes),
+        "note": "CPU restatement of the reference gather (the reference itself has no CPU "
+                "extraction routine) over a private anonymous host table",
+        "mkeys_per_s": a.steps * G * a.batch / dt / 1e6,
+        "batches_per_step": G, "cores": threads,
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": "%d full batches of %d keys" % (a.steps, a.batch)},
+                         "sample": "%d steps of %d full batches of %d keys (one per rank's key "
+                                   "stream), private anonymous table" % (a.steps, G, a.batch)},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -577,6 +631,10 @@ def run_ours(a):
         tune["programmatic_launch"] = 0
     if a.pdl >= 0:
         tune["programmatic_launch"] = a.pdl
+    if a.extract_mode:
+        tune["extract_mode"] = {"auto": 0, "grouped": 1, "direct": 2}[a.extract_mode]
+    if a.direct_ctas_per_sm:
+        tune["direct_ctas_per_sm"] = a.direct_ctas_per_sm
     if tune:
         cache.tune(rank, **tune)
     if world > 1:
@@ -620,29 +678,37 @@ def run_ours(a):
     def step(i):
         cache.lookup_ptr(rank, keys_dev[i].data_ptr(), 8, sizes[i], out.data_ptr(), stream)
 
-    # ---- optional verification of one batch against the oracle -------------------------
-    verified = None
-    if a.verify and rank == 0:
+    # ---- verification of one batch on EVERY rank against the oracle ----------------------
+    def verify_batch(i):
+        """This rank's batch i through the lookup, against rows regenerated key by key by the
+        oracle's counter-based generator (no second copy of the table is read)."""
         from oracle import oracle as orc
-        step(0)
+        out.fill_(0xA5)
+        step(i)
         torch.cuda.synchronize()
-        got = out.cpu().numpy()
-        tv = table.np.reshape(host_rows, row_bytes)
-        want = orc.gather(tv, keys_np[0][:sizes[0]], empty_feat=a.empty_feat)
-        verified = bool(got[:sizes[0]].tobytes() == want.tobytes())
-        # the table itself against the oracle's generator on sampled rows
-        rows = np.unique(keys_np[0][:64] % host_rows)
-        want_rows = orc.gen_rows_for_keys(a.seed, rows, a.dim,
-                                          np.float32 if elem == 4 else np.float16)
-        verified = verified and bool(tv[rows].tobytes() == want_rows.tobytes())
+        got = out.cpu().numpy()[:sizes[i]]
+        k = keys_np[i][:sizes[i]]
+        if a.empty_feat:
+            k = k & ((1 << a.empty_feat) - 1)
+        want = orc.gen_rows_for_keys(a.seed, k, a.dim, np.float32 if elem == 4 else np.float16)
+        return bool(got.tobytes() == want.tobytes())
+
+    verified = None
+    verified_ranks = 0
+    if a.verify:
+        ok_pre = verify_batch(0)
+        verified_ranks = int(round(all_sum(1.0 if ok_pre else 0.0)))
+        verified = verified_ranks == G
         if not verified:
-            raise SystemExit("bench: lookup output differs from the oracle")
+            raise SystemExit("bench: lookup output differs from the oracle on %d of %d ranks"
+                             % (G - verified_ranks, G))
     barrier()
 
     # ---- warm-up, then the timed region (inputs resident in HBM) ----------------------
     for i in range(a.warmup):
         step(i)
     torch.cuda.synchronize()
+    launches_before = cache.launches(rank)
     sampler = ClockSampler(local)
     sampler.start()
     time.sleep(0.3)
@@ -651,12 +717,16 @@ def run_ours(a):
     torch.cuda.synchronize()
     t0 = time.time()
     e0.record()
+    h0 = time.perf_counter()
     for i in range(a.warmup, total):
         step(i)
+    enqueue_us = (time.perf_counter() - h0) / a.steps * 1e6   # host time to enqueue one lookup
     e1.record()
     torch.cuda.synchronize()
     t1 = time.time()
     barrier()
+    enqueue_all = all_list(enqueue_us)
+    launches_timed = cache.launches(rank)
     ms_rank = e0.elapsed_time(e1)
     ms_total = all_max(ms_rank)
     ms_all = all_list(ms_rank)
@@ -737,13 +807,8 @@ def run_ours(a):
         barrier(); tr.append(time.perf_counter())
         after = cache.stats(rank)
         ok = None
-        if a.verify and rank == 0:
-            from oracle import oracle as orc
-            step(0)
-            torch.cuda.synchronize()
-            tv = table.np.reshape(host_rows, row_bytes)
-            ok = bool(out.cpu().numpy()[:sizes[0]].tobytes() ==
-                      orc.gather(tv, keys_np[0][:sizes[0]], empty_feat=a.empty_feat).tobytes())
+        if a.verify:
+            ok = int(round(all_sum(1.0 if verify_batch(0) else 0.0))) == G
         refresh = {"drift_fraction": a.refresh, "seconds": {"classify_evict": tr[1] - tr[0], "fill_insert": tr[2] - tr[1],
                                                           "attach_peers": tr[3] - tr[2], "commit": tr[4] - tr[3],
                                                           "total": tr[4] - tr[0]},
@@ -751,6 +816,16 @@ def run_ours(a):
                    "free_rows_after": after["free_rows"], "table_errors": after["err_table"],
                    "lookup_exact_after_refresh": ok}
         barrier()
+
+    # ---- the same check after everything above ran (last timed batch, every rank) ----------
+    if a.verify:
+        ok_post = verify_batch(total - 1)
+        n_post = int(round(all_sum(1.0 if ok_post else 0.0)))
+        verified = verified and n_post == G
+        verified_ranks = min(verified_ranks, n_post)
+        if not verified:
+            raise SystemExit("bench: lookup output differs from the oracle after the timed region "
+                             "on %d of %d ranks" % (G - n_post, G))
 
     # ---- end to end with host buffers -------------------------------------------------
     e2e = None
@@ -771,10 +846,48 @@ def run_ours(a):
         barrier()
         e2e_ms = all_max(ee0.elapsed_time(ee1))
         ke_keys = sum(sizes[a.warmup:a.warmup + ke])
+        # the same call with staging copies instead of in-place pinned buffers
+        zc = cache.get_tuning(rank)["host_zero_copy"]
+        cache.tune(rank, host_zero_copy=0)
+        cache.lookup_host_ptr(rank, kpin[0].data_ptr(), 8, sizes[a.warmup], opin.data_ptr(), stream)
+        barrier()
+        torch.cuda.synchronize()
+        es0, es1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        es0.record()
+        for i in range(ke):
+            cache.lookup_host_ptr(rank, kpin[i].data_ptr(), 8, sizes[a.warmup + i], opin.data_ptr(), stream)
+        es1.record()
+        torch.cuda.synchronize()
+        barrier()
+        staged_ms = all_max(es0.elapsed_time(es1))
+        cache.tune(rank, host_zero_copy=zc)
+        # ceiling: the rows of one step copied device -> pinned host by the copy engine, all
+        # ranks at once, nothing else running
+        nb = ke_keys // ke * row_bytes
+        src_flat, dst_flat = out.view(-1)[:nb], opin.view(-1)[:nb]
+        dst_flat.copy_(src_flat, non_blocking=True)
+        barrier()
+        torch.cuda.synchronize()
+        ec0, ec1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ec0.record()
+        for i in range(10):
+            dst_flat.copy_(src_flat, non_blocking=True)
+        ec1.record()
+        torch.cuda.synchronize()
+        barrier()
+        d2h_ms = all_max(ec0.elapsed_time(ec1)) / 10
         e2e = {"value": G * ke_keys * row_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": ke_keys // ke * 8, "d2h_bytes_per_step": ke_keys // ke * row_bytes,
                "steps": ke, "ms_per_step": e2e_ms / ke,
-               "note": "ugc_lookup_host: pinned host keys in, pinned host rows out, every step"}
+               "staged_copies_ms_per_step": staged_ms / ke,
+               "d2h_copy_ceiling": {"ms_per_step": d2h_ms, "value": G * nb / (d2h_ms * 1e-3) / 1e9,
+                                    "unit": "GB/s",
+                                    "note": "plain device-to-pinned-host copy of one step's rows on "
+                                            "all %d GPUs at once" % G},
+               "frac_of_d2h_ceiling": d2h_ms / (e2e_ms / ke),
+               "note": "ugc_lookup_host: pinned host keys in, pinned host rows out, every step; "
+                       "host_zero_copy=%d (the kernel reads keys / writes rows across PCIe in "
+                       "place)" % zc}
 
     # ---- same, but the rows stay on the GPU (the reference's call shape: its consumer is a
     # model on the same GPU); the step's result read back is a 64-bit checksum of the rows ----
@@ -806,8 +919,19 @@ def run_ours(a):
     cpu = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         from oracle import oracle as orc
+        import psutil
         tv = table.np.reshape(host_rows, row_bytes)
-        threads = orc.max_threads()
+        kind_note = "the GPU-visible pinned table (not enough free memory for a private copy)"
+        if psutil.virtual_memory().available > host_rows * row_bytes + (24 << 30):
+            # same table kind as --impl reference: a private anonymous copy
+            pmm, ptab = private_table(host_rows, row_bytes, elem, a.dim)
+            pv = ptab.view(np.uint8).reshape(host_rows, row_bytes)
+            step_rows = max(1, (1 << 30) // row_bytes)
+            for r0 in range(0, host_rows, step_rows):
+                np.copyto(pv[r0:r0 + step_rows], tv[r0:r0 + step_rows])
+            tv = pv
+            kind_note = "a private anonymous copy of the host table (as --impl reference)"
+        threads = cpu_thread_count(a)
         o = np.empty((a.batch, row_bytes), dtype=np.uint8)
         for i in range(3):
             orc.gather(tv, keys_np[i % total][:sizes[i % total]], empty_feat=a.empty_feat,
@@ -821,10 +945,8 @@ def run_ours(a):
         cdt = time.perf_counter() - c0
         cpu = {"value": cpu_keys * row_bytes / cdt / 1e9, "unit": "GB/s",
                "cores": threads, "kind": "port",
-               "sample": "%d batches of %d keys over the same host table (the GPU-visible pinned "
-                         "allocation, which the CPU reads more slowly than the private anonymous "
-                         "table of --impl reference), after 3 warm-up batches, all host threads"
-                         % (a.cpu_steps, a.batch)}
+               "sample": "%d batches of %d keys over %s, after 3 warm-up batches, %d threads"
+                         % (a.cpu_steps, a.batch, kind_note, threads)}
 
     # ---- the line -------------------------------------------------------------------------
     sec = ms_total * 1e-3
@@ -844,9 +966,10 @@ def run_ours(a):
     def tstar(hbm, nvl, pcie):
         return max((b_loc + b_out) / hbm, b_rem / nvl, b_host / pcie) / 1e9 * 1e6  # us
 
-    # DRAM traffic per gather launch, from the ncu capture of this batch shape (71.9 MB: the
-    # Zipf head is served from L2 and half of the output is still in L2 when the kernel ends)
-    traffic = 71.9e6 if (a.batch == 8192 * 26 and row_bytes == 512 and a.alpha == 1.2 and G == 1) else None
+    # DRAM traffic per launch of the dominant kernel: read from the committed summary of the
+    # ncu capture taken for this batch shape (none for other shapes)
+    dominant = "extract_direct" if launches_timed - launches_before == a.steps else "gather_roles"
+    traffic, traffic_src = recorded_traffic(dominant, a.batch, row_bytes, a.alpha, G)
     step_us = ms_total / a.steps * 1e3
     mixed = {
         "t_star_us_nominal": tstar(NOMINAL["hbm"], NOMINAL["nvlink"], NOMINAL["pcie"]),
@@ -861,13 +984,10 @@ def run_ours(a):
         "n_gpus": G, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_total / a.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
         "data": "synthetic",
-        "config": {"workload": workload_name(a), "rows": a.rows, "dim": a.dim,
-                   "row_bytes": row_bytes, "keys_per_gpu_per_step": a.batch, "alpha": a.alpha,
-                   "cache_fraction_per_gpu": a.cache_pct, "policy": a.policy,
+        "config": {**config_block(a, row_bytes),
                    "table": {1: "flat", 2: "hashed"}.get(st["table_kind"], "?"),
                    "parallelism": "replicas=%d, cache partitioned+replicated by placement, "
                                   "one-sided P2P reads, no collective" % G,
-                   "empty_feat": a.empty_feat,
                    "l2": "inputs larger than L2 (%.1f GB slice + %.1f GB host table), a new key "
                          "batch every step, no flush" % (st["slice_bytes"] / 1e9,
                                                          host_rows * row_bytes / 1e9),
@@ -877,14 +997,10 @@ def run_ours(a):
         "source_split": {"local": n_local / n_all, "remote": n_remote / n_all,
                          "host": n_host / n_all},
         "mixed_roofline": mixed,
-        "roofline": {"bound": "hbm", "kernel": "gather_roles", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "peak_kind": "of " + peak_kind, "traffic": traffic,
-                     "traffic_note": "dram read+write per launch from the ncu capture of a 20 M-row "
-                                     "case, same batch and kernel (profiles/gather_roles_dlr.md); "
-                                     "captured before the row loads allocated in L1, which moves "
-                                     "former L2 hits into L1 and leaves DRAM traffic as it was"
-                                     if traffic else None,
+                     "traffic_note": traffic_src,
                      "algorithmic_bytes_per_launch": algo_bytes,
                      "avg_launch_us": gather_ms_avg * 1e3,
                      "lookup_group_avg_us": lookup_ms_avg * 1e3,
@@ -895,7 +1011,10 @@ def run_ours(a):
                      "achieved_by_device_clock": (algo_bytes / (float(max(grp)) * 1e-6) / 1e9
                                                   if max(grp) > 0 else None)},
         "cpu_baseline": cpu, "e2e": e2e, "e2e_device_consumer": e2e_dev, "clocks": clocks,
-        "gpu_launches": 2 * a.steps * G,
+        "gpu_launches": int(round(all_sum(float(launches_timed - launches_before)))),
+        "host_enqueue_us_per_lookup": enqueue_all,
+        "verified_ranks": verified_ranks,
+        "lookups_direct_share": st_last["lookups_direct"] / max(st_last["lookups"], 1),
         "per_rank": {"step_us": [m / a.steps * 1e3 for m in ms_all], "gather_us": ga_all,
                      "group_done_us": {"local": grp_all[0], "remote": grp_all[1], "host": grp_all[2]}},
         "variants": variants, "refresh": refresh,

@@ -57,6 +57,21 @@ typedef enum {
 
 typedef enum { UGC_TABLE_AUTO = 0, UGC_TABLE_FLAT = 1, UGC_TABLE_HASHED = 2 } ugc_table_kind;
 
+/* How a lookup extracts its rows.  The reference offers both shapes among its extraction
+ * implementations (coll_cache_lib/common.h:85-101): grouped by source with a per-source share
+ * of the SMs (its default, coll_cache_lib/cache_context.cu:1405-1465), and ungrouped, one copy
+ * kernel that resolves the source row by row (kDirectNoGroup, cache_context.cu:1295-1329).
+ *   GROUPED  lookup kernel writes one index list per source group (local / peers / host),
+ *            gather kernel splits its CTAs over the groups: best when many rows of a batch
+ *            come from the host table;
+ *   DIRECT   one kernel probes the table and copies each row from wherever it is, with no
+ *            index lists: best when nearly all rows come from GPU memory;
+ *   AUTO     DIRECT while the last finished lookup of the replica took no more than
+ *            ugc_tuning.direct_host_permille of its rows from the host table, else GROUPED
+ *            (the library reads those counts from a pinned mirror the kernels write; no
+ *            synchronisation). */
+typedef enum { UGC_EXTRACT_AUTO = 0, UGC_EXTRACT_GROUPED = 1, UGC_EXTRACT_DIRECT = 2 } ugc_extract_mode;
+
 /* Device-memory allocator supplied by the caller, the C form of the reference's
  * std::function<MemHandle(size_t)> gpu_mem_allocator (coll_cache_lib/facade.h:57-60,
  * coll_cache_lib/common.h:140-149).  Called with the replica's device current.
@@ -132,6 +147,8 @@ typedef struct {
   /* device-clock time (ns) from the start of the last gather kernel until the last CTA of
      each source group was done; 0 for an empty group */
   uint64_t last_local_ns, last_remote_ns, last_host_ns;
+  uint64_t lookups_direct;     /* lookups that took the direct (one-kernel) extraction  */
+  uint64_t kernel_launches;    /* kernels launched by lookups: 2 per grouped, 1 per direct */
 } ugc_stats_t;
 
 const char* ugc_version(void);
@@ -229,10 +246,9 @@ int ugc_lookup_i64(ugc_ctx* ctx, int replica_id, const int64_t* keys, size_t n, 
  * it, held until the process exits) instead of the scratch that ugc_build / ugc_reserve_batch
  * obtain from the allocator.  Meant for callers that cannot get device memory at the point
  * where they look keys up: a caller-supplied allocator that is a fixed arena with nothing left
- * once the cache slice is in it, a serving thread that must not take the device-wide
- * synchronisation ugc_reserve_batch does when a batch outgrows max_batch, or a lookup issued
- * while a stream is being captured (allocation calls are not allowed there).  The call
- * itself performs no allocation of any kind.
+ * once the cache slice is in it, or a serving thread that must not take the device-wide
+ * synchronisation ugc_reserve_batch does when a batch outgrows max_batch.  The call itself
+ * performs no allocation of any kind.
  *   - at most 262,144 keys per call (UGC_ERR_INVALID beyond that);
  *   - the first call on a GPU asks the runtime for the array's device address; make that
  *     first call before any stream capture starts;
@@ -250,9 +266,13 @@ int ugc_lookup_i64_static(ugc_ctx* ctx, int replica_id, const int64_t* keys, siz
  * is in flight. */
 int ugc_reserve_batch(ugc_ctx* ctx, int replica_id, uint32_t max_batch);
 
-/* Host-buffer form: keys and out are HOST pointers (pinned memory gives full speed).
- * Copies the keys to the GPU, runs the lookup, copies the rows back and returns after
- * they have landed.  key_bytes is 4 or 8. */
+/* Host-buffer form: keys and out are HOST pointers.  Returns after the rows have landed in
+ * `out`.  key_bytes is 4 or 8.  Pageable buffers go through device staging copies.  A buffer
+ * that is pinned and mapped for the GPU (cudaHostAlloc / cudaHostRegister with the mapped
+ * flag, or ugc_host_alloc) is used in place when ugc_tuning.host_zero_copy allows it: the
+ * extraction kernel reads the keys and writes the rows across PCIe itself, so rows start
+ * crossing the link while others are still being fetched and no staging buffer or copy-engine
+ * pass is needed. */
 int ugc_lookup_host(ugc_ctx* ctx, int replica_id, const void* keys, int key_bytes, size_t n,
                     void* out, void* stream);
 
@@ -315,6 +335,13 @@ typedef struct {
                                      kernel (its key loads and probes overlap the tail of
                                      the previous gather), bit 1 for the gather kernel (it is
                                      scheduled while the lookup kernel drains)              */
+  int32_t extract_mode;           /* ugc_extract_mode                                       */
+  int32_t direct_ctas_per_sm;     /* CTAs of the direct extraction kernel per SM, 1..8      */
+  int32_t direct_host_permille;   /* auto mode: direct while the last finished lookup took at
+                                     most this many of 1000 rows from the host table        */
+  int32_t host_zero_copy;         /* ugc_lookup_host with GPU-mapped pinned buffers: bit 0 the
+                                     kernel reads the keys in place, bit 1 it writes the rows
+                                     in place; a cleared bit selects a staging copy          */
 } ugc_tuning;
 int ugc_get_tuning(ugc_ctx* ctx, int replica_id, ugc_tuning* out);
 int ugc_set_tuning(ugc_ctx* ctx, int replica_id, const ugc_tuning* in);

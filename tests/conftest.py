@@ -34,6 +34,13 @@ def golden_cases():
         return json.load(f)
 
 
+@pytest.fixture(scope="session")
+def golden_cases_large():
+    """Cases at the sizes the benchmark configurations name (tests/golden/make_golden.py)."""
+    with open(os.path.join(GOLDEN, "cases_large.json")) as f:
+        return json.load(f)
+
+
 def oracle_solver(policy, G, rank_ids, rank_freqs, cache_percent):
     """Placement through the oracle's restatement of the reference heuristics."""
     from oracle import oracle as orc

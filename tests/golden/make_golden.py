@@ -59,6 +59,18 @@ CASES = [
 ]
 
 
+# Cases at the sizes the benchmark configurations name: the CPU-runnable configuration in full
+# (1,000,000 x 128 fp32 rows, one batch of 65,536 Zipf-1.2 draws deduplicated, every row on the
+# host) and the fp16 x 64 row shape of the flat-skew configuration over more than a million
+# rows with 20 % cached per GPU.  Kept in cases_large.json.
+LARGE_CASES = [
+    dict(name="c1_full_1Mx128_host_only", N=1_000_000, dim=128, dtype="float32", G=1, pct=0.0,
+         alpha=1.2, n_keys=65_536, policy="rep", seed=101, dedup=True, large=True),
+    dict(name="c4_shape_2Mx64f16_4gpu", N=2_000_000, dim=64, dtype="float16", G=4, pct=0.20,
+         alpha=1.05, n_keys=100_000, policy="intuitive", seed=102, dedup=False, large=True),
+]
+
+
 def oracle_solver(policy, G, rank_ids, rank_freqs, cache_percent):
     """Placement through the ORACLE's restatement of the reference heuristics, with the
     B200 time ratios local : peer : host = 1 : 8000/900 : 8000/64."""
@@ -71,12 +83,15 @@ def oracle_solver(policy, G, rank_ids, rank_freqs, cache_percent):
     return orc.solve_clique_part(G, rank_ids, cache_percent)
 
 
-def make_cases():
+def make_cases(cases=None, fname="cases.json"):
     from ugache_b200 import workload as wl
     from oracle import oracle as orc
     out = []
-    for c in CASES:
-        w = wl.Workload(solver=oracle_solver, **{k: v for k, v in c.items() if k != "name"})
+    for c in (CASES if cases is None else cases):
+        kw = {k: v for k, v in c.items() if k not in ("name", "large")}
+        if c.get("large"):
+            kw["table_array"] = orc.gen_rows(c["seed"], 0, c["N"], c["dim"], np.dtype(c["dtype"]))
+        w = wl.Workload(solver=oracle_solver, **kw)
         entry = dict(c)
         entry["table_head"] = digest(w.table[:64])
         entry["table"] = digest(w.table)
@@ -90,16 +105,21 @@ def make_cases():
                                  out=digest(orc.gather(w.table, keys)))
         entry["ranks"] = ranks
         out.append(entry)
-    with open(os.path.join(HERE, "cases.json"), "w") as f:
+    with open(os.path.join(HERE, fname), "w") as f:
         json.dump(out, f, indent=1)
-    print("cases.json:", [c["name"] for c in out])
+    print(fname + ":", [c["name"] for c in out])
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("UGACHE_REFERENCE", ""),
+                    help="root of the reference's source tree (or $UGACHE_REFERENCE); needed for "
+                         "ref_pin.json only")
     ap.add_argument("--skip-ref", action="store_true")
     a = ap.parse_args()
     if not a.skip_ref:
+        if not a.reference:
+            ap.error("--reference (or $UGACHE_REFERENCE) is required unless --skip-ref is given")
         make_ref_pin(a.reference)
     make_cases()
+    make_cases(LARGE_CASES, "cases_large.json")

@@ -12,6 +12,11 @@ def case_workload(case, solver=None):
     from ugache_b200 import workload as wl
     kw = {k: v for k, v in case.items()
           if k in ("N", "dim", "dtype", "G", "pct", "alpha", "n_keys", "policy", "seed", "dedup")}
+    if case.get("large"):
+        # full-size cases: the rows come from the oracle's C generator (same definition as
+        # workload.table, checked on the small cases; numpy needs GBs of temporaries here)
+        from oracle import oracle as orc
+        kw["table_array"] = orc.gen_rows(case["seed"], 0, case["N"], case["dim"], np.dtype(case["dtype"]))
     return wl.Workload(solver=solver, **kw)
 
 

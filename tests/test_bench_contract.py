@@ -37,3 +37,26 @@ def test_reference_gpu_arm_reports_unavailable_without_a_gpu():
     assert p.returncode == 0, p.stderr[-2000:]
     line = json.loads(p.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference-gpu" and "unavailable" in line
+
+
+def test_reference_arm_ignores_the_launchers_thread_limit_and_times_every_ranks_batch():
+    """torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm must still use every core
+    it may run on, and with --gpus N time N batches per step (the whole job's keys)."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", RANK="0", WORLD_SIZE="4", LOCAL_RANK="0")
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
+                        "--gpus", "4", "--rows", "200000", "--batch", "4096", "--steps", "2",
+                        "--warmup", "1"],
+                       capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
+    assert p.returncode == 0, p.stderr
+    d = json.loads([l for l in p.stdout.splitlines() if l.startswith("{")][0])
+    cores = len(os.sched_getaffinity(0))
+    assert d["cores"] == cores and d["cpu_baseline"]["cores"] == cores
+    assert d["batches_per_step"] == 4 and d["n_gpus"] == 4
+    # value counts all four batches of a step
+    assert abs(d["value"] - 4 * 4096 * 512 / (d["ms_per_step"] * 1e-3) / 1e9) < 1e-6 * d["value"] + 1e-9
+    one = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
+                          "--rows", "200000", "--batch", "4096", "--steps", "2", "--warmup", "1",
+                          "--cpu-threads", "2"], capture_output=True, text=True, timeout=300, cwd=ROOT)
+    d1 = json.loads([l for l in one.stdout.splitlines() if l.startswith("{")][0])
+    assert d1["cores"] == 2 and d1["batches_per_step"] == 1
+    assert d1["config"] == {**d["config"]}

@@ -19,6 +19,14 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
+@pytest.fixture(autouse=True, params=["grouped", "direct", "auto"])
+def extract_mode(request, monkeypatch):
+    """Every test of this module runs once per extraction mode (index lists + per-source CTA
+    groups / one fused kernel / chosen per lookup from the previous lookup's counts)."""
+    monkeypatch.setenv("UGC_EXTRACT_MODE", request.param)
+    return request.param
+
+
 def pinned_table(np_table):
     t = torch.from_numpy(np_table.view(np.uint8).reshape(np_table.shape[0], -1).copy()).pin_memory()
     return t
@@ -491,3 +499,104 @@ def test_lookups_stay_exact_while_a_refresh_runs(built_lib, kind):
     for r in range(G):
         assert cache.stats(r)["err_table"] == 0
     cache.close()
+
+
+@pytest.mark.parametrize("out_off,table_off,vec", [(4, 0, 32), (16, 0, 32), (0, 4, 16), (8, 16, 32), (0, 0, 32)])
+def test_unaligned_output_and_host_table(built_lib, out_off, table_off, vec):
+    """`out` and the host table may start at any multiple of 4 bytes: the kernels then fall
+    back to narrower vector loads instead of faulting on a misaligned address.  Checked for
+    lookups (local and host rows) and for the build-time fill."""
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim = 30000, 32                        # 128-byte rows
+    rb = dim * 4
+    table = wl.table(77, N, dim)
+    ids, freqs = wl.analytic_hotness(N, 1.2)
+    raw = torch.empty(N * rb + 64, dtype=torch.uint8).pin_memory()
+    raw[table_off:table_off + N * rb] = torch.from_numpy(table.view(np.uint8).reshape(-1))
+    cache = rt.Cache(1, N, rb, 0.10, max_batch=1 << 14, gather_vec_bytes=vec)
+    cache.set_placement(rt.solve_placement("rep", 1, ids, freqs, 10.0))
+    cache.build(0, 0, raw.data_ptr() + table_off)
+    keys = wl.zipf_keys(3, 9000, N, 1.1)
+    k = torch.from_numpy(keys).cuda()
+    buf = torch.full((len(keys) * rb + 64,), 0x77, dtype=torch.uint8, device="cuda")
+    out = buf[out_off:out_off + len(keys) * rb]
+    cache.lookup_ptr(0, k.data_ptr(), 8, len(keys), out.data_ptr(),
+                     torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    got = buf.cpu().numpy()
+    assert got[out_off:out_off + len(keys) * rb].tobytes() == orc.gather(table, keys).tobytes()
+    assert (got[:out_off] == 0x77).all() and (got[out_off + len(keys) * rb:] == 0x77).all()
+    st = cache.stats(0)
+    assert st["err_table"] == 0 and st["last_host"] > 0 and st["last_local"] > 0
+    cache.close()
+
+
+def test_host_buffers_in_place_and_staged(built_lib, golden_cases):
+    """ugc_lookup_host with pinned buffers the GPU has mapped (read and written in place by the
+    kernel) and with the staging copies forced: same bytes either way, int64 and uint32 keys."""
+    case = golden_cases[2]
+    w = case_workload(case)
+    cache = make_cache(w)
+    keys = w.keys(rank=0)
+    want = orc.gather(w.table, keys).tobytes()
+    kpin = torch.from_numpy(keys).pin_memory()
+    k32 = torch.from_numpy(keys.astype(np.int32)).pin_memory()
+    for zc in (3, 2, 1, 0):
+        cache.tune(0, host_zero_copy=zc)
+        for kt, kb in ((kpin, 8), (k32, 4)):
+            opin = torch.full((len(keys), w.row_bytes), 0x11, dtype=torch.uint8).pin_memory()
+            cache.lookup_host_ptr(0, kt.data_ptr(), kb, len(keys), opin.data_ptr(),
+                                  torch.cuda.current_stream().cuda_stream)
+            assert opin.numpy().tobytes() == want, (zc, kb)
+    cache.close()
+
+
+def test_auto_mode_follows_the_host_share(built_lib, extract_mode):
+    """In auto mode the first lookup is grouped; later ones go direct once a finished lookup
+    has shown a small host share, and back when the share is large."""
+    if extract_mode != "auto":
+        pytest.skip("only meaningful in auto mode")
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim = 40000, 32
+    table = wl.table(5, N, dim)
+    ids, freqs = wl.analytic_hotness(N, 1.2)
+    cache = rt.Cache(1, N, dim * 4, 0.25, max_batch=1 << 14)
+    p = rt.solve_placement("rep", 1, ids, freqs, 25.0)
+    cache.set_placement(p)
+    host = pinned_table(table)
+    cache.build(0, 0, host.data_ptr())
+    cached = np.nonzero(np.asarray(p.block_access_from).reshape(1, -1)[0][p.nid_to_block] == 0)[0]
+    missing = np.nonzero(np.asarray(p.block_access_from).reshape(1, -1)[0][p.nid_to_block] != 0)[0]
+    rng = np.random.default_rng(1)
+    hot = rng.choice(cached, 6000).astype(np.int64)
+    cold = rng.choice(missing, 6000).astype(np.int64)
+    for keys in (hot, hot, hot):
+        assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
+    st = cache.stats(0)
+    assert st["lookups"] == 3 and st["lookups_direct"] == 2 and st["kernel_launches"] == 4
+    for keys in (cold, cold):        # first of these still direct (decided by the last hot one)
+        assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
+    st = cache.stats(0)
+    assert st["lookups_direct"] == 3 and st["kernel_launches"] == 7
+    cache.close()
+
+
+def test_golden_cases_at_configuration_sizes(built_lib, golden_cases_large, extract_mode):
+    """Full-size cases: 1 M x 128 fp32 with every row on the host and one deduplicated batch of
+    65,536 draws; 2 M x 64 fp16 (128-byte rows) on 4 replicas with 20 % cached each."""
+    if extract_mode == "auto":
+        pytest.skip("grouped and direct cover it")
+    for case in golden_cases_large:
+        w = case_workload(case)
+        cache = make_cache(w, max_batch=1 << 17)
+        for r in range(w.G):
+            keys = w.keys(rank=r)
+            got = lookup_np(cache, r, keys)
+            assert digest(got) == case["ranks"][str(r)]["out"], (case["name"], r)
+            st = cache.stats(r)
+            assert st["err_key_range"] == 0 and st["err_table"] == 0
+            per_src = case["ranks"][str(r)]["per_src"]
+            assert st["num_local_rows"] == per_src[r]
+            if w.G == 1 and w.pct == 0.0:
+                assert (st["last_local"], st["last_remote"], st["last_host"]) == (0, 0, len(keys))
+        cache.close()

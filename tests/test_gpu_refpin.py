@@ -71,10 +71,13 @@ def test_reference_extraction_kernels_agree_with_oracle(tmp_path, case):
 
 
 @pytest.mark.skipif(not os.path.exists(REF_EXTRACT), reason="reference pin binary not built")
+@pytest.mark.parametrize("mode", ["grouped", "direct"])
 @pytest.mark.parametrize("case", REF_EXTRACT_CASES, ids=[c["name"] for c in REF_EXTRACT_CASES])
-def test_product_lookup_equals_reference_extraction(built_lib, tmp_path, case):
+def test_product_lookup_equals_reference_extraction(built_lib, tmp_path, case, mode, monkeypatch):
     """The shipped library (through its C ABI) against the reference's device code directly:
-    same table, same placement, same reader, same key batch -> same output bytes."""
+    same table, same placement, same reader, same key batch -> same output bytes, in both
+    extraction modes."""
+    monkeypatch.setenv("UGC_EXTRACT_MODE", mode)
     from tests.helpers import case_workload
     from tests.test_gpu_parity import lookup_np, make_cache
     blob, _ = ref_extract_case(orc, oracle_solver, case)

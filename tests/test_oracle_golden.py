@@ -104,6 +104,29 @@ def test_golden_cases(golden_cases):
             assert digest(orc.gather(w.table, keys)) == want["out"]
 
 
+def test_golden_cases_at_configuration_sizes(golden_cases_large):
+    """The CPU-runnable configuration in full (1 M x 128 fp32, 65,536 draws deduplicated, all
+    rows on the host) and the fp16 x 64 row shape over 2 M rows: keys, placement, per-key words
+    and gathered bytes against the committed digests."""
+    for case in golden_cases_large:
+        w = case_workload(case, oracle_solver)
+        assert digest(w.table) == case["table"], case["name"]
+        assert digest(w.placement.nid_to_block) + digest(w.placement.block_access_from) \
+            == case["placement"]
+        for r, want in case["ranks"].items():
+            keys = w.keys(rank=int(r))
+            assert digest(keys) == want["keys"]
+            if case["dedup"]:
+                assert len(np.unique(keys)) == len(keys) <= case["n_keys"]
+            words, cnt, _ = orc.model_build(w.placement, int(r), w.capacity)
+            assert digest(words) == want["words"]
+            assert [int(x) for x in cnt] == want["per_src"]
+            assert digest(orc.gather(w.table, keys)) == want["out"]
+    c1 = golden_cases_large[0]
+    assert c1["N"] == 1_000_000 and c1["dim"] == 128 and c1["n_keys"] == 65_536 and c1["pct"] == 0.0
+    assert c1["ranks"]["0"]["per_src"][0] == 0            # nothing cached: every key is a host row
+
+
 def test_refresh_slot_model():
     N, G = 4000, 2
     ids = np.arange(N, dtype=np.uint32)

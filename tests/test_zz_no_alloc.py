@@ -1,7 +1,7 @@
 """ugc_lookup_i64_static: the lookup whose scratch is a fixed array inside the library, for
 callers that cannot obtain device memory where they look keys up (a fixed-arena allocator
 that is already full, a serving thread that must not trigger the device-wide synchronisation
-of a scratch re-allocation, a lookup issued during stream capture).
+of a scratch re-allocation).
 
 The check: through the C ABI, its output equals that of the ordinary entry point
 (ugc_lookup_i64) byte for byte, on two calls in a row with different batches that share the

@@ -12,6 +12,7 @@ UGC_MAX_DEVICE = 8
 UGC_OK = 0
 POLICY_INTUITIVE, POLICY_REP, POLICY_CLIQUE_PART, POLICY_SPLIT_SEARCH = 9, 12, 14, 100
 TABLE_AUTO, TABLE_FLAT, TABLE_HASHED = 0, 1, 2
+EXTRACT_AUTO, EXTRACT_GROUPED, EXTRACT_DIRECT = 0, 1, 2
 
 ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_size_t, C.c_void_p)
 FREE_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)
@@ -76,6 +77,8 @@ class Stats(C.Structure):
         ("last_local_ns", C.c_uint64),
         ("last_remote_ns", C.c_uint64),
         ("last_host_ns", C.c_uint64),
+        ("lookups_direct", C.c_uint64),
+        ("kernel_launches", C.c_uint64),
     ]
 
 
@@ -90,6 +93,10 @@ class Tuning(C.Structure):
         ("bulk_mask", C.c_int32),
         ("lookup_keys_per_thread", C.c_int32),
         ("programmatic_launch", C.c_int32),
+        ("extract_mode", C.c_int32),
+        ("direct_ctas_per_sm", C.c_int32),
+        ("direct_host_permille", C.c_int32),
+        ("host_zero_copy", C.c_int32),
     ]
 
 

@@ -525,6 +525,16 @@ struct Replica {
   int bulk_mask = 0;
   int lookup_kpt = 1;
   int pdl = 3;  // bit 0: lookup kernel, bit 1: gather kernel launched with programmatic serialization
+  // extraction mode: UGC_EXTRACT_AUTO / _GROUPED / _DIRECT; in auto mode the choice follows
+  // the host-row share of the last finished lookup, read from the pinned mirror below
+  int extract_mode = UGC_EXTRACT_AUTO;
+  int direct_grid = 0;
+  double direct_host_share = 0.004;
+  Feedback* feedback = nullptr;      // pinned host memory, written by the kernels
+  Feedback* feedback_dev = nullptr;  // the same memory as the device addresses it
+  uint64_t lookups_direct = 0;
+  uint64_t kernel_launches = 0;
+  int host_zero_copy = 3;
   // per-kernel profiling (three events per lookup)
   std::vector<cudaEvent_t> prof_events;
   size_t prof_used = 0;
@@ -770,6 +780,7 @@ void release_replica(ugc_ctx* c, Replica* r) {
   ctx_free(c, r->stage_out.ptr);
   ctx_free(c, r->stage_a.ptr);
   ctx_free(c, r->stage_b.ptr);
+  if (r->feedback) cudaFreeHost(r->feedback);
   *r = Replica{};
 }
 
@@ -779,6 +790,7 @@ GatherParams gather_params(ugc_ctx* c, Replica* r, void* out, uint32_t n) {
   p.out = out;
   for (int g = 0; g < kNumGroup; g++) p.list[g] = r->list[g];
   p.counters = r->counters;
+  p.feedback = r->feedback_dev;
   p.row_bytes = c->cfg.row_bytes;
   p.n_keys = n;
   p.remote_cta_cap = r->remote_ctas;
@@ -787,6 +799,33 @@ GatherParams gather_params(ugc_ctx* c, Replica* r, void* out, uint32_t n) {
   p.bulk_mask = r->bulk_mask;
   p.pdl = (r->pdl & 2) ? 1 : 0;
   return p;
+}
+
+// Device-side address of pinned host memory that the GPU has mapped, else nullptr.
+void* mapped_device_pointer(const void* host) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (attr.type != cudaMemoryTypeHost || !attr.devicePointer) return nullptr;
+  return attr.devicePointer;
+}
+
+uint32_t host_mask_value(int empty_feat) {
+  return empty_feat > 0 && empty_feat < 32 ? ((1u << empty_feat) - 1u) : 0xffffffffu;
+}
+
+// Direct (one fused kernel) or grouped (index lists + per-source CTA groups) for the lookup
+// about to be enqueued.  In auto mode the last finished lookup decides: few host rows ->
+// direct.  The mirror is read without synchronising, so the answer may lag a few lookups.
+bool choose_direct(const Replica* r) {
+  if (r->extract_mode == UGC_EXTRACT_DIRECT) return true;
+  if (r->extract_mode == UGC_EXTRACT_GROUPED || !r->feedback) return false;
+  const volatile Feedback* f = r->feedback;
+  const uint32_t keys = f->keys, host = f->count[kGroupHost];
+  if (f->seq == 0 || keys == 0) return false;
+  return (double)host <= r->direct_host_share * (double)keys;
 }
 
 int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n, void* out,
@@ -799,6 +838,29 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
     return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
   const bool prof = r->prof_on && r->prof_used + 3 <= r->prof_events.size();
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used], s));
+  if (choose_direct(r)) {
+    if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 1], s));
+    DirectParams d{};
+    for (int i = 0; i < kMaxLocation; i++) d.src_base[i] = r->src_base[i];
+    d.out = out;
+    d.table = r->table;
+    d.counters = r->counters;
+    d.feedback = r->feedback_dev;
+    d.n_keys = (uint32_t)n;
+    d.row_bytes = c->cfg.row_bytes;
+    d.local_loc = (uint32_t)r->id;
+    d.host_loc = (uint32_t)c->cfg.num_device;
+    d.host_mask = host_mask_value(c->cfg.empty_feat);
+    UGC_CUDA(launch_extract_direct(keys, key_bytes, d, r->direct_grid, r->vec_bytes, (r->pdl & 1) != 0, s));
+    if (prof) {
+      UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 2], s));
+      r->prof_used += 3;
+    }
+    r->lookups++;
+    r->lookups_direct++;
+    r->kernel_launches += 1;
+    return UGC_OK;
+  }
   UGC_CUDA(launch_lookup_group(keys, key_bytes, (uint32_t)n, r->table, (uint32_t)r->id,
                                (uint32_t)c->cfg.num_device, c->cfg.empty_feat, r->list[kGroupLocal],
                                r->list[kGroupRemote], r->list[kGroupHost], r->counters, r->lookup_kpt, (r->pdl & 1) != 0, s));
@@ -810,6 +872,7 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
     r->prof_used += 3;
   }
   r->lookups++;
+  r->kernel_launches += 2;
   return UGC_OK;
 }
 
@@ -838,6 +901,12 @@ int static_scratch_address(int device, void** out) {
   if (device < 0 || device >= kStaticMaxDevices) return fail(UGC_ERR_UNSUPPORTED, "device ordinal %d too large", device);
   std::lock_guard<std::mutex> lock(g_static_mu);
   if (!g_static_addr[device]) {
+    // the symbol query answers for whichever device is current: make sure it is `device`
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != device) {
+      cudaGetLastError();
+      return fail(UGC_ERR_STATE, "static scratch set-up needs device %d current, found %d", device, cur);
+    }
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
     if (e != cudaSuccess || !p) {
@@ -1032,6 +1101,12 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
   r->sm_count = prop.multiProcessorCount;
   const int per_sm = c->cfg.gather_ctas_per_sm > 0 ? c->cfg.gather_ctas_per_sm : 8;
   r->gather_grid = r->sm_count * per_sm;
+  r->direct_grid = r->sm_count * 4;
+  if (const char* m = getenv("UGC_EXTRACT_MODE")) {  // initial ugc_tuning.extract_mode
+    if (!strcmp(m, "grouped")) r->extract_mode = UGC_EXTRACT_GROUPED;
+    if (!strcmp(m, "direct")) r->extract_mode = UGC_EXTRACT_DIRECT;
+    if (!strcmp(m, "auto")) r->extract_mode = UGC_EXTRACT_AUTO;
+  }
   r->host_ctas = c->cfg.host_ctas > 0 ? c->cfg.host_ctas : std::max(2, r->sm_count);
   r->remote_ctas = c->cfg.remote_ctas > 0 ? c->cfg.remote_ctas : std::max(2, r->sm_count * per_sm / 2);
   // 32-byte loads win when almost every row comes from HBM (8 GPUs, 458 host rows per batch:
@@ -1087,6 +1162,20 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
   }
   r->counters = static_cast<Counters*>(ctx_alloc(c, sizeof(Counters)));
   if (!r->counters) return bail(fail(UGC_ERR_NOMEM, "counter allocation failed"));
+  // pinned mirror of the last lookup's counts (16 bytes written across PCIe per lookup)
+  {
+    void* fb = nullptr;
+    void* fb_dev = nullptr;
+    if (cudaHostAlloc(&fb, sizeof(Feedback), cudaHostAllocMapped) == cudaSuccess &&
+        cudaHostGetDevicePointer(&fb_dev, fb, 0) == cudaSuccess) {
+      memset(fb, 0, sizeof(Feedback));
+      r->feedback = static_cast<Feedback*>(fb);
+      r->feedback_dev = static_cast<Feedback*>(fb_dev);
+    } else {  // without the mirror the auto mode stays on the grouped path
+      cudaGetLastError();
+      if (fb) cudaFreeHost(fb);
+    }
+  }
   if (cudaMemsetAsync(r->counters, 0, sizeof(Counters), s) != cudaSuccess)
     return bail(fail(UGC_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(cudaGetLastError())));
 
@@ -1382,13 +1471,22 @@ int ugc_lookup_host(ugc_ctx* c, int replica_id, const void* keys, int key_bytes,
   UGC_TRY(get_replica(c, replica_id, true, &r));
   if (key_bytes != 4 && key_bytes != 8) return fail(UGC_ERR_INVALID, "key_bytes must be 4 or 8");
   if (n == 0) return UGC_OK;
+  if (!keys || !out) return fail(UGC_ERR_INVALID, "keys and out must be non-null");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   UGC_CUDA(cudaSetDevice(r->device));
-  UGC_TRY(ensure(c, r->stage_keys, n * (size_t)key_bytes));
-  UGC_TRY(ensure(c, r->stage_out, n * (size_t)c->cfg.row_bytes));
-  UGC_CUDA(cudaMemcpyAsync(r->stage_keys.ptr, keys, n * (size_t)key_bytes, cudaMemcpyHostToDevice, s));
-  UGC_TRY(do_lookup(c, r, r->stage_keys.ptr, key_bytes, n, r->stage_out.ptr, s));
-  UGC_CUDA(cudaMemcpyAsync(out, r->stage_out.ptr, n * (size_t)c->cfg.row_bytes, cudaMemcpyDeviceToHost, s));
+  // Pinned buffers that the GPU has mapped are used in place: the kernel reads the keys and
+  // writes the rows across PCIe itself.
+  const void* keys_dev = (r->host_zero_copy & 1) ? mapped_device_pointer(keys) : nullptr;
+  void* out_dev = (r->host_zero_copy & 2) ? mapped_device_pointer(out) : nullptr;
+  if (!keys_dev) {
+    UGC_TRY(ensure(c, r->stage_keys, n * (size_t)key_bytes));
+    UGC_CUDA(cudaMemcpyAsync(r->stage_keys.ptr, keys, n * (size_t)key_bytes, cudaMemcpyHostToDevice, s));
+    keys_dev = r->stage_keys.ptr;
+  }
+  if (!out_dev) UGC_TRY(ensure(c, r->stage_out, n * (size_t)c->cfg.row_bytes));
+  UGC_TRY(do_lookup(c, r, keys_dev, key_bytes, n, out_dev ? out_dev : r->stage_out.ptr, s));
+  if (!out_dev)
+    UGC_CUDA(cudaMemcpyAsync(out, r->stage_out.ptr, n * (size_t)c->cfg.row_bytes, cudaMemcpyDeviceToHost, s));
   UGC_CUDA(cudaStreamSynchronize(s));
   return UGC_OK;
 }
@@ -1593,6 +1691,8 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   out->last_local_ns = span(kGroupLocal);
   out->last_remote_ns = span(kGroupRemote);
   out->last_host_ns = span(kGroupHost);
+  out->lookups_direct = r->lookups_direct;
+  out->kernel_launches = r->kernel_launches;
   return UGC_OK;
 }
 
@@ -1610,6 +1710,10 @@ int ugc_get_tuning(ugc_ctx* c, int replica_id, ugc_tuning* out) {
   out->bulk_mask = r->bulk_mask;
   out->lookup_keys_per_thread = r->lookup_kpt;
   out->programmatic_launch = r->pdl;
+  out->extract_mode = r->extract_mode;
+  out->direct_ctas_per_sm = r->direct_grid / std::max(r->sm_count, 1);
+  out->direct_host_permille = (int)(r->direct_host_share * 1000.0 + 0.5);
+  out->host_zero_copy = r->host_zero_copy;
   return UGC_OK;
 }
 
@@ -1620,7 +1724,10 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   const int bt = t->gather_block_threads, kpt = t->lookup_keys_per_thread, vec = t->gather_vec_bytes;
   if (t->gather_ctas_per_sm < 1 || t->gather_ctas_per_sm > 32 || (bt != 256 && bt != 512 && bt != 1024) ||
       (vec != 16 && vec != 32) || t->host_ctas < 1 || t->remote_ctas < 1 || t->bulk_mask < 0 ||
-      t->bulk_mask > 3 || (kpt != 1 && kpt != 2 && kpt != 4))
+      t->bulk_mask > 3 || (kpt != 1 && kpt != 2 && kpt != 4) || t->extract_mode < UGC_EXTRACT_AUTO ||
+      t->extract_mode > UGC_EXTRACT_DIRECT || t->direct_ctas_per_sm < 1 || t->direct_ctas_per_sm > 8 ||
+      t->direct_host_permille < 0 || t->direct_host_permille > 1000 || t->host_zero_copy < 0 ||
+      t->host_zero_copy > 3)
     return fail(UGC_ERR_INVALID, "ugc_tuning holds a value outside its range");
   r->gather_grid = r->sm_count * t->gather_ctas_per_sm;
   r->block_threads = bt;
@@ -1630,6 +1737,10 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   r->bulk_mask = t->bulk_mask;
   r->lookup_kpt = kpt;
   r->pdl = t->programmatic_launch & 3;
+  r->extract_mode = t->extract_mode;
+  r->direct_grid = r->sm_count * t->direct_ctas_per_sm;
+  r->direct_host_share = t->direct_host_permille / 1000.0;
+  r->host_zero_copy = t->host_zero_copy;
   return UGC_OK;
 }
 

@@ -65,6 +65,16 @@ struct Counters {
   // device clock (ns) of the last gather: earliest CTA start and, per group, latest CTA end
   unsigned long long t_start;
   unsigned long long t_end[kNumGroup];
+  uint32_t seq;                  // extractions finished on these counters
+  uint32_t reserved;
+};
+
+// Written by the last CTA of every extraction into pinned host memory: the host reads it
+// without synchronising to pick the extraction mode of the lookups it enqueues next.
+struct Feedback {
+  uint32_t keys;
+  uint32_t count[kNumGroup];
+  uint32_t seq;  // lookups finished so far (written last)
 };
 
 // Everything the role-partitioned gather needs.
@@ -73,6 +83,7 @@ struct GatherParams {
   void* out;
   const uint64_t* list[kNumGroup];
   Counters* counters;
+  Feedback* feedback;   // pinned host mirror of the last lookup's counts, or nullptr
   uint32_t row_bytes;
   uint32_t n_keys;
   int remote_cta_cap;   // most CTAs of the peer group
@@ -80,6 +91,21 @@ struct GatherParams {
   int rows_per_cta_min; // do not give a group more CTAs than count / this
   int pdl;              // launched with programmatic stream serialization
   int bulk_mask;        // bit 0: host rows, bit 1: peer rows go through bulk-async staging
+};
+
+// Everything the direct extraction (lookup and row copy in one kernel, no index lists) needs.
+struct DirectParams {
+  const void* src_base[kMaxLocation];
+  void* out;
+  TableView table;
+  Counters* counters;
+  Feedback* feedback;   // pinned host mirror of the last lookup's counts, or nullptr
+  uint32_t n_keys;
+  uint32_t row_bytes;
+  uint32_t local_loc;
+  uint32_t host_loc;
+  uint32_t host_mask;
+  uint32_t lpr_shift;   // log2 of the lanes that share one row
 };
 
 // Classification of the whole id space into ascending key lists.

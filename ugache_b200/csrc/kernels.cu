@@ -3,6 +3,7 @@
 // is not a multiple of 16).
 #include "kernels.cuh"
 
+#include <algorithm>
 #include <cstring>
 
 namespace ugc {
@@ -477,6 +478,19 @@ __device__ __forceinline__ bool copy_rows_bulk(const RecordIndex& ix, uint32_t c
   return ok_all;
 }
 
+// Counts of the lookup that just finished, into the pinned host mirror (plain stores that
+// cross PCIe; the sequence number goes last).
+__device__ __forceinline__ void publish_feedback(Feedback* f, uint32_t n_keys,
+                                                 const uint32_t cnt[kNumGroup], uint32_t seq) {
+  if (f == nullptr) return;
+  volatile Feedback* vf = f;
+  vf->keys = n_keys;
+#pragma unroll
+  for (int g = 0; g < kNumGroup; g++) vf->count[g] = cnt[g];
+  __threadfence_system();
+  vf->seq = seq;
+}
+
 template <int VEC, int LPR, int UNROLL>
 __global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
   extern __shared__ __align__(128) unsigned char dyn_smem[];
@@ -562,6 +576,202 @@ __global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
       }
       p.counters->last_keys = p.n_keys;
       p.counters->done_ctas = 0;
+      publish_feedback(p.feedback, p.n_keys, cnt, ++p.counters->seq);
+      __threadfence();
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// direct extraction: table probe and row copy in ONE kernel, no index lists
+// ------------------------------------------------------------------------------------
+// A warp owns tiles of 32 consecutive keys.  Lane l probes the table for key l of the tile;
+// the row addresses then travel by shuffle to the lane groups that copy the rows, so the
+// destination of a tile is one contiguous piece of the output.  Rows of every source (local
+// slice, peer slice over NVLink, pinned host memory) are copied where they come up, which
+// spreads the few far rows of a batch evenly over the SMs and over the kernel's duration.
+// Keys are loaded two tiles ahead and probed one tile ahead of the tile being copied.
+// Tiles are dealt to warps so that consecutive tiles land on different CTAs: every SM gets
+// the same number of rows to within one tile.
+//
+// This is the counterpart of the reference's ungrouped extraction (one extract_data over
+// DataIterMixLoc, coll_cache_lib/cache_context.cu:1295-1329, :137-159) with the table
+// lookup folded in; the grouped path above stays the better shape when many rows of a batch
+// come from the host.
+struct Probe {  // a table read in flight: one 4-slot line (probing table) or one word (flat)
+  uint32_t k0, k1, k2, k3, w0, w1, w2, w3;
+};
+
+__device__ __forceinline__ void probe_issue(const TableView& t, uint32_t key, bool valid, Probe& pr) {
+  pr.k0 = pr.k1 = pr.k2 = pr.k3 = kEmptyWord;
+  pr.w0 = pr.w1 = pr.w2 = pr.w3 = kEmptyWord;
+  if (valid) {
+    if (t.kind == kTableFlat) {
+      asm volatile("ld.global.cg.b32 %0, [%1];" : "=r"(pr.w0) : "l"(t.flat + key));
+    } else {
+      const uint2* a = t.slots + (size_t)(murmur3_32(key) & t.line_mask) * kSlotsPerLine;
+      asm volatile("ld.global.cg.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(pr.k0), "=r"(pr.w0), "=r"(pr.k1), "=r"(pr.w1), "=r"(pr.k2), "=r"(pr.w2),
+                     "=r"(pr.k3), "=r"(pr.w3)
+                   : "l"(a));
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t probe_resolve(const TableView& t, const Probe& pr, uint32_t key,
+                                                  bool valid) {
+  if (!valid || t.kind == kTableFlat) return pr.w0;
+  if (pr.k0 == key) return pr.w0;  // live slots carry the key with the top bit clear
+  if (pr.k1 == key) return pr.w1;
+  if (pr.k2 == key) return pr.w2;
+  if (pr.k3 == key) return pr.w3;
+  if (pr.k0 == kEmptyWord || pr.k1 == kEmptyWord || pr.k2 == kEmptyWord || pr.k3 == kEmptyWord)
+    return kEmptyWord;  // a never-used slot ends the search
+  return probe_rest(t.slots, t.line_mask, key, murmur3_32(key) & t.line_mask);
+}
+
+// Key `lane` of tile `tl`; ids outside [0, num_keys) are counted and dropped.
+template <typename KeyT>
+__device__ __forceinline__ void fetch_key(const KeyT* __restrict__ keys, uint32_t tl, uint32_t n_tiles,
+                                          uint32_t n_keys, uint64_t num_keys, uint32_t lane,
+                                          uint32_t& key, bool& valid, uint32_t& bad) {
+  const uint32_t idx = (tl << 5) + lane;
+  valid = tl < n_tiles && idx < n_keys;
+  uint64_t k = valid ? (uint64_t)keys[idx] : 0;
+  if (k >= num_keys) {  // also catches negative int64 ids
+    valid = false;
+    bad++;
+    k = 0;
+  }
+  key = (uint32_t)k;
+}
+
+template <typename KeyT, int VEC>
+__global__ void __launch_bounds__(kBlock, 4) extract_direct_kernel(const KeyT* __restrict__ keys,
+                                                                  DirectParams p) {
+  constexpr int UNROLL = VEC == 32 ? 2 : 4;
+  __shared__ uint32_t s_cnt[kNumGroup];
+  __shared__ const char* s_src[kMaxLocation];
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < kMaxLocation; i++) s_src[i] = static_cast<const char*>(p.src_base[i]);
+  }
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t n_warps = gridDim.x * kWarpsPerBlock;
+  const uint32_t n_tiles = (p.n_keys + 31) >> 5;
+  uint32_t tile = (threadIdx.x >> 5) * gridDim.x + blockIdx.x;
+  if (threadIdx.x < kNumGroup) s_cnt[threadIdx.x] = 0;
+
+  unsigned long long t0 = 0;
+  if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+
+  uint32_t bad = 0;
+
+  // Keys and table are not written by the extraction ahead of this one in the stream: the
+  // first two key loads and the first probe run before the dependency wait.
+  uint32_t key_cur, key_nxt;
+  bool ok_cur, ok_nxt;
+  fetch_key(keys, tile, n_tiles, p.n_keys, p.table.num_keys, lane, key_cur, ok_cur, bad);
+  fetch_key(keys, tile + n_warps, n_tiles, p.n_keys, p.table.num_keys, lane, key_nxt, ok_nxt, bad);
+  Probe pr;
+  probe_issue(p.table, key_cur, ok_cur, pr);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  uint32_t word = probe_resolve(p.table, pr, key_cur, ok_cur);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  const uint32_t lpr = 1u << p.lpr_shift;
+  const uint32_t rpi = 32u >> p.lpr_shift;       // rows per warp-wide load
+  const uint32_t sub = lane & (lpr - 1);
+  const uint32_t rsel = lane >> p.lpr_shift;
+  const uint32_t vecs_per_row = p.row_bytes / VEC;
+  uint32_t n_local = 0, n_remote = 0, n_host = 0;
+  __syncthreads();  // s_src, s_cnt
+
+  while (tile < n_tiles) {
+    // next tile's probe and the key load two tiles ahead go out before this tile's rows
+    probe_issue(p.table, key_nxt, ok_nxt, pr);
+    uint32_t key_nn;
+    bool ok_nn;
+    fetch_key(keys, tile + 2 * n_warps, n_tiles, p.n_keys, p.table.num_keys, lane, key_nn, ok_nn, bad);
+
+    // this lane's key: source address and group
+    const char* src = nullptr;
+    uint32_t group = kNumGroup;
+    if (ok_cur) {
+      uint32_t loc, off;
+      if (word == kEmptyWord) {
+        loc = p.host_loc;
+        off = key_cur & p.host_mask;
+        group = kGroupHost;
+      } else {
+        loc = word_loc(word);
+        off = word_off(word);
+        group = loc == p.local_loc ? kGroupLocal : kGroupRemote;
+      }
+      src = s_src[loc] + (size_t)off * p.row_bytes;
+    }
+    n_local += __popc(__ballot_sync(kFull, group == (uint32_t)kGroupLocal));
+    n_remote += __popc(__ballot_sync(kFull, group == (uint32_t)kGroupRemote));
+    n_host += __popc(__ballot_sync(kFull, group == (uint32_t)kGroupHost));
+
+    char* out_tile = static_cast<char*>(p.out) + (size_t)tile * 32 * p.row_bytes;
+    const unsigned long long src_bits = reinterpret_cast<unsigned long long>(src);
+    const size_t row_step = (size_t)rpi * p.row_bytes;  // between the rows of one lane group
+    for (uint32_t rb = 0; rb < 32; rb += UNROLL * rpi) {
+      const char* s[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; u++) {
+        const uint32_t r = rb + u * rpi + rsel;
+        const unsigned long long a = __shfl_sync(kFull, src_bits, r & 31);
+        s[u] = r < 32 ? reinterpret_cast<const char*>(a) : nullptr;
+      }
+      char* d0 = out_tile + (size_t)(rb + rsel) * p.row_bytes;
+      for (uint32_t c = sub; c < vecs_per_row; c += lpr) {
+        Vec<VEC> v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+          if (s[u]) ld_row(v[u], s[u] + (size_t)c * VEC);
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+          if (s[u]) st_row(d0 + u * row_step + (size_t)c * VEC, v[u]);
+      }
+    }
+
+    word = probe_resolve(p.table, pr, key_nxt, ok_nxt);
+    key_cur = key_nxt;
+    ok_cur = ok_nxt;
+    key_nxt = key_nn;
+    ok_nxt = ok_nn;
+    tile += n_warps;
+  }
+
+  if (bad) atomicAdd(&p.counters->err_key_range, (unsigned long long)bad);
+  if (lane == 0) {
+    if (n_local) atomicAdd(&s_cnt[kGroupLocal], n_local);
+    if (n_remote) atomicAdd(&s_cnt[kGroupRemote], n_remote);
+    if (n_host) atomicAdd(&s_cnt[kGroupHost], n_host);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int g = 0; g < kNumGroup; g++)
+      if (s_cnt[g]) atomicAdd(&p.counters->count[g], s_cnt[g]);
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (blockIdx.x == 0) p.counters->t_start = t0;
+    atomicMax(&p.counters->t_end[kGroupLocal], t1);  // one span for the whole kernel
+    __threadfence();
+    const uint32_t done = atomicAdd(&p.counters->done_ctas, 1u);
+    if (done == gridDim.x - 1) {
+      uint32_t cnt[kNumGroup];
+#pragma unroll
+      for (int g = 0; g < kNumGroup; g++) {
+        cnt[g] = atomicExch(&p.counters->count[g], 0u);
+        p.counters->last_count[g] = cnt[g];
+      }
+      p.counters->last_keys = p.n_keys;
+      p.counters->done_ctas = 0;
+      publish_feedback(p.feedback, p.n_keys, cnt, ++p.counters->seq);
       __threadfence();
     }
   }
@@ -969,9 +1179,44 @@ cudaError_t launch_lookup_group(const void* keys, int key_bytes, uint32_t n, con
 #undef UGC_LAUNCH_LOOKUP
 }
 
+int usable_vec_bytes(uint32_t row_bytes, int want, const void* out, const void* const* src_base,
+                     int n_src) {
+  uintptr_t bits = reinterpret_cast<uintptr_t>(out) | row_bytes;
+  for (int i = 0; i < n_src; i++) bits |= reinterpret_cast<uintptr_t>(src_base[i]);
+  if (want >= 32 && (bits & 31) == 0) return 32;
+  if (want >= 16 && (bits & 15) == 0) return 16;
+  return 4;
+}
+
+cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectParams& p_in, int grid,
+                                  int vec_bytes, bool pdl, cudaStream_t stream) {
+  if (p_in.n_keys == 0) return cudaSuccess;
+  DirectParams p = p_in;
+  const int vec = usable_vec_bytes(p.row_bytes, vec_bytes, p.out, p.src_base, kMaxLocation);
+  const int lpr = lanes_per_row(p.row_bytes, vec);
+  p.lpr_shift = 0;
+  while ((1 << p.lpr_shift) < lpr) p.lpr_shift++;
+  const int tiles = (int)((p.n_keys + 31) / 32);
+  grid = std::max(1, std::min(grid, (tiles + kWarpsPerBlock - 1) / kWarpsPerBlock));
+#define UGC_LAUNCH_DIRECT(KEYT, VEC)                                                              \
+  return launch_pdl(extract_direct_kernel<KEYT, VEC>, grid, kBlock, 0, stream, pdl,                \
+                    static_cast<const KEYT*>(keys), p)
+  if (key_bytes == 8) {
+    if (vec == 32) UGC_LAUNCH_DIRECT(long long, 32);
+    if (vec == 16) UGC_LAUNCH_DIRECT(long long, 16);
+    UGC_LAUNCH_DIRECT(long long, 4);
+  } else {
+    if (vec == 32) UGC_LAUNCH_DIRECT(uint32_t, 32);
+    if (vec == 16) UGC_LAUNCH_DIRECT(uint32_t, 16);
+    UGC_LAUNCH_DIRECT(uint32_t, 4);
+  }
+#undef UGC_LAUNCH_DIRECT
+}
+
 cudaError_t launch_gather_roles(const GatherParams& p_in, int grid, int block, int vec_bytes,
                                 cudaStream_t stream) {
   GatherParams p = p_in;
+  vec_bytes = usable_vec_bytes(p.row_bytes, vec_bytes, p.out, p.src_base, kMaxLocation);
   if (grid < 3) grid = 3;  // one CTA per source group at least
   if (block != 256 && block != 512 && block != 1024) block = 256;
   // bulk staging needs 16-byte aligned rows on both sides
@@ -984,8 +1229,8 @@ cudaError_t launch_gather_roles(const GatherParams& p_in, int grid, int block, i
       smem = 0;
     }
   }
-  if (vec_bytes == 32 && p.row_bytes % 32 == 0) return gather_dispatch_lpr<32, 2>(p, grid, block, smem, stream);
-  if (p.row_bytes % 16 == 0) return gather_dispatch_lpr<16, 4>(p, grid, block, smem, stream);
+  if (vec_bytes == 32) return gather_dispatch_lpr<32, 2>(p, grid, block, smem, stream);
+  if (vec_bytes == 16) return gather_dispatch_lpr<16, 4>(p, grid, block, smem, stream);
   return gather_dispatch_lpr<4, 4>(p, grid, block, smem, stream);
 }
 
@@ -1002,7 +1247,8 @@ cudaError_t launch_fill_scatter(const void* host_table, void* slice, const uint3
   ix.slice = static_cast<char*>(slice);
   ix.row_bytes = row_bytes;
   if (grid < 1) grid = 1;
-  if (row_bytes % 16 == 0) return fill_dispatch_lpr<16, 8>(ix, n, grid, stream);
+  const void* bases[1] = {host_table};
+  if (usable_vec_bytes(row_bytes, 16, slice, bases, 1) == 16) return fill_dispatch_lpr<16, 8>(ix, n, grid, stream);
   return fill_dispatch_lpr<4, 8>(ix, n, grid, stream);
 }
 

@@ -6,6 +6,8 @@
 //   gather_roles   one launch whose CTAs split into per-source groups sized from those
 //                  counts and the per-link CTA caps; each group copies its rows with vector
 //                  loads (local HBM, peer HBM over NVLink P2P, zero-copy host over PCIe).
+//   extract_direct lookup and row copy fused: each warp probes 32 keys and copies their rows
+//                  from whatever source holds them; no lists, one launch.
 //   fill_scatter   host rows -> cache slots (build and refresh).
 //   table_*        insert / evict / word lookup / peer-table resolve.
 //   gen_table      seeded synthetic table rows (benchmark input helper).
@@ -26,6 +28,16 @@ cudaError_t launch_lookup_group(const void* keys, int key_bytes, uint32_t n, con
 
 cudaError_t launch_gather_roles(const GatherParams& p, int grid, int block, int vec_bytes,
                                 cudaStream_t stream);
+
+// Lookup and row copy in one kernel (no index lists): out[i] = row of keys[i].  `grid` is
+// the most CTAs to use (a multiple of the SM count); fewer are launched for small batches.
+cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectParams& p, int grid,
+                                  int vec_bytes, bool pdl, cudaStream_t stream);
+
+// Widest of 32 / 16 / 4 bytes, not above `want`, that divides row_bytes and the address of
+// `out` and of every non-null source base: rows then start on a multiple of it on both sides.
+int usable_vec_bytes(uint32_t row_bytes, int want, const void* out, const void* const* src_base,
+                     int n_src);
 
 // slice[slot(j)] = host[key(j) & mask]; slots == nullptr means slot(j) = slot_base + j.
 cudaError_t launch_fill_scatter(const void* host_table, void* slice, const uint32_t* keys,

@@ -270,6 +270,10 @@ class Cache:
         check(_lib.lib().ugc_stats(self._h, replica_id, C.byref(s)))
         return {name: getattr(s, name) for name, _ in s._fields_}
 
+    def launches(self, replica_id):
+        """Kernels launched by this replica's lookups so far."""
+        return int(self.stats(replica_id)["kernel_launches"])
+
     def get_tuning(self, replica_id):
         t = _lib.Tuning()
         check(_lib.lib().ugc_get_tuning(self._h, replica_id, C.byref(t)))

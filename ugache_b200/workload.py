@@ -91,12 +91,13 @@ class Workload:
     """A small seeded case: table, hotness, placement (through `solver`) and key batches."""
 
     def __init__(self, N, dim, dtype, G, pct, alpha, n_keys, policy, seed, dedup=False,
-                 solver=None):
+                 solver=None, table_array=None):
         self.N, self.dim, self.G, self.pct = N, dim, G, pct
         self.dtype = np.dtype(dtype)
         self.alpha, self.n_keys, self.policy, self.seed, self.dedup = alpha, n_keys, policy, seed, dedup
         self.row_bytes = dim * self.dtype.itemsize
-        self.table = table(seed, N, dim, self.dtype)
+        # large cases hand in the rows from a faster generator with the same definition
+        self.table = table(seed, N, dim, self.dtype) if table_array is None else table_array
         self.rank_ids, self.rank_freqs = analytic_hotness(N, alpha)
         self.capacity = int(N * (pct + 0.001))
         if solver is None:
