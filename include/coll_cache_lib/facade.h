@@ -11,13 +11,18 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <chrono>
+#include <condition_variable>
 #include <cstdint>
+#include <cstdio>
 #include <functional>
 #include <map>
 #include <memory>
 #include <mutex>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../ugache_b200.h"
@@ -59,6 +64,122 @@ struct ContFreqBuf {
   std::vector<IdType> freq_vec;
 };
 
+// Step and epoch profile items, numbered as in the reference (coll_cache_lib/profiler.h:61-138)
+// so that values logged by an application against those names land in the same slots.
+enum LogStepItem {
+  kLogL1NumSample = 0, kLogL1NumNode, kLogL1SampleTotalTime, kLogL1SampleTime, kLogL1SendTime,
+  kLogL1RecvTime, kLogL1CopyTime, kLogL1ConvertTime, kLogL1TrainTime, kLogL1FeatureBytes,
+  kLogL1LabelBytes, kLogL1IdBytes, kLogL1GraphBytes, kLogL1MissBytes, kLogL1RemoteBytes,
+  kLogL1PrefetchAdvanced, kLogL1GetNeighbourTime, kLogL1SamplerId,
+  kLogL2ShuffleTime, kLogL2LastLayerTime, kLogL2LastLayerSize, kLogL2CoreSampleTime,
+  kLogL2IdRemapTime, kLogL2GraphCopyTime, kLogL2IdCopyTime, kLogL2ExtractTime, kLogL2FeatCopyTime,
+  kLogL2CacheCopyTime,
+  kLogL3KHopSampleCooTime, kLogL3KHopSampleKernelTime, kLogL3KHopSampleSortCooTime,
+  kLogL3KHopSampleCountEdgeTime, kLogL3KHopSampleCompactEdgesTime, kLogL3RandomWalkSampleCooTime,
+  kLogL3RandomWalkTopKTime, kLogL3RandomWalkTopKStep1Time, kLogL3RandomWalkTopKStep2Time,
+  kLogL3RandomWalkTopKStep3Time, kLogL3RandomWalkTopKStep4Time, kLogL3RandomWalkTopKStep5Time,
+  kLogL3RandomWalkTopKStep6Time, kLogL3RandomWalkTopKStep7Time, kLogL3RemapFillUniqueTime,
+  kLogL3RemapPopulateTime, kLogL3RemapMapNodeTime, kLogL3RemapMapEdgeTime,
+  kLogL3CacheGetIndexTime, KLogL3CacheCopyIndexTime, kLogL3CacheExtractMissTime,
+  kLogL3CacheCopyMissTime, kLogL3CacheCombineMissTime, kLogL3CacheCombineCacheTime,
+  kLogL3CacheCombineRemoteTime, kLogL3LabelExtractTime,
+  kNumLogStepItems
+};
+enum LogEpochItem {
+  kLogEpochSampleTime = 0, KLogEpochSampleGetCacheMissIndexTime, kLogEpochSampleSendTime,
+  kLogEpochSampleTotalTime, kLogEpochCoreSampleTime, kLogEpochSampleCooTime, kLogEpochIdRemapTime,
+  kLogEpochShuffleTime, kLogEpochSampleKernelTime, kLogEpochCopyTime, kLogEpochConvertTime,
+  kLogEpochTrainTime, kLogEpochTotalTime, kLogEpochFeatureBytes, kLogEpochMissBytes,
+  kNumLogEpochItems
+};
+
+// In-process stand-in for the reference's Profiler (coll_cache_lib/profiler.h/.cc; its
+// shared-memory report backend is not rebuilt): values per step key and per epoch, averages,
+// and the percentiles of the lookup time the reference prints in report_avg
+// (coll_cache_lib/facade.cc:570-584).
+class Profiler {
+ public:
+  void LogStep(uint64_t key, LogStepItem item, double val) {
+    if (item < 0 || item >= kNumLogStepItems) return;
+    std::lock_guard<std::mutex> lock(_mu);
+    Row& r = _steps[key];
+    r.val[item] = val;
+    r.set[item] = true;
+  }
+  void LogEpochAdd(uint64_t epoch, LogEpochItem item, double val) {
+    if (item < 0 || item >= kNumLogEpochItems) return;
+    std::lock_guard<std::mutex> lock(_mu);
+    _epochs[epoch].val[item] += val;
+    _epochs[epoch].set[item] = true;
+  }
+  bool Get(uint64_t key, LogStepItem item, double* out) {
+    std::lock_guard<std::mutex> lock(_mu);
+    auto it = _steps.find(key);
+    if (it == _steps.end() || !it->second.set[item]) return false;
+    *out = it->second.val[item];
+    return true;
+  }
+  void ReportStep(uint64_t key) {
+    std::lock_guard<std::mutex> lock(_mu);
+    auto it = _steps.find(key);
+    if (it == _steps.end()) return;
+    std::printf("[Step %llu]", (unsigned long long)key);
+    for (int i = 0; i < kNumLogStepItems; i++)
+      if (it->second.set[i]) std::printf(" item%d=%.6g", i, it->second.val[i]);
+    std::printf("\n");
+    std::fflush(stdout);
+  }
+  // Averages over the steps whose key is >= first_key, then percentiles of the lookup time.
+  void ReportStepAverage(uint64_t first_key = 0) {
+    std::lock_guard<std::mutex> lock(_mu);
+    double sum[kNumLogStepItems] = {0};
+    size_t cnt[kNumLogStepItems] = {0};
+    std::vector<double> copy;
+    for (auto& kv : _steps) {
+      if (kv.first < first_key) continue;
+      for (int i = 0; i < kNumLogStepItems; i++)
+        if (kv.second.set[i]) {
+          sum[i] += kv.second.val[i];
+          cnt[i]++;
+          if (i == kLogL2CacheCopyTime) copy.push_back(kv.second.val[i]);
+        }
+    }
+    std::printf("[Step(average)]");
+    for (int i = 0; i < kNumLogStepItems; i++)
+      if (cnt[i]) std::printf(" item%d=%.6g", i, sum[i] / cnt[i]);
+    std::printf("\n");
+    if (!copy.empty()) {
+      std::sort(copy.begin(), copy.end());
+      const double ps[] = {50, 90, 95, 99, 99.9};
+      std::printf("tail_logl2featcopy");
+      for (double p : ps)
+        std::printf(" p%g=%.6g", p, copy[std::min(copy.size() - 1, (size_t)(p / 100.0 * copy.size()))]);
+      std::printf("\n");
+    }
+    for (auto& kv : _epochs) {
+      std::printf("[Epoch %llu]", (unsigned long long)kv.first);
+      for (int i = 0; i < kNumLogEpochItems; i++)
+        if (kv.second.set[i]) std::printf(" item%d=%.6g", i, kv.second.val[i]);
+      std::printf("\n");
+    }
+    std::fflush(stdout);
+  }
+  size_t NumSteps() {
+    std::lock_guard<std::mutex> lock(_mu);
+    return _steps.size();
+  }
+
+ private:
+  static constexpr int kRowItems =
+      (int)kNumLogStepItems > (int)kNumLogEpochItems ? (int)kNumLogStepItems : (int)kNumLogEpochItems;
+  struct Row {
+    double val[kRowItems] = {0};
+    bool set[kRowItems] = {false};
+  };
+  std::mutex _mu;
+  std::map<uint64_t, Row> _steps, _epochs;
+};
+
 // The few static settings of the reference's RunConfig this path reads
 // (coll_cache_lib/run_config.h:30-111).
 struct RunConfig {
@@ -66,6 +187,9 @@ struct RunConfig {
   static int& cache_policy() { static int v = UGC_POLICY_INTUITIVE; return v; }
   static std::vector<int>& device_id_list() { static std::vector<int> v; return v; }
   static uint32_t& max_batch() { static uint32_t v = 1u << 21; return v; }
+  // step keys are epoch * steps_per_epoch + step (coll_cache_lib/run_config.h)
+  static uint64_t& num_global_step_per_epoch() { static uint64_t v = 1; return v; }
+  static uint64_t& num_epoch() { static uint64_t v = 1; return v; }
 };
 
 }  // namespace common
@@ -75,9 +199,64 @@ using namespace common;
 class CollCache : public std::enable_shared_from_this<CollCache> {
  public:
   CollCache(BarHandle process_barrier, BarHandle replica_barrier)
-      : _process_barrier(process_barrier), _replica_barrier(replica_barrier) {}
+      : _process_barrier(process_barrier), _replica_barrier(replica_barrier),
+        _profiler(std::make_shared<Profiler>()) {}
   ~CollCache() {
     if (_ctx) ugc_destroy(_ctx);
+  }
+
+  // The two-call form of the reference (coll_cache_lib/facade.h:47-53, facade.cc:38-72): `solve`
+  // fixes the placement from a hotness ranking, `build` then builds every replica of this
+  // process, one thread per replica, each with the allocator `allocator_builder` returns for it.
+  void solve(IdType* ranking_nodes_list_ptr, IdType* ranking_nodes_freq_list_ptr, IdType num_node) {
+    _solve_ids.assign(ranking_nodes_list_ptr, ranking_nodes_list_ptr + num_node);
+    if (ranking_nodes_freq_list_ptr)
+      _solve_freqs.assign(ranking_nodes_freq_list_ptr, ranking_nodes_freq_list_ptr + num_node);
+    else
+      _solve_freqs.clear();
+  }
+  void build(std::function<std::function<MemHandle(size_t)>(int)> allocator_builder, void* cpu_data,
+             DataType dtype, size_t dim, double cache_percentage, StreamHandle stream = nullptr) {
+    if (_solve_ids.empty()) throw std::runtime_error("CollCache::build: call solve() first");
+    const int G = RunConfig::num_device();
+    // the replica barrier handed to the constructor belongs to the caller's own threads; the
+    // builder threads of this call meet at a barrier of their own
+    struct LocalBarrier : ExternalBarrierHandler {
+      explicit LocalBarrier(int n) : n(n) {}
+      void Wait() override {
+        std::unique_lock<std::mutex> lock(mu);
+        const uint64_t gen = generation;
+        if (++waiting == n) {
+          waiting = 0;
+          generation++;
+          cv.notify_all();
+        } else {
+          cv.wait(lock, [&] { return generation != gen; });
+        }
+      }
+      int n, waiting = 0;
+      uint64_t generation = 0;
+      std::mutex mu;
+      std::condition_variable cv;
+    };
+    BarHandle saved = _replica_barrier;
+    _replica_barrier = std::make_shared<LocalBarrier>(G);
+    std::vector<std::thread> builders;
+    std::vector<std::string> errors(G);
+    for (int r = 0; r < G; r++)
+      builders.emplace_back([&, r] {
+        try {
+          build_v2(r, _solve_ids.data(), _solve_freqs.empty() ? nullptr : _solve_freqs.data(),
+                   (IdType)_solve_ids.size(), allocator_builder(r), cpu_data, dtype, dim,
+                   cache_percentage, stream);
+        } catch (const std::exception& e) {
+          errors[r] = e.what();
+        }
+      });
+    for (auto& t : builders) t.join();
+    _replica_barrier = saved;
+    for (auto& e : errors)
+      if (!e.empty()) throw std::runtime_error("CollCache::build: " + e);
   }
 
   void build_v2(int replica_id, IdType* ranking_nodes_list_ptr, IdType* ranking_nodes_freq_list_ptr,
@@ -90,6 +269,7 @@ class CollCache : public std::enable_shared_from_this<CollCache> {
       cfg.num_device = G;
       cfg.num_total_item = num_node;
       cfg.row_bytes = (uint32_t)(dim * GetDataTypeBytes(dtype));
+      _row_bytes = cfg.row_bytes;
       cfg.cache_percentage = cache_percentage;
       cfg.max_batch = RunConfig::max_batch();
       cfg.alloc = &CollCache::alloc_tramp;
@@ -124,12 +304,28 @@ class CollCache : public std::enable_shared_from_this<CollCache> {
   }
 
   // Returns after the rows are in `output` (the reference synchronises its internal streams).
+  // The time of the call goes to the step log under kLogL2CacheCopyTime as in the reference
+  // (coll_cache_lib/facade.cc:85-87); the phase times the reference logs inside its extraction
+  // (index building, then the copy from each kind of source, cache_context.cu:1662-1679) come
+  // from the device clock of the kernels, and the byte counts from the per-source row counts.
   void lookup(int replica_id, const IdType* nodes, const size_t num_nodes, void* output,
               StreamHandle stream, uint64_t step_key) {
-    (void)step_key;
+    const auto t0 = std::chrono::steady_clock::now();
     check(ugc_lookup_u32(_ctx, replica_id, nodes, num_nodes, output, stream), "ugc_lookup_u32");
     if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess)
       throw std::runtime_error("CollCache::lookup: stream synchronise failed");
+    const double dt = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    _profiler->LogStep(step_key, kLogL2CacheCopyTime, dt);
+    ugc_stats_t st;
+    if (ugc_stats(_ctx, replica_id, &st) == UGC_OK) {
+      _profiler->LogStep(step_key, kLogL3CacheGetIndexTime, st.last_index_ns * 1e-9);
+      _profiler->LogStep(step_key, kLogL3CacheCombineMissTime, st.last_host_ns * 1e-9);
+      _profiler->LogStep(step_key, kLogL3CacheCombineRemoteTime, st.last_remote_ns * 1e-9);
+      _profiler->LogStep(step_key, kLogL3CacheCombineCacheTime, st.last_local_ns * 1e-9);
+      _profiler->LogStep(step_key, kLogL1FeatureBytes, (double)num_nodes * _row_bytes);
+      _profiler->LogStep(step_key, kLogL1MissBytes, (double)st.last_host * _row_bytes);
+      _profiler->LogStep(step_key, kLogL1RemoteBytes, (double)st.last_remote * _row_bytes);
+    }
   }
 
   void refresh(int replica_id, IdType* ranking_nodes_list_ptr, IdType* ranking_nodes_freq_list_ptr,
@@ -152,9 +348,21 @@ class CollCache : public std::enable_shared_from_this<CollCache> {
             freq_rank ? freq_rank->freq_vec.data() : nullptr, stream, foreground);
   }
 
-  void report_avg() {}
-  void report_last_epoch(uint64_t) {}
-  void report(uint64_t) {}
+  // coll_cache_lib/facade.cc:559-588
+  void report_avg() { _profiler->ReportStepAverage(0); }
+  void report_last_epoch(uint64_t epoch) {
+    _profiler->ReportStepAverage(epoch * RunConfig::num_global_step_per_epoch());
+  }
+  void report(uint64_t key) { _profiler->ReportStep(key); }
+  std::shared_ptr<Profiler> _profiler;
+
+  // for profile (coll_cache_lib/facade.h:75-81)
+  inline void set_step_profile_value(uint64_t key, LogStepItem item, double val) {
+    _profiler->LogStep(key, item, val);
+  }
+  inline void add_epoch_profile_value(uint64_t key, LogEpochItem item, double val) {
+    _profiler->LogEpochAdd(key, item, val);
+  }
 
   ugc_ctx* context() { return _ctx; }
 
@@ -191,6 +399,8 @@ class CollCache : public std::enable_shared_from_this<CollCache> {
     _num_node = num_node;
     _pct = pct;
   }
+  std::vector<IdType> _solve_ids, _solve_freqs;
+  uint32_t _row_bytes = 0;
   // the caller's allocator returns ref-counted handles; keep them until the library frees
   static void* alloc_tramp(size_t nbytes, void* user) {
     CollCache* self = static_cast<CollCache*>(user);

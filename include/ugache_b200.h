@@ -93,12 +93,15 @@ typedef struct {
   uint32_t max_batch;       /* largest key batch one lookup may carry (scratch size)   */
   int32_t register_host;    /* 1: cudaHostRegister the host table if it is not already
                                GPU-visible (coll_cache_lib/facade.cc:476)              */
-  /* Link model used to size the per-source CTA groups of the gather (the B200
-   * counterpart of coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289).  0 = default. */
+  /* Link bandwidths (GB/s) used to share the gather's CTAs out over the source groups in
+   * proportion to bytes / bandwidth (the B200 counterpart of
+   * coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289).  0 = ugc_link_desc's figure. */
   double bw_local_gbs, bw_remote_gbs, bw_host_gbs;
   int32_t gather_ctas_per_sm; /* CTAs of the gather kernel per SM; 0 = default          */
-  int32_t host_ctas;          /* most CTAs the host-row group may take; 0 = default          */
-  int32_t remote_ctas;        /* most CTAs the peer-row group may take; 0 = default          */
+  int32_t host_ctas;          /* most CTAs the host-row group may take; 0 = what keeps the
+                                 host link full by ugc_link_desc                         */
+  int32_t remote_ctas;        /* most CTAs the peer-row group may take; 0 = what keeps the
+                                 NVLink port full by ugc_link_desc                       */
   int32_t gather_vec_bytes;   /* 16 or 32 bytes per lane per load in the gather (host rows
                                  always use 16); 0 = 32 with 8 GPUs, else 16            */
   ugc_alloc_fn alloc;
@@ -121,7 +124,8 @@ typedef struct {
   int32_t table_kind;
   int32_t has_ipc;             /* 0: pointers only (same process); 1: cudaIpcMemHandle_t in
                                   the two blobs; 2: {int64 file descriptor in the owner's
-                                  process, int64 mapped size} in the two blobs -- blocks from
+                                  process, int64 mapped size, int64 token of the owner's
+                                  descriptor socket} in the two blobs -- blocks from
                                   the CUDA virtual-memory API, which the importer maps with
                                   the owner's 2 MiB pages                               */
   unsigned char slice_ipc[64];
@@ -147,6 +151,9 @@ typedef struct {
   /* device-clock time (ns) from the start of the last gather kernel until the last CTA of
      each source group was done; 0 for an empty group */
   uint64_t last_local_ns, last_remote_ns, last_host_ns;
+  uint64_t last_index_ns;      /* grouped extraction: device-clock time from the start of
+                                  the lookup kernel to the start of the gather kernel (the
+                                  index-building phase); 0 for a direct extraction        */
   uint64_t lookups_direct;     /* lookups that took the direct (one-kernel) extraction  */
   uint64_t kernel_launches;    /* kernels launched by lookups: 2 per grouped, 1 per direct */
 } ugc_stats_t;
@@ -180,6 +187,26 @@ int ugc_solve_placement(int policy, int num_device, uint64_t num_total_item,
 /* Default B200 time-per-byte ratios (local : remote : host) for the solvers, the
  * counterpart of coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289. */
 int ugc_link_model(int num_device, double* t_local, double* t_remote, double* t_cpu);
+
+/* The B200 link description behind that model, for a job of num_device GPUs and rows of
+ * row_bytes (0: bandwidth figures only): what one GPU can pull from local HBM, from all its
+ * peers together (one NVLink port through the switch) and from the host table while every GPU
+ * of the job does the same (its own PCIe link, its share of what the host side sustains for
+ * all GPUs, and the rate at which scattered pinned rows arrive), the load-to-use latencies, and
+ * from bandwidth x latency the number of gather CTAs that keeps each far link full.  The
+ * reference holds such a table per platform with SM counts per link
+ * (coll_cache_lib/coll_cache/asymm_link_desc.cc:242-392).  struct_size must be set. */
+typedef struct {
+  uint32_t struct_size;
+  int32_t num_device;
+  double bw_local_gbs, bw_remote_gbs, bw_host_gbs;
+  double lat_local_us, lat_remote_us, lat_host_us;
+  double host_rows_per_s;
+  double host_total_gbs;
+  double t_local, t_remote, t_cpu; /* time-per-byte ratios with the row-rate host term */
+  int32_t host_ctas, remote_ctas, per_peer_ctas;
+} ugc_link_desc_t;
+int ugc_link_desc(int num_device, uint32_t row_bytes, ugc_link_desc_t* out);
 
 /* Modelled cost per reader of a placement under the concurrent-source model above (shares of
  * the recorded hotness served from the local slice, from peers and from the host).  No
@@ -267,12 +294,14 @@ int ugc_lookup_i64_static(ugc_ctx* ctx, int replica_id, const int64_t* keys, siz
 int ugc_reserve_batch(ugc_ctx* ctx, int replica_id, uint32_t max_batch);
 
 /* Host-buffer form: keys and out are HOST pointers.  Returns after the rows have landed in
- * `out`.  key_bytes is 4 or 8.  Pageable buffers go through device staging copies.  A buffer
- * that is pinned and mapped for the GPU (cudaHostAlloc / cudaHostRegister with the mapped
- * flag, or ugc_host_alloc) is used in place when ugc_tuning.host_zero_copy allows it: the
- * extraction kernel reads the keys and writes the rows across PCIe itself, so rows start
- * crossing the link while others are still being fetched and no staging buffer or copy-engine
- * pass is needed. */
+ * `out`.  key_bytes is 4 or 8.  A buffer that is pinned and mapped for the GPU (cudaHostAlloc /
+ * cudaHostRegister with the mapped flag, or ugc_host_alloc) can be used in place, as
+ * ugc_tuning.host_zero_copy says: by default the kernel reads the keys across PCIe itself,
+ * while the rows are staged in device memory and leave through the copy engine (measured
+ * faster than stores from the SMs: 56 against 51 GB/s), in eight pieces for batches of 65,536
+ * keys or more so that one piece crosses PCIe while the next is being extracted.  After such
+ * a call ugc_stats' last_* fields describe the last piece only.  Pageable buffers always go
+ * through staging copies. */
 int ugc_lookup_host(ugc_ctx* ctx, int replica_id, const void* keys, int key_bytes, size_t n,
                     void* out, void* stream);
 
@@ -290,7 +319,9 @@ int ugc_lookup_host(ugc_ctx* ctx, int replica_id, const void* keys, int key_byte
  * Lookups of the same replica may be issued from another thread (on another stream) during all
  * of it, as the reference's background refresh allows: an evicted key is served from the host
  * table until it is cached again, a slot is reused only after every lookup that could still
- * name it has drained (ugc_refresh_evict ends with a device-wide wait), and a new entry becomes
+ * name it has drained (ugc_refresh_evict waits, on the host, until the replica's count of
+ * finished lookups has reached the number enqueued; no stream of the device is stalled; the
+ * reference waits on its step counter, cache_context.cu:4045-4052), and a new entry becomes
  * visible only after its row has been written (same stream, one 64-bit publish).  The phase
  * calls of one replica must come from one thread at a time.
  */
@@ -339,6 +370,13 @@ typedef struct {
   int32_t direct_ctas_per_sm;     /* CTAs of the direct extraction kernel per SM, 1..8      */
   int32_t direct_host_permille;   /* auto mode: direct while the last finished lookup took at
                                      most this many of 1000 rows from the host table        */
+  int32_t direct_tile_keys;       /* keys one warp of the direct kernel probes at a time: 8,
+                                     16 or 32; 0 = the largest that balances the warps      */
+  int32_t direct_deep;            /* direct kernel: 1 = twice the rows in flight per warp at
+                                     3 instead of 4 CTAs per SM                             */
+  int32_t gather_dynamic;         /* grouped gather: 1 = lists are handed out in chunks and a
+                                     CTA whose own list is drained takes chunks of the other
+                                     groups' lists; 0 = fixed striding inside each group     */
   int32_t host_zero_copy;         /* ugc_lookup_host with GPU-mapped pinned buffers: bit 0 the
                                      kernel reads the keys in place, bit 1 it writes the rows
                                      in place; a cleared bit selects a staging copy          */

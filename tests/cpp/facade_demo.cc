@@ -101,7 +101,7 @@ int main() {
       cudaMemcpy(dkeys, keys.data(), n * sizeof(common::IdType), cudaMemcpyHostToDevice);
       std::vector<float> got(n * dim);
       for (int round = 0; round < 2; round++) {
-        cache->lookup(r, dkeys, n, dout, stream, (uint64_t)r);
+        cache->lookup(r, dkeys, n, dout, stream, (uint64_t)(round * G + r));
         cudaMemcpy(got.data(), dout, got.size() * sizeof(float), cudaMemcpyDeviceToHost);
         for (size_t i = 0; i < n; i++)
           if (memcmp(&got[i * dim], &table[(size_t)keys[i] * dim], dim * sizeof(float)) != 0) {
@@ -121,7 +121,61 @@ int main() {
   std::vector<std::thread> ts;
   for (int r = 0; r < G; r++) ts.emplace_back(worker, r);
   for (auto& t : ts) t.join();
+
+  // profile surface of the facade: the lookups above logged their time, phase times and byte
+  // counts per step key; the application adds values of its own under the reference's item names
+  cache->set_step_profile_value(0, common::kLogL1TrainTime, 0.125);
+  cache->add_epoch_profile_value(0, common::kLogEpochTrainTime, 1.5);
+  cache->add_epoch_profile_value(0, common::kLogEpochTrainTime, 2.5);
+  double v = 0;
+  if (cache->_profiler->NumSteps() != (size_t)(2 * G)) failures++;
+  if (!cache->_profiler->Get(0, common::kLogL2CacheCopyTime, &v) || v <= 0) failures++;
+  if (!cache->_profiler->Get(1, common::kLogL1FeatureBytes, &v) || v != 5000.0 * dim * sizeof(float)) failures++;
+  if (!cache->_profiler->Get(0, common::kLogL1TrainTime, &v) || v != 0.125) failures++;
+  cache->report(0);
+  cache->report_last_epoch(0);
+  cache->report_avg();
   cache.reset();
+
+  // the two-call form: solve() fixes the placement, build() builds every replica in threads of
+  // its own with the allocator the builder returns per replica
+  {
+    auto cache2 = std::make_shared<CollCache>(nullptr, barrier);
+    cache2->solve(rank_ids.data(), rank_freqs.data(), N);
+    cache2->build(
+        [&](int r) -> std::function<common::MemHandle(size_t)> {
+          const int dev = common::RunConfig::device_id_list()[r];
+          return [dev](size_t nbytes) -> common::MemHandle {
+            auto h = std::make_shared<CudaMem>();
+            cudaSetDevice(dev);
+            if (cudaMalloc(&h->p, nbytes) != cudaSuccess) return nullptr;
+            h->n = nbytes;
+            return h;
+          };
+        },
+        table, common::kF32, dim, 0.10, nullptr);
+    const size_t n = 3000;
+    std::vector<common::IdType> keys(n);
+    for (size_t i = 0; i < n; i++) keys[i] = (common::IdType)(mix(77 + i) % N);
+    for (int r = 0; r < G; r++) {
+      cudaSetDevice(common::RunConfig::device_id_list()[r]);
+      common::IdType* dkeys;
+      float* dout;
+      cudaMalloc(&dkeys, n * sizeof(common::IdType));
+      cudaMalloc(&dout, n * dim * sizeof(float));
+      cudaMemcpy(dkeys, keys.data(), n * sizeof(common::IdType), cudaMemcpyHostToDevice);
+      cache2->lookup(r, dkeys, n, dout, nullptr, (uint64_t)r);
+      std::vector<float> got(n * dim);
+      cudaMemcpy(got.data(), dout, got.size() * sizeof(float), cudaMemcpyDeviceToHost);
+      for (size_t i = 0; i < n; i++)
+        if (memcmp(&got[i * dim], &table[(size_t)keys[i] * dim], dim * sizeof(float)) != 0) {
+          failures++;
+          break;
+        }
+      cudaFree(dkeys);
+      cudaFree(dout);
+    }
+  }
   cudaFreeHost(table);
   if (failures.load()) {
     printf("facade FAILED (%d)\n", failures.load());

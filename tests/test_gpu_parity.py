@@ -19,10 +19,17 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
-@pytest.fixture(autouse=True, params=["grouped", "direct", "auto"])
+@pytest.fixture(autouse=True, params=["grouped", "grouped_static", "direct", "auto"])
 def extract_mode(request, monkeypatch):
     """Every test of this module runs once per extraction mode (index lists + per-source CTA
     groups / one fused kernel / chosen per lookup from the previous lookup's counts)."""
+    # the two main shapes run everywhere; the other two on the tests that exercise the gather
+    # and the mode switch (keeps the suite short)
+    wide = {"test_golden_cases_bit_exact", "test_ragged_batch_sizes", "test_auto_mode_follows_the_host_share",
+            "test_duplicates_and_single_source_batches", "test_out_of_range_keys_are_counted_and_skipped",
+            "test_unaligned_output_and_host_table", "test_refresh_keeps_results_identical"}
+    if request.param in ("auto", "grouped_static") and request.node.originalname not in wide:
+        pytest.skip("covered by the grouped and direct runs")
     monkeypatch.setenv("UGC_EXTRACT_MODE", request.param)
     return request.param
 
@@ -584,7 +591,7 @@ def test_auto_mode_follows_the_host_share(built_lib, extract_mode):
 def test_golden_cases_at_configuration_sizes(built_lib, golden_cases_large, extract_mode):
     """Full-size cases: 1 M x 128 fp32 with every row on the host and one deduplicated batch of
     65,536 draws; 2 M x 64 fp16 (128-byte rows) on 4 replicas with 20 % cached each."""
-    if extract_mode == "auto":
+    if extract_mode in ("auto", "grouped_static"):
         pytest.skip("grouped and direct cover it")
     for case in golden_cases_large:
         w = case_workload(case)

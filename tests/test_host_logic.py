@@ -220,3 +220,26 @@ def test_lookup_unique_helper_reassembles_the_batch(built_lib):
         assert rows.shape == (u.numel(), dim)
         assert torch.equal(u, torch.unique(keys)) and (u.numel() < 2 or bool((u[1:] > u[:-1]).all()))
         assert torch.equal(rows[inverse], table[keys])
+
+
+def test_link_description_follows_the_number_of_gpus(built_lib):
+    """The B200 link description: no peers with one GPU; the host share per GPU shrinks as more
+    GPUs read the host side together; small rows are bound by the scattered-row rate; the CTA
+    budgets of the far links follow bandwidth x latency."""
+    from ugache_b200 import runtime as rt
+    d1, d2, d8 = (rt.link_desc(g, 512) for g in (1, 2, 8))
+    assert d1["bw_remote_gbs"] == 0 and d2["bw_remote_gbs"] == d8["bw_remote_gbs"] == 900
+    assert d1["bw_host_gbs"] >= d2["bw_host_gbs"] >= d8["bw_host_gbs"] > 0
+    assert d8["bw_host_gbs"] <= d8["host_total_gbs"] / 8 + 1e-9
+    small = rt.link_desc(1, 128)
+    assert abs(small["bw_host_gbs"] - small["host_rows_per_s"] * 128 / 1e9) < 1e-9   # row-rate bound
+    assert rt.link_desc(1, 0)["bw_host_gbs"] == 64                                   # bandwidth only
+    # Little's law: CTAs = 2 * ceil(bw * latency / 16 KiB in flight per CTA)
+    import math
+    assert d8["remote_ctas"] == 2 * math.ceil(900e3 * d8["lat_remote_us"] / 16384)
+    assert d8["host_ctas"] == 2 * math.ceil(64e3 * d8["lat_host_us"] / 16384)
+    assert d8["per_peer_ctas"] == d8["remote_ctas"] // 7
+    assert d8["t_cpu"] > d1["t_cpu"] > d8["t_remote"] > d8["t_local"] == 1.0
+    tl, tr, tc = rt.link_model(8, 512)
+    assert (tl, tr, tc) == (d8["t_local"], d8["t_remote"], d8["t_cpu"])
+    assert rt.link_model(8) == (1.0, 8000.0 / 900.0, 8000.0 / 64.0)                  # solver defaults

@@ -134,3 +134,35 @@ def test_fork_shared_barrier(built_lib, tmp_path):
     p = subprocess.run([sys.executable, str(script)], env=dict(os.environ, UGC_BARRIER_TIMEOUT_S="20"),
                        capture_output=True, text=True, timeout=120)
     assert p.returncode == 0, p.stdout + p.stderr
+
+
+FAILING_PEER = textwrap.dedent("""
+    import os, sys, time
+    sys.path.insert(0, %(root)r)
+    from ugache_b200.collcache import common     # loaded before the fork: shared control block
+    b = common._basics
+    b.config({"cache_percentage": 0.1, "_cache_policy": 12, "num_device": 2,
+              "num_global_step_per_epoch": 1, "num_epoch": 1, "num_total_item": 1000,
+              "omp_thread_num": 2})
+    pid = os.fork()
+    if pid == 0:
+        # this replica fails inside a call all replicas make together (no cache was built)
+        rc = b.C_LIB_CTYPES.coll_cache_refresh(1, None)
+        os._exit(0 if rc != 0 else 3)
+    t0 = time.time()
+    rc = b.C_LIB_CTYPES.coll_cache_train_barrier()       # would wait 60 s for the failed peer
+    dt = time.time() - t0
+    st = b.wait_one_child()
+    print("rc", rc, "dt", dt, "child", st)
+    sys.exit(0 if (rc == 5 and dt < 20 and st == 0) else 1)   # UGC_ERR_STATE, promptly
+""")
+
+
+def test_failure_of_one_replica_releases_the_others_promptly(built_lib, tmp_path):
+    """A replica that fails in a collective call flags the shared control block, so replicas
+    waiting at a barrier return an error at once instead of sitting out the time limit."""
+    script = tmp_path / "failing_peer.py"
+    script.write_text(FAILING_PEER % {"root": ROOT})
+    p = subprocess.run([sys.executable, str(script)], env=dict(os.environ, UGC_BARRIER_TIMEOUT_S="60"),
+                       capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stdout + p.stderr

@@ -77,6 +77,7 @@ class Stats(C.Structure):
         ("last_local_ns", C.c_uint64),
         ("last_remote_ns", C.c_uint64),
         ("last_host_ns", C.c_uint64),
+        ("last_index_ns", C.c_uint64),
         ("lookups_direct", C.c_uint64),
         ("kernel_launches", C.c_uint64),
     ]
@@ -96,7 +97,23 @@ class Tuning(C.Structure):
         ("extract_mode", C.c_int32),
         ("direct_ctas_per_sm", C.c_int32),
         ("direct_host_permille", C.c_int32),
+        ("direct_tile_keys", C.c_int32),
+        ("direct_deep", C.c_int32),
+        ("gather_dynamic", C.c_int32),
         ("host_zero_copy", C.c_int32),
+    ]
+
+
+class LinkDesc(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("num_device", C.c_int32),
+        ("bw_local_gbs", C.c_double), ("bw_remote_gbs", C.c_double), ("bw_host_gbs", C.c_double),
+        ("lat_local_us", C.c_double), ("lat_remote_us", C.c_double), ("lat_host_us", C.c_double),
+        ("host_rows_per_s", C.c_double),
+        ("host_total_gbs", C.c_double),
+        ("t_local", C.c_double), ("t_remote", C.c_double), ("t_cpu", C.c_double),
+        ("host_ctas", C.c_int32), ("remote_ctas", C.c_int32), ("per_peer_ctas", C.c_int32),
     ]
 
 
@@ -120,6 +137,7 @@ SIGNATURES = {
     "ugc_solve_placement": (_I, [_I, _I, _U64, _P, _P, _D, _D, _D, _D, _P, _P, _P, _P,
                                  C.POINTER(_I)]),
     "ugc_link_model": (_I, [_I, C.POINTER(_D), C.POINTER(_D), C.POINTER(_D)]),
+    "ugc_link_desc": (_I, [_I, C.c_uint32, C.POINTER(LinkDesc)]),
     "ugc_placement_cost": (_I, [_I, _U64, _P, _P, _P, _P, _I, _D, _D, _D, _P]),
     "ugc_set_placement": (_I, [_P, _P, _P, _P, _P, _I]),
     "ugc_classify_keys": (_I, [_P, _I, _P, _P]),

@@ -3,8 +3,8 @@
 // aborts: every entry point returns a ugc_status and records a per-thread message.
 #include <cuda.h>
 #include <cuda_runtime.h>
-#include <sys/prctl.h>
 #include <sys/socket.h>
+#include <sys/time.h>
 #include <sys/un.h>
 #include <sys/syscall.h>
 #include <unistd.h>
@@ -15,7 +15,6 @@
 #include <cstddef>
 #include <cstdio>
 #include <cstring>
-#include <deque>
 #include <map>
 #include <mutex>
 #include <new>
@@ -324,11 +323,25 @@ int dev_block_export_fd(void* p) {
 std::set<int> g_served_fds;
 bool g_fd_server_running = false;
 
-void fd_socket_name(int64_t pid, sockaddr_un* addr, socklen_t* len) {
+uint64_t g_fd_token = 0;   // random per process; part of the socket name, carried in the handle
+std::string g_fd_server_error;
+
+// Abstract-namespace name: uid, pid and a random token, so that processes in different pid
+// namespaces that share a network namespace do not collide and the name cannot be guessed.
+void fd_socket_name(int64_t pid, uint64_t token, sockaddr_un* addr, socklen_t* len) {
   memset(addr, 0, sizeof(*addr));
   addr->sun_family = AF_UNIX;
-  int n = snprintf(addr->sun_path + 1, sizeof(addr->sun_path) - 1, "ugc_fd_%lld", (long long)pid);
+  int n = snprintf(addr->sun_path + 1, sizeof(addr->sun_path) - 1, "ugc_fd_%u_%lld_%016llx",
+                   (unsigned)geteuid(), (long long)pid, (unsigned long long)token);
   *len = (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + n);
+}
+
+void set_socket_timeouts(int fd, int seconds) {
+  timeval tv;
+  tv.tv_sec = seconds;
+  tv.tv_usec = 0;
+  setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+  setsockopt(fd, SOL_SOCKET, SO_SNDTIMEO, &tv, sizeof(tv));
 }
 
 void fd_server_loop(int listen_fd) {
@@ -345,6 +358,7 @@ void fd_server_loop(int listen_fd) {
       close(c);
       continue;
     }
+    set_socket_timeouts(c, 2);  // a client that stalls must not block the importers behind it
     int wanted = -1;
     if (read(c, &wanted, sizeof(wanted)) == (ssize_t)sizeof(wanted)) {
       bool ok;
@@ -369,36 +383,53 @@ void fd_server_loop(int listen_fd) {
         cm->cmsg_len = CMSG_LEN(sizeof(int));
         memcpy(CMSG_DATA(cm), &wanted, sizeof(int));
       }
-      sendmsg(c, &msg, 0);
+      sendmsg(c, &msg, MSG_NOSIGNAL);  // a client that left must not raise SIGPIPE here
     }
     close(c);
   }
 }
 
-// Called by the owner when it exports descriptor `fd`.
-void fd_server_publish(int fd) {
+// Called by the owner when it exports descriptor `fd`.  Returns false (and keeps a message)
+// if the descriptor socket could not be set up; the pidfd route may still work then.
+bool fd_server_publish(int fd) {
   std::lock_guard<std::mutex> lock(g_vmm_mu);
   g_served_fds.insert(fd);
-  if (g_fd_server_running) return;
+  if (g_fd_server_running) return true;
+  if (g_fd_token == 0) {
+    uint64_t t = 0;
+    FILE* f = fopen("/dev/urandom", "rb");
+    if (f) {
+      if (fread(&t, sizeof(t), 1, f) != 1) t = 0;
+      fclose(f);
+    }
+    if (t == 0) t = ((uint64_t)getpid() << 32) ^ (uint64_t)reinterpret_cast<uintptr_t>(&t) ^ 0x9e3779b97f4a7c15ull;
+    g_fd_token = t;
+  }
   int s = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
-  if (s < 0) return;
+  if (s < 0) {
+    g_fd_server_error = std::string("descriptor socket: socket() failed: ") + strerror(errno);
+    return false;
+  }
   sockaddr_un addr;
   socklen_t len;
-  fd_socket_name((int64_t)getpid(), &addr, &len);
+  fd_socket_name((int64_t)getpid(), g_fd_token, &addr, &len);
   if (bind(s, reinterpret_cast<sockaddr*>(&addr), len) != 0 || listen(s, 16) != 0) {
+    g_fd_server_error = std::string("descriptor socket: bind/listen failed: ") + strerror(errno);
     close(s);
-    return;
+    return false;
   }
   g_fd_server_running = true;
   std::thread(fd_server_loop, s).detach();
+  return true;
 }
 
-int fd_from_socket(int64_t pid, int fd) {
+int fd_from_socket(int64_t pid, uint64_t token, int fd) {
   int s = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
   if (s < 0) return -1;
+  set_socket_timeouts(s, 5);
   sockaddr_un addr;
   socklen_t len;
-  fd_socket_name(pid, &addr, &len);
+  fd_socket_name(pid, token, &addr, &len);
   int got = -1;
   if (connect(s, reinterpret_cast<sockaddr*>(&addr), len) == 0 &&
       write(s, &fd, sizeof(fd)) == (ssize_t)sizeof(fd)) {
@@ -421,8 +452,10 @@ int fd_from_socket(int64_t pid, int fd) {
   return got;
 }
 
-// A duplicate, in this process, of descriptor `fd` of process `pid`.
-int steal_fd(int64_t pid, int fd) {
+// A duplicate, in this process, of descriptor `fd` of process `pid`: straight out of the owner
+// where the kernel's ptrace policy lets this process do that (same user and an unrestricted
+// ptrace scope, or a privileged importer), else over the owner's descriptor socket.
+int steal_fd(int64_t pid, uint64_t token, int fd) {
   if (!getenv("UGC_NO_PIDFD")) {
 #if defined(SYS_pidfd_open) && defined(SYS_pidfd_getfd)
     int pidfd = (int)syscall(SYS_pidfd_open, (pid_t)pid, 0);
@@ -433,14 +466,14 @@ int steal_fd(int64_t pid, int fd) {
     }
 #endif
   }
-  return fd_from_socket(pid, fd);
+  return fd_from_socket(pid, token, fd);
 }
 
 // Maps another process' exported block for `device`.
-void* dev_import(int64_t pid, int fd, size_t size, int device) {
+void* dev_import(int64_t pid, uint64_t token, int fd, size_t size, int device) {
   const VmmApi& a = vmm_api();
   if (!a.ok) return nullptr;
-  int local = steal_fd(pid, fd);
+  int local = steal_fd(pid, token, fd);
   if (local < 0) return nullptr;
   CUmemGenericAllocationHandle h;
   CUresult rc = a.import_handle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(local)),
@@ -502,7 +535,19 @@ struct Replica {
   DevBuf stage_a, stage_b;
   // bookkeeping mirrored from the reference's CacheEntryManager
   // (coll_cache_lib/cuda/cache_hashtable.cuh:548-557): keys per source, free slots
-  std::deque<uint32_t> free_slots;
+  // free cache rows: a ring of slot numbers in device memory, `capacity` entries; evicted rows
+  // are appended at the tail, new rows take slots from the head
+  // (coll_cache_lib/cuda/cache_hashtable.cuh:637-645 keeps the same order on the host)
+  uint32_t* free_ring = nullptr;
+  uint64_t free_head = 0, free_count = 0;
+  bool static_used = false;                // lookups through the fixed scratch array were issued
+  int refresh_fill_ctas = 20;              // grid of the refresh-time fill kernel
+  float t_byte[kNumGroup] = {0, 0, 0};     // seconds per byte (any common scale) per source group
+  int gather_dynamic = 1;
+  cudaStream_t copy_stream = nullptr;      // host-buffer lookups: rows leave on this stream
+  std::vector<cudaEvent_t> copy_events;
+  int direct_tile_shift = 0;               // 0: chosen per launch
+  int direct_deep = 0;
   uint64_t n_local = 0;                    // rows stored here
   uint64_t n_remote = 0;                   // keys read from peers
   // Device-resident placement view of this reader and the key lists of the last
@@ -529,12 +574,12 @@ struct Replica {
   // the host-row share of the last finished lookup, read from the pinned mirror below
   int extract_mode = UGC_EXTRACT_AUTO;
   int direct_grid = 0;
-  double direct_host_share = 0.004;
+  double direct_host_share = 0.05;
   Feedback* feedback = nullptr;      // pinned host memory, written by the kernels
   Feedback* feedback_dev = nullptr;  // the same memory as the device addresses it
   uint64_t lookups_direct = 0;
   uint64_t kernel_launches = 0;
-  int host_zero_copy = 3;
+  int host_zero_copy = 1;  // keys read in place; rows staged (the copy engine beats SM stores over PCIe)
   // per-kernel profiling (three events per lookup)
   std::vector<cudaEvent_t> prof_events;
   size_t prof_used = 0;
@@ -764,12 +809,15 @@ int upload_n2b(ugc_ctx* c, const Placement& p, uint32_t** dst, cudaStream_t s) {
 void release_replica(ugc_ctx* c, Replica* r) {
   if (r->device >= 0) cudaSetDevice(r->device);
   for (cudaEvent_t e : r->prof_events) cudaEventDestroy(e);
+  for (cudaEvent_t e : r->copy_events) cudaEventDestroy(e);
+  if (r->copy_stream) cudaStreamDestroy(r->copy_stream);
   for (int i = 0; i < r->n_ipc_opened; i++)
     if (!dev_block_free(r->ipc_opened[i])) cudaIpcCloseMemHandle(r->ipc_opened[i]);
   ctx_free_shared(c, r->slice);
   ctx_free_shared(c, r->table_mem);
   for (auto& l : r->list) ctx_free(c, l);
   ctx_free(c, r->counters);
+  ctx_free(c, r->free_ring);
   ctx_free(c, r->hot_counts);
   ctx_free(c, r->n2b_dev);
   ctx_free(c, r->n2b_next);
@@ -796,6 +844,8 @@ GatherParams gather_params(ugc_ctx* c, Replica* r, void* out, uint32_t n) {
   p.remote_cta_cap = r->remote_ctas;
   p.host_cta_cap = r->host_ctas;
   p.rows_per_cta_min = 32;
+  for (int g = 0; g < kNumGroup; g++) p.t_byte[g] = r->t_byte[g];
+  p.dynamic = r->gather_dynamic;
   p.bulk_mask = r->bulk_mask;
   p.pdl = (r->pdl & 2) ? 1 : 0;
   return p;
@@ -810,6 +860,31 @@ void* mapped_device_pointer(const void* host) {
   }
   if (attr.type != cudaMemoryTypeHost || !attr.devicePointer) return nullptr;
   return attr.devicePointer;
+}
+
+// Waits until every lookup of this replica enqueued so far has finished on the GPU.  The
+// kernels publish the number of finished lookups in the pinned mirror, so this polls host
+// memory and stalls no stream (the reference waits for the trainer's step counter in the same
+// spirit, coll_cache_lib/cache_context.cu:4045-4052).  Bounded: after `limit_s` seconds, or
+// when lookups were issued that do not report there, it falls back to a device-wide wait.
+int drain_lookups(Replica* r, double limit_s = 20.0) {
+  const uint32_t target = (uint32_t)__atomic_load_n(&r->lookups, __ATOMIC_SEQ_CST);
+  if (r->feedback && !r->static_used) {
+    const volatile Feedback* f = r->feedback;
+    timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (uint64_t spin = 0;; spin++) {
+      if ((int32_t)(f->seq - target) >= 0) return UGC_OK;
+      if ((spin & 63) == 63) {
+        timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        if ((t1.tv_sec - t0.tv_sec) + (t1.tv_nsec - t0.tv_nsec) * 1e-9 > limit_s) break;
+        usleep(20);
+      }
+    }
+  }
+  UGC_CUDA(cudaDeviceSynchronize());
+  return UGC_OK;
 }
 
 uint32_t host_mask_value(int empty_feat) {
@@ -838,6 +913,8 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
     return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
   const bool prof = r->prof_on && r->prof_used + 3 <= r->prof_events.size();
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used], s));
+  // counted before the launch: drain_lookups() must never miss a lookup that could be running
+  __atomic_fetch_add(&r->lookups, 1, __ATOMIC_SEQ_CST);
   if (choose_direct(r)) {
     if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 1], s));
     DirectParams d{};
@@ -851,12 +928,13 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
     d.local_loc = (uint32_t)r->id;
     d.host_loc = (uint32_t)c->cfg.num_device;
     d.host_mask = host_mask_value(c->cfg.empty_feat);
-    UGC_CUDA(launch_extract_direct(keys, key_bytes, d, r->direct_grid, r->vec_bytes, (r->pdl & 1) != 0, s));
+    d.tile_shift = (uint32_t)r->direct_tile_shift;
+    UGC_CUDA(launch_extract_direct(keys, key_bytes, d, r->direct_grid, r->vec_bytes, r->direct_deep != 0,
+                                   (r->pdl & 1) != 0, s));
     if (prof) {
       UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 2], s));
       r->prof_used += 3;
     }
-    r->lookups++;
     r->lookups_direct++;
     r->kernel_launches += 1;
     return UGC_OK;
@@ -871,7 +949,6 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
     UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 2], s));
     r->prof_used += 3;
   }
-  r->lookups++;
   r->kernel_launches += 2;
   return UGC_OK;
 }
@@ -1029,6 +1106,28 @@ int ugc_placement_cost(int num_device, uint64_t N, const uint32_t* rank_ids, con
   return UGC_OK;
 }
 
+int ugc_link_desc(int num_device, uint32_t row_bytes, ugc_link_desc_t* out) {
+  if (!out || out->struct_size != sizeof(ugc_link_desc_t)) return fail(UGC_ERR_INVALID, "bad ugc_link_desc_t");
+  if (num_device < 1 || num_device > UGC_MAX_DEVICE) return fail(UGC_ERR_INVALID, "num_device must be 1..%d", UGC_MAX_DEVICE);
+  const LinkDesc d = b200_link_desc(num_device, row_bytes);
+  out->num_device = d.num_device;
+  out->bw_local_gbs = d.bw_local_gbs;
+  out->bw_remote_gbs = d.bw_remote_gbs;
+  out->bw_host_gbs = d.bw_host_gbs;
+  out->lat_local_us = d.lat_local_us;
+  out->lat_remote_us = d.lat_remote_us;
+  out->lat_host_us = d.lat_host_us;
+  out->host_rows_per_s = d.host_rows_per_s;
+  out->host_total_gbs = d.host_total_gbs;
+  out->t_local = d.t_local;
+  out->t_remote = d.t_remote;
+  out->t_cpu = d.t_cpu;
+  out->host_ctas = d.host_ctas;
+  out->remote_ctas = d.remote_ctas;
+  out->per_peer_ctas = d.per_peer_ctas;
+  return UGC_OK;
+}
+
 int ugc_link_model(int num_device, double* t_local, double* t_remote, double* t_cpu) {
   if (!t_local || !t_remote || !t_cpu) return fail(UGC_ERR_INVALID, "null output");
   b200_link_model(num_device, t_local, t_remote, t_cpu);
@@ -1106,9 +1205,23 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
     if (!strcmp(m, "grouped")) r->extract_mode = UGC_EXTRACT_GROUPED;
     if (!strcmp(m, "direct")) r->extract_mode = UGC_EXTRACT_DIRECT;
     if (!strcmp(m, "auto")) r->extract_mode = UGC_EXTRACT_AUTO;
+    if (!strcmp(m, "grouped_static")) {  // grouped with fixed striding instead of chunk hand-out
+      r->extract_mode = UGC_EXTRACT_GROUPED;
+      r->gather_dynamic = 0;
+    }
   }
-  r->host_ctas = c->cfg.host_ctas > 0 ? c->cfg.host_ctas : std::max(2, r->sm_count);
-  r->remote_ctas = c->cfg.remote_ctas > 0 ? c->cfg.remote_ctas : std::max(2, r->sm_count * per_sm / 2);
+  // Far-source CTA budgets and the per-group time-per-byte come from the link description:
+  // bandwidth x latency gives the CTAs that keep a link full, bytes / bandwidth the share of
+  // the launch each group gets.
+  {
+    const LinkDesc ld = b200_link_desc(G, c->cfg.row_bytes, c->cfg.bw_local_gbs, c->cfg.bw_remote_gbs,
+                                       c->cfg.bw_host_gbs);
+    r->host_ctas = c->cfg.host_ctas > 0 ? c->cfg.host_ctas : ld.host_ctas;
+    r->remote_ctas = c->cfg.remote_ctas > 0 ? c->cfg.remote_ctas : ld.remote_ctas;
+    r->t_byte[kGroupLocal] = (float)(1.0 / ld.bw_local_gbs);
+    r->t_byte[kGroupRemote] = ld.bw_remote_gbs > 0 ? (float)(1.0 / ld.bw_remote_gbs) : 0.0f;
+    r->t_byte[kGroupHost] = (float)(1.0 / ld.bw_host_gbs);
+  }
   // 32-byte loads win when almost every row comes from HBM (8 GPUs, 458 host rows per batch:
   // 36.5 us per step against 45); with more host rows per batch 16-byte loads were faster
   // (1 GPU: 113 vs 133 us, 2 GPUs: 84 vs 110 us, 4 GPUs: 54 vs 61 us).
@@ -1180,7 +1293,7 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
     return bail(fail(UGC_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(cudaGetLastError())));
 
   // 4. fill: slice[j] = host[local_keys[j]]
-  if (launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, replica_id), nullptr, 0,
+  if (launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, replica_id), SlotView{nullptr, 0, 0},
                           (uint32_t)n_local, c->cfg.row_bytes, c->cfg.empty_feat, r->sm_count * 2,
                           s) != cudaSuccess)
     return bail(fail(UGC_ERR_CUDA, "fill launch failed: %s", cudaGetErrorString(cudaGetLastError())));
@@ -1192,14 +1305,19 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
   const uint64_t max_entries = std::min<uint64_t>(N, (uint64_t)G * r->capacity);
   if ((rc = alloc_table(c, r, n_local + n_remote, std::max(n_local + n_remote, max_entries), s)) != UGC_OK)
     return bail(rc);
-  if (launch_table_insert(r->table, list_ptr(r, replica_id), nullptr, 0,
+  if (launch_table_insert(r->table, list_ptr(r, replica_id), SlotView{nullptr, 0, 0},
                           (uint32_t)replica_id, (uint32_t)n_local, r->counters, s) != cudaSuccess)
     return bail(fail(UGC_ERR_CUDA, "insert launch failed: %s", cudaGetErrorString(cudaGetLastError())));
   if ((rc = check_table_errors(r, s, "build insert")) != UGC_OK) return bail(rc);
 
   // 6. free slots: [n_local, capacity)  (coll_cache_lib/cache_context.cu:2577-2585)
-  r->free_slots.clear();
-  for (uint64_t o = n_local; o < r->capacity; o++) r->free_slots.push_back((uint32_t)o);
+  r->free_ring = static_cast<uint32_t*>(ctx_alloc(c, std::max<size_t>(r->capacity, 1) * sizeof(uint32_t)));
+  if (!r->free_ring) return bail(fail(UGC_ERR_NOMEM, "free-slot ring allocation failed"));
+  r->free_head = 0;
+  r->free_count = r->capacity - n_local;
+  if (launch_iota(r->free_ring, (uint32_t)n_local, (uint32_t)r->free_count, s) != cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess)
+    return bail(fail(UGC_ERR_CUDA, "free-slot ring set-up failed: %s", cudaGetErrorString(cudaGetLastError())));
 
   r->src_base[replica_id] = r->slice;
   r->src_base[G] = c->host_dev;
@@ -1230,15 +1348,15 @@ int ugc_export(ugc_ctx* c, int replica_id, ugc_peer_handle* out) {
   if (!c->cfg.alloc && dev_block_find(r->slice, &sb) && dev_block_find(r->table_mem, &tb)) {
     const int sfd = dev_block_export_fd(r->slice), tfd = dev_block_export_fd(r->table_mem);
     if (sfd >= 0 && tfd >= 0) {
-      // other processes of this user may duplicate the two descriptors out of this process,
-      // or ask for them over the descriptor socket
-      prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0);
-      fd_server_publish(sfd);
-      fd_server_publish(tfd);
+      // Importers duplicate the two descriptors out of this process where the kernel lets
+      // them, else ask for them over the descriptor socket (same user only).  Nothing is done
+      // here to widen who may attach to this process.
+      const bool served = fd_server_publish(sfd) && fd_server_publish(tfd);
+      if (!served) g_last_error = g_fd_server_error;  // not fatal: read with ugc_last_error()
       out->has_ipc = 2;
-      int64_t v[2] = {sfd, (int64_t)sb.size};
+      int64_t v[3] = {sfd, (int64_t)sb.size, (int64_t)g_fd_token};
       memcpy(out->slice_ipc, v, sizeof(v));
-      int64_t w[2] = {tfd, (int64_t)tb.size};
+      int64_t w[3] = {tfd, (int64_t)tb.size, (int64_t)g_fd_token};
       memcpy(out->table_ipc, w, sizeof(w));
       return UGC_OK;
     }
@@ -1307,15 +1425,15 @@ int ugc_import_peer(ugc_ctx* c, int replica_id, const ugc_peer_handle* peer) {
     }
   } else if (peer->has_ipc == 2) {
     UGC_CUDA(cudaSetDevice(r->device));
-    int64_t v[2], w[2];
+    int64_t v[3], w[3];
     memcpy(v, peer->slice_ipc, sizeof(v));
     memcpy(w, peer->table_ipc, sizeof(w));
-    slice = dev_import(peer->pid, (int)v[0], (size_t)v[1], r->device);
+    slice = dev_import(peer->pid, (uint64_t)v[2], (int)v[0], (size_t)v[1], r->device);
     if (!slice)
       return fail(UGC_ERR_CUDA, "cannot import replica %d's slice (descriptor %d of process %lld)", p,
                   (int)v[0], (long long)peer->pid);
     r->ipc_opened[r->n_ipc_opened++] = slice;
-    table = dev_import(peer->pid, (int)w[0], (size_t)w[1], r->device);
+    table = dev_import(peer->pid, (uint64_t)w[2], (int)w[0], (size_t)w[1], r->device);
     if (!table) return fail(UGC_ERR_CUDA, "cannot import replica %d's table", p);
     r->ipc_opened[r->n_ipc_opened++] = table;
   } else {
@@ -1364,10 +1482,9 @@ static int attach_keys(ugc_ctx* c, Replica* r, int src, const uint32_t* keys_dev
   if (!r->peer_known[src] || !r->src_base[src])
     return fail(UGC_ERR_STATE, "replica %d reads from replica %d, which has not been imported", r->id, src);
   UGC_TRY(ensure(c, r->stage_b, n * sizeof(uint32_t)));
-  UGC_CUDA(launch_table_resolve(r->peer_table[src], keys_dev, (uint32_t)n, (uint32_t)src,
-                                static_cast<uint32_t*>(r->stage_b.ptr), r->counters, s));
-  UGC_CUDA(launch_table_insert(r->table, keys_dev, static_cast<uint32_t*>(r->stage_b.ptr), 0, (uint32_t)src,
-                               (uint32_t)n, r->counters, s));
+  const SlotView offs{static_cast<uint32_t*>(r->stage_b.ptr), 0, 0};
+  UGC_CUDA(launch_table_resolve(r->peer_table[src], keys_dev, (uint32_t)n, (uint32_t)src, offs, r->counters, s));
+  UGC_CUDA(launch_table_insert(r->table, keys_dev, offs, (uint32_t)src, (uint32_t)n, r->counters, s));
   // the offset buffer is reused by the next source
   return check_table_errors(r, s, "peer attach");
 }
@@ -1416,6 +1533,7 @@ int ugc_lookup_i64_static(ugc_ctx* c, int replica_id, const int64_t* keys, size_
     return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   UGC_CUDA(cudaSetDevice(r->device));
+  r->static_used = true;  // a refresh then drains the device instead of counting lookups
   void* base = nullptr;
   UGC_TRY(static_scratch_address(r->device, &base));
   Counters* counters = static_cast<Counters*>(base);
@@ -1436,6 +1554,8 @@ int ugc_lookup_i64_static(ugc_ctx* c, int replica_id, const int64_t* keys, size_
   p.remote_cta_cap = r->remote_ctas;
   p.host_cta_cap = r->host_ctas;
   p.rows_per_cta_min = 32;
+  for (int g = 0; g < kNumGroup; g++) p.t_byte[g] = r->t_byte[g];
+  p.dynamic = 0;
   p.bulk_mask = 0;
   p.pdl = 0;
   UGC_CUDA(launch_gather_roles(p, r->gather_grid, r->block_threads, r->vec_bytes, s));
@@ -1448,7 +1568,7 @@ int ugc_reserve_batch(ugc_ctx* c, int replica_id, uint32_t max_batch) {
   if (max_batch == 0 || max_batch > kMaxBatch) return fail(UGC_ERR_INVALID, "max_batch must be in [1, 2^28]");
   if (max_batch <= r->max_batch) return UGC_OK;
   UGC_CUDA(cudaSetDevice(r->device));
-  UGC_CUDA(cudaDeviceSynchronize());
+  UGC_TRY(drain_lookups(r));  // the old lists may still be in use by lookups in flight
   uint64_t* fresh[kNumGroup] = {nullptr, nullptr, nullptr};
   for (int g = 0; g < kNumGroup; g++) {
     fresh[g] = static_cast<uint64_t*>(ctx_alloc(c, (size_t)max_batch * sizeof(uint64_t)));
@@ -1483,10 +1603,42 @@ int ugc_lookup_host(ugc_ctx* c, int replica_id, const void* keys, int key_bytes,
     UGC_CUDA(cudaMemcpyAsync(r->stage_keys.ptr, keys, n * (size_t)key_bytes, cudaMemcpyHostToDevice, s));
     keys_dev = r->stage_keys.ptr;
   }
-  if (!out_dev) UGC_TRY(ensure(c, r->stage_out, n * (size_t)c->cfg.row_bytes));
-  UGC_TRY(do_lookup(c, r, keys_dev, key_bytes, n, out_dev ? out_dev : r->stage_out.ptr, s));
-  if (!out_dev)
-    UGC_CUDA(cudaMemcpyAsync(out, r->stage_out.ptr, n * (size_t)c->cfg.row_bytes, cudaMemcpyDeviceToHost, s));
+  if (out_dev) {
+    UGC_TRY(do_lookup(c, r, keys_dev, key_bytes, n, out_dev, s));
+    UGC_CUDA(cudaStreamSynchronize(s));
+    return UGC_OK;
+  }
+  // Rows are staged in device memory and leave through the copy engine, which moves them
+  // faster than stores from the SMs do.  Large batches go in pieces: while piece i crosses
+  // PCIe on a second stream, piece i+1 is being extracted.
+  const size_t rb = c->cfg.row_bytes;
+  UGC_TRY(ensure(c, r->stage_out, n * rb));
+  size_t pieces = n >= (1u << 16) ? 8 : 1;
+  const size_t piece = (n / pieces + 31) / 32 * 32;  // multiples of 32 keys keep every piece aligned
+  if (pieces > 1) {
+    if (!r->copy_stream) UGC_CUDA(cudaStreamCreateWithFlags(&r->copy_stream, cudaStreamNonBlocking));
+    while (r->copy_events.size() < pieces) {
+      cudaEvent_t e;
+      UGC_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+      r->copy_events.push_back(e);
+    }
+  }
+  const char* kp = static_cast<const char*>(keys_dev);
+  char* stage = static_cast<char*>(r->stage_out.ptr);
+  size_t idx = 0;
+  for (size_t off = 0; off < n; off += piece, idx++) {
+    const size_t m = std::min(piece, n - off);
+    UGC_TRY(do_lookup(c, r, kp + off * (size_t)key_bytes, key_bytes, m, stage + off * rb, s));
+    if (pieces > 1) {
+      UGC_CUDA(cudaEventRecord(r->copy_events[idx], s));
+      UGC_CUDA(cudaStreamWaitEvent(r->copy_stream, r->copy_events[idx], 0));
+      UGC_CUDA(cudaMemcpyAsync(static_cast<char*>(out) + off * rb, stage + off * rb, m * rb,
+                               cudaMemcpyDeviceToHost, r->copy_stream));
+    } else {
+      UGC_CUDA(cudaMemcpyAsync(out, stage, m * rb, cudaMemcpyDeviceToHost, s));
+    }
+  }
+  if (pieces > 1) UGC_CUDA(cudaStreamSynchronize(r->copy_stream));
   UGC_CUDA(cudaStreamSynchronize(s));
   return UGC_OK;
 }
@@ -1518,30 +1670,41 @@ int ugc_refresh_evict(ugc_ctx* c, int replica_id, void* stream) {
   const uint64_t n_evict = r->list_count[kListEvict], n_insert = r->list_count[kListInsert];
   const uint64_t n_drop = r->list_count[kListDropRemote];
   const uint64_t n_new_local = r->n_local - n_evict + n_insert;
+  // a placement that does not fit is refused before anything changed: give back what the
+  // classification allocated so that a later refresh starts clean
+  auto refuse = [&](int rc) {
+    std::string keep = g_last_error;
+    ctx_free(c, r->n2b_next);
+    r->n2b_next = nullptr;
+    ctx_free(c, r->lists.ptr);
+    r->lists = DevBuf{};
+    g_last_error = keep;
+    return rc;
+  };
   if (n_new_local > r->capacity)
-    return fail(UGC_ERR_CAPACITY, "new placement stores %llu rows on replica %d, slice holds %llu",
-                (unsigned long long)n_new_local, me, (unsigned long long)r->capacity);
+    return refuse(fail(UGC_ERR_CAPACITY, "new placement stores %llu rows on replica %d, slice holds %llu",
+                (unsigned long long)n_new_local, me, (unsigned long long)r->capacity));
   uint64_t n_attach = 0;
   for (int s2 = 0; s2 < G; s2++)
     if (s2 != me) n_attach += r->list_count[kListAttach0 + s2];
   const uint64_t n_new_entries = r->n_local + r->n_remote - n_evict - n_drop + n_insert + n_attach;
   if (r->table.kind == kTableHashed && n_new_entries > r->table_entry_cap)
-    return fail(UGC_ERR_CAPACITY, "new placement needs %llu table entries, table is sized for %llu",
-                (unsigned long long)n_new_entries, (unsigned long long)r->table_entry_cap);
-  if (n_insert > r->free_slots.size() + n_evict)
-    return fail(UGC_ERR_CAPACITY, "refresh needs %llu free slots, %llu available",
-                (unsigned long long)n_insert, (unsigned long long)(r->free_slots.size() + n_evict));
+    return refuse(fail(UGC_ERR_CAPACITY, "new placement needs %llu table entries, table is sized for %llu",
+                       (unsigned long long)n_new_entries, (unsigned long long)r->table_entry_cap));
+  if (n_insert > r->free_count + n_evict)
+    return refuse(fail(UGC_ERR_CAPACITY, "refresh needs %llu free slots, %llu available",
+                       (unsigned long long)n_insert, (unsigned long long)(r->free_count + n_evict)));
 
-  // step 3: evicted rows give their slots back (appended to the free list), then leave the table
+  // step 3: evicted rows give their slots back (written by the resolve kernel straight to the
+  // tail of the free ring; the slot numbers never visit the host), then leave the table
   if (n_evict) {
-    UGC_TRY(ensure(c, r->stage_b, n_evict * sizeof(uint32_t)));
-    UGC_CUDA(launch_table_resolve(r->table, list_ptr(r, kListEvict), (uint32_t)n_evict, (uint32_t)me,
-                                  static_cast<uint32_t*>(r->stage_b.ptr), r->counters, s));
-    std::vector<uint32_t> slots(n_evict);
-    UGC_CUDA(cudaMemcpyAsync(slots.data(), r->stage_b.ptr, n_evict * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    const SlotView tail{r->free_ring, (uint32_t)((r->free_head + r->free_count) % r->capacity),
+                        (uint32_t)r->capacity};
+    UGC_CUDA(launch_table_resolve(r->table, list_ptr(r, kListEvict), (uint32_t)n_evict, (uint32_t)me, tail,
+                                  r->counters, s));
     UGC_CUDA(launch_table_evict(r->table, list_ptr(r, kListEvict), (uint32_t)n_evict, r->counters, s));
     UGC_TRY(check_table_errors(r, s, "refresh evict"));
-    for (uint32_t o : slots) r->free_slots.push_back(o);
+    r->free_count += n_evict;
   }
   // step 4: remote entries whose source changed (coll_cache_lib/cache_context.cu:3103-3136)
   if (n_drop) {
@@ -1550,12 +1713,12 @@ int ugc_refresh_evict(ugc_ctx* c, int replica_id, void* stream) {
   }
   // Grace period.  A lookup that was enqueued before the evictions above completed may hold a
   // record naming a slot that is about to be given to another key (here, or on a peer that this
-  // replica just stopped reading from).  Everything enqueued on this device so far is drained
-  // before the call returns; the caller's barrier between the evict and fill phases then keeps
-  // every replica's fill behind every replica's drain.  Lookups enqueued from now on see only
-  // the tables without the evicted entries.  (The reference waits for the trainer's step
-  // counter to advance instead, coll_cache_lib/cache_context.cu:4050-4052.)
-  UGC_CUDA(cudaDeviceSynchronize());
+  // replica just stopped reading from).  Every lookup of this replica enqueued so far is
+  // drained before the call returns (by its finished-lookup counter, no stream is stalled);
+  // the caller's barrier between the evict and fill phases then keeps every replica's fill
+  // behind every replica's drain.  Lookups enqueued from now on see only the tables without
+  // the evicted entries.
+  UGC_TRY(drain_lookups(r));
   r->next_n_local = n_new_local;
   r->refresh_open = true;
   return UGC_OK;
@@ -1569,22 +1732,19 @@ int ugc_refresh_fill(ugc_ctx* c, int replica_id, void* stream) {
   UGC_CUDA(cudaSetDevice(r->device));
   const size_t n = (size_t)r->list_count[kListInsert];
   if (n) {
-    // new rows take slots from the FRONT of the free list
+    // new rows take slots from the HEAD of the free ring
     // (coll_cache_lib/cuda/cache_hashtable.cuh:637-645)
-    std::vector<uint32_t> slots(n);
-    for (size_t i = 0; i < n; i++) {
-      slots[i] = r->free_slots.front();
-      r->free_slots.pop_front();
-    }
-    UGC_TRY(upload_u32(c, r->stage_b, slots.data(), n, s));
+    if (n > r->free_count) return fail(UGC_ERR_CAPACITY, "refresh fill: free slots ran out");
+    const SlotView head{r->free_ring, (uint32_t)r->free_head, (uint32_t)r->capacity};
     // A small grid keeps the refill from taking bandwidth from running lookups
     // (the reference limits it to 20 blocks, coll_cache_lib/cache_context.cu:4067).
-    UGC_CUDA(launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, kListInsert),
-                                 static_cast<uint32_t*>(r->stage_b.ptr), 0, (uint32_t)n,
-                                 c->cfg.row_bytes, c->cfg.empty_feat, 20, s));
-    UGC_CUDA(launch_table_insert(r->table, list_ptr(r, kListInsert), static_cast<uint32_t*>(r->stage_b.ptr), 0,
-                                 (uint32_t)replica_id, (uint32_t)n, r->counters, s));
+    UGC_CUDA(launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, kListInsert), head, (uint32_t)n,
+                                 c->cfg.row_bytes, c->cfg.empty_feat, r->refresh_fill_ctas, s));
+    UGC_CUDA(launch_table_insert(r->table, list_ptr(r, kListInsert), head, (uint32_t)replica_id, (uint32_t)n,
+                                 r->counters, s));
     UGC_TRY(check_table_errors(r, s, "refresh insert"));
+    r->free_head = (r->free_head + n) % r->capacity;
+    r->free_count -= n;
   }
   return UGC_OK;
 }
@@ -1674,7 +1834,7 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   out->num_remote_keys = r->n_remote;
   out->num_host_keys = c->cfg.num_total_item - out->num_local_rows - out->num_remote_keys;
   out->capacity_rows = r->capacity;
-  out->free_rows = r->free_slots.size();
+  out->free_rows = r->free_count;
   out->table_kind = r->table.kind;
   out->table_bytes = r->table_bytes;
   out->slice_bytes = r->slice_bytes;
@@ -1691,6 +1851,7 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   out->last_local_ns = span(kGroupLocal);
   out->last_remote_ns = span(kGroupRemote);
   out->last_host_ns = span(kGroupHost);
+  out->last_index_ns = (h.t_index && h.t_start > h.t_index) ? (uint64_t)(h.t_start - h.t_index) : 0;
   out->lookups_direct = r->lookups_direct;
   out->kernel_launches = r->kernel_launches;
   return UGC_OK;
@@ -1714,6 +1875,9 @@ int ugc_get_tuning(ugc_ctx* c, int replica_id, ugc_tuning* out) {
   out->direct_ctas_per_sm = r->direct_grid / std::max(r->sm_count, 1);
   out->direct_host_permille = (int)(r->direct_host_share * 1000.0 + 0.5);
   out->host_zero_copy = r->host_zero_copy;
+  out->gather_dynamic = r->gather_dynamic;
+  out->direct_tile_keys = r->direct_tile_shift ? (1 << r->direct_tile_shift) : 0;
+  out->direct_deep = r->direct_deep;
   return UGC_OK;
 }
 
@@ -1741,6 +1905,9 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   r->direct_grid = r->sm_count * t->direct_ctas_per_sm;
   r->direct_host_share = t->direct_host_permille / 1000.0;
   r->host_zero_copy = t->host_zero_copy;
+  r->gather_dynamic = t->gather_dynamic ? 1 : 0;
+  r->direct_tile_shift = t->direct_tile_keys == 8 ? 3 : t->direct_tile_keys == 16 ? 4 : t->direct_tile_keys == 32 ? 5 : 0;
+  r->direct_deep = t->direct_deep ? 1 : 0;
   return UGC_OK;
 }
 

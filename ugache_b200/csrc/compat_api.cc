@@ -31,6 +31,10 @@ constexpr int kMaxReplica = UGC_MAX_DEVICE;
 constexpr int kNumLogItems = 64;  // the reference has 54 step items (profiler.h:58-120)
 constexpr int kLogL1FeatureBytes = 9, kLogL1MissBytes = 13, kLogL1RemoteBytes = 14;
 constexpr int kLogL2CacheCopyTime = 27;
+// per-phase times of one extraction (profiler.h:111-117; logged by the reference at
+// coll_cache_lib/cache_context.cu:1662-1679)
+constexpr int kLogL3CacheGetIndexTime = 46, kLogL3CacheCombineMissTime = 50,
+              kLogL3CacheCombineCacheTime = 51, kLogL3CacheCombineRemoteTime = 52;
 
 // ---- state shared by all replicas' processes ----------------------------------------------
 struct Barrier {
@@ -165,6 +169,14 @@ int fail(int code, const std::string& msg) {
 int pass(int rc, const char* what) {
   if (rc == UGC_OK) return rc;
   return fail(rc, std::string(what) + ": " + ugc_last_error());
+}
+
+// An error return out of a call that every replica makes together (init, refresh): the other
+// replicas are, or soon will be, waiting at a barrier for this one, so whatever the error
+// code, they are told at once instead of waiting for the barrier's time limit.
+int collective(int rc) {
+  if (rc != UGC_OK && g_ctl) g_ctl->failed.store(1, std::memory_order_release);
+  return rc;
 }
 
 int g_device_map[kMaxReplica] = {-1, -1, -1, -1, -1, -1, -1, -1};
@@ -427,20 +439,20 @@ int coll_cache_record(int replica_id, uint32_t* key, size_t n) {
 int coll_cache_init_c(int replica_id, size_t key_space_size, ugc_alloc_fn alloc, ugc_free_fn free_fn,
                       void* alloc_user, void* cpu_data, int dtype, size_t dim, double cache_percentage,
                       void* stream) {
-  if (!g_cfg.configured) return fail(UGC_ERR_STATE, "coll_cache_config has not been called");
-  if (replica_id < 0 || replica_id >= g_cfg.num_device) return fail(UGC_ERR_INVALID, "bad replica id");
+  if (!g_cfg.configured) return collective(fail(UGC_ERR_STATE, "coll_cache_config has not been called"));
+  if (replica_id < 0 || replica_id >= g_cfg.num_device) return collective(fail(UGC_ERR_INVALID, "bad replica id"));
   if (key_space_size != g_cfg.num_total_item)
-    return fail(UGC_ERR_INVALID, "key_space_size differs from the configured num_total_item");
+    return collective(fail(UGC_ERR_INVALID, "key_space_size differs from the configured num_total_item"));
   const size_t eb = elem_bytes(dtype);
-  if (!eb || !dim) return fail(UGC_ERR_INVALID, "bad dtype / dim");
+  if (!eb || !dim) return collective(fail(UGC_ERR_INVALID, "bad dtype / dim"));
   const int G = g_cfg.num_device;
   int rc;
-  if ((rc = barrier_wait(&g_ctl->bar)) != UGC_OK) return fail(rc, "replicas did not all reach init");
+  if ((rc = barrier_wait(&g_ctl->bar)) != UGC_OK) return collective(fail(rc, "replicas did not all reach init"));
   if (replica_id == 0) {
     g_ctl->placement_epoch = 1;
-    if ((rc = solve_to_shm(1)) != UGC_OK) return rc;
+    if ((rc = solve_to_shm(1)) != UGC_OK) return collective(rc);
   }
-  if ((rc = barrier_wait(&g_ctl->bar)) != UGC_OK) return fail(rc, "placement was not published");
+  if ((rc = barrier_wait(&g_ctl->bar)) != UGC_OK) return collective(fail(rc, "placement was not published"));
   {
     std::lock_guard<std::mutex> lock(g_mu);
     if (!g_ctx) {
@@ -458,31 +470,31 @@ int coll_cache_init_c(int replica_id, size_t key_space_size, ugc_alloc_fn alloc,
       cfg.alloc = alloc;
       cfg.free = free_fn;
       cfg.alloc_user = alloc_user;
-      if ((rc = ugc_create(&cfg, &g_ctx)) != UGC_OK) return pass(rc, "ugc_create");
+      if ((rc = ugc_create(&cfg, &g_ctx)) != UGC_OK) return collective(pass(rc, "ugc_create"));
       g_row_bytes = cfg.row_bytes;
       g_cpu_data = cpu_data;
     }
     if (!g_placement_set) {
       void* base;
       PlaceView v;
-      if ((rc = open_placement(1, &base, &v)) != UGC_OK) return rc;
+      if ((rc = open_placement(1, &base, &v)) != UGC_OK) return collective(rc);
       rc = ugc_set_placement(g_ctx, v.nid_to_block, v.block_placement, v.access, v.density, *v.num_block);
       munmap(base, place_bytes(key_space_size, G));
-      if (rc != UGC_OK) return pass(rc, "ugc_set_placement");
+      if (rc != UGC_OK) return collective(pass(rc, "ugc_set_placement"));
       g_placement_set = true;
     }
   }
   if ((rc = ugc_build(g_ctx, replica_id, device_of(replica_id), cpu_data, stream)) != UGC_OK)
-    return pass(rc, "ugc_build");
-  if ((rc = ugc_export(g_ctx, replica_id, &g_ctl->handles[replica_id])) != UGC_OK) return pass(rc, "ugc_export");
-  if ((rc = barrier_wait(&g_ctl->bar)) != UGC_OK) return fail(rc, "peers did not publish their handles");
+    return collective(pass(rc, "ugc_build"));
+  if ((rc = ugc_export(g_ctx, replica_id, &g_ctl->handles[replica_id])) != UGC_OK) return collective(pass(rc, "ugc_export"));
+  if ((rc = barrier_wait(&g_ctl->bar)) != UGC_OK) return collective(fail(rc, "peers did not publish their handles"));
   for (int r = 0; r < G; r++) {
     if (r == replica_id) continue;
     ugc_peer_handle h = g_ctl->handles[r];
-    if ((rc = ugc_import_peer(g_ctx, replica_id, &h)) != UGC_OK) return pass(rc, "ugc_import_peer");
+    if ((rc = ugc_import_peer(g_ctx, replica_id, &h)) != UGC_OK) return collective(pass(rc, "ugc_import_peer"));
   }
-  if ((rc = ugc_attach_peers(g_ctx, replica_id, stream)) != UGC_OK) return pass(rc, "ugc_attach_peers");
-  if ((rc = barrier_wait(&g_ctl->bar)) != UGC_OK) return fail(rc, "peers did not finish attaching");
+  if ((rc = ugc_attach_peers(g_ctx, replica_id, stream)) != UGC_OK) return collective(pass(rc, "ugc_attach_peers"));
+  if ((rc = barrier_wait(&g_ctl->bar)) != UGC_OK) return collective(fail(rc, "peers did not finish attaching"));
   return UGC_OK;
 }
 
@@ -508,21 +520,25 @@ int coll_cache_lookup(int replica_id, uint32_t* key, size_t num_keys, void* outp
     coll_cache_log_step_by_key(step_key, kLogL1FeatureBytes, (double)num_keys * g_row_bytes);
     coll_cache_log_step_by_key(step_key, kLogL1MissBytes, (double)st.last_host * g_row_bytes);
     coll_cache_log_step_by_key(step_key, kLogL1RemoteBytes, (double)st.last_remote * g_row_bytes);
+    coll_cache_log_step_by_key(step_key, kLogL3CacheGetIndexTime, st.last_index_ns * 1e-9);
+    coll_cache_log_step_by_key(step_key, kLogL3CacheCombineMissTime, st.last_host_ns * 1e-9);
+    coll_cache_log_step_by_key(step_key, kLogL3CacheCombineRemoteTime, st.last_remote_ns * 1e-9);
+    coll_cache_log_step_by_key(step_key, kLogL3CacheCombineCacheTime, st.last_local_ns * 1e-9);
   }
   return UGC_OK;
 }
 
 int coll_cache_refresh(int replica_id, void* stream) {
-  if (!g_ctx) return fail(UGC_ERR_STATE, "coll_cache_init has not run");
+  if (!g_ctx) return collective(fail(UGC_ERR_STATE, "coll_cache_init has not run"));
   const int G = g_cfg.num_device;
   int rc;
   Barrier* b = &g_ctl->refresh_bar;
-  if ((rc = barrier_wait(b)) != UGC_OK) return fail(rc, "replicas did not all reach refresh");
+  if ((rc = barrier_wait(b)) != UGC_OK) return collective(fail(rc, "replicas did not all reach refresh"));
   if (replica_id == 0) {
     g_ctl->placement_epoch++;
-    if ((rc = solve_to_shm(g_ctl->placement_epoch)) != UGC_OK) return rc;
+    if ((rc = solve_to_shm(g_ctl->placement_epoch)) != UGC_OK) return collective(rc);
   }
-  if ((rc = barrier_wait(b)) != UGC_OK) return fail(rc, "new placement was not published");
+  if ((rc = barrier_wait(b)) != UGC_OK) return collective(fail(rc, "new placement was not published"));
   static std::mutex once_mu;
   static uint32_t loaded_epoch = 1, committed_epoch = 1;
   const uint32_t epoch = g_ctl->placement_epoch;
@@ -531,29 +547,29 @@ int coll_cache_refresh(int replica_id, void* stream) {
     if (loaded_epoch != epoch) {
       void* base;
       PlaceView v;
-      if ((rc = open_placement(epoch, &base, &v)) != UGC_OK) return rc;
+      if ((rc = open_placement(epoch, &base, &v)) != UGC_OK) return collective(rc);
       rc = ugc_refresh_set_placement(g_ctx, v.nid_to_block, v.block_placement, v.access, v.density, *v.num_block);
       munmap(base, place_bytes(g_cfg.num_total_item, G));
-      if (rc != UGC_OK) return pass(rc, "ugc_refresh_set_placement");
+      if (rc != UGC_OK) return collective(pass(rc, "ugc_refresh_set_placement"));
       loaded_epoch = epoch;
     }
   }
-  if ((rc = ugc_refresh_evict(g_ctx, replica_id, stream)) != UGC_OK) return pass(rc, "ugc_refresh_evict");
-  if ((rc = barrier_wait(b)) != UGC_OK) return fail(rc, "refresh: evict phase incomplete");
-  if ((rc = ugc_refresh_fill(g_ctx, replica_id, stream)) != UGC_OK) return pass(rc, "ugc_refresh_fill");
-  if ((rc = barrier_wait(b)) != UGC_OK) return fail(rc, "refresh: fill phase incomplete");
-  if ((rc = ugc_refresh_attach(g_ctx, replica_id, stream)) != UGC_OK) return pass(rc, "ugc_refresh_attach");
-  if ((rc = barrier_wait(b)) != UGC_OK) return fail(rc, "refresh: attach phase incomplete");
+  if ((rc = ugc_refresh_evict(g_ctx, replica_id, stream)) != UGC_OK) return collective(pass(rc, "ugc_refresh_evict"));
+  if ((rc = barrier_wait(b)) != UGC_OK) return collective(fail(rc, "refresh: evict phase incomplete"));
+  if ((rc = ugc_refresh_fill(g_ctx, replica_id, stream)) != UGC_OK) return collective(pass(rc, "ugc_refresh_fill"));
+  if ((rc = barrier_wait(b)) != UGC_OK) return collective(fail(rc, "refresh: fill phase incomplete"));
+  if ((rc = ugc_refresh_attach(g_ctx, replica_id, stream)) != UGC_OK) return collective(pass(rc, "ugc_refresh_attach"));
+  if ((rc = barrier_wait(b)) != UGC_OK) return collective(fail(rc, "refresh: attach phase incomplete"));
   {
     // every replica of every process has finished its phases: the first caller in this
     // process makes the new placement current
     std::lock_guard<std::mutex> lock(once_mu);
     if (committed_epoch != epoch) {
-      if ((rc = ugc_refresh_commit(g_ctx)) != UGC_OK) return pass(rc, "ugc_refresh_commit");
+      if ((rc = ugc_refresh_commit(g_ctx)) != UGC_OK) return collective(pass(rc, "ugc_refresh_commit"));
       committed_epoch = epoch;
     }
   }
-  if ((rc = barrier_wait(b)) != UGC_OK) return fail(rc, "refresh: commit incomplete");
+  if ((rc = barrier_wait(b)) != UGC_OK) return collective(fail(rc, "refresh: commit incomplete"));
   return UGC_OK;
 }
 

@@ -67,6 +67,11 @@ struct Counters {
   unsigned long long t_end[kNumGroup];
   uint32_t seq;                  // extractions finished on these counters
   uint32_t reserved;
+  // grouped gather: rows of each list handed out so far beyond every CTA's first chunk
+  // (zeroed by the last CTA of the gather)
+  uint32_t cursor[kNumGroup];
+  uint32_t reserved2;
+  unsigned long long t_index;    // device clock (ns) when the lookup kernel started; 0 = direct
 };
 
 // Written by the last CTA of every extraction into pinned host memory: the host reads it
@@ -86,9 +91,15 @@ struct GatherParams {
   Feedback* feedback;   // pinned host mirror of the last lookup's counts, or nullptr
   uint32_t row_bytes;
   uint32_t n_keys;
-  int remote_cta_cap;   // most CTAs of the peer group
-  int host_cta_cap;     // most CTAs of the host group
+  int remote_cta_cap;   // most CTAs of the peer group: what keeps the NVLink port full
+  int host_cta_cap;     // most CTAs of the host group: what keeps the host link full
   int rows_per_cta_min; // do not give a group more CTAs than count / this
+  // Seconds per byte over each group's link, scaled by any common factor (local counts twice:
+  // row read and row write both use HBM).  The CTAs of a launch are shared out in proportion
+  // to rows * row_bytes * t_byte of the groups, within the caps above.
+  float t_byte[kNumGroup];
+  int dynamic;          // 1: lists are handed out in chunks; a CTA whose own list is drained
+                        //    takes chunks of the other groups' lists.  0: fixed striding.
   int pdl;              // launched with programmatic stream serialization
   int bulk_mask;        // bit 0: host rows, bit 1: peer rows go through bulk-async staging
 };
@@ -106,7 +117,21 @@ struct DirectParams {
   uint32_t host_loc;
   uint32_t host_mask;
   uint32_t lpr_shift;   // log2 of the lanes that share one row
+  uint32_t tile_shift;  // log2 of the keys one warp probes at a time (3..5)
 };
+
+// Slot (row offset) numbers for entries j = 0..n-1 of a build / refresh step:
+//   data == nullptr          slot(j) = base + j
+//   data != nullptr, size 0  slot(j) = data[j]
+//   data != nullptr, size>0  slot(j) = data[(base + j) % size]   (a window of the free-slot ring)
+struct SlotView {
+  uint32_t* data;
+  uint32_t base;
+  uint32_t size;
+};
+__host__ __device__ inline uint32_t slot_pos(const SlotView& v, uint32_t j) {
+  return v.size ? (uint32_t)(((uint64_t)v.base + j) % v.size) : j;
+}
 
 // Classification of the whole id space into ascending key lists.
 //  build   (n2b_old == nullptr): list s = keys this reader fetches from GPU s, s in [0, G)

@@ -176,6 +176,8 @@ __global__ void __launch_bounds__(kBlock)
   const uint32_t tid = threadIdx.x;
   const uint32_t warp = tid >> 5, lane = tid & 31;
   const uint32_t tile_base = blockIdx.x * (kBlock * kKeysPerThread);
+  unsigned long long t_begin = 0;
+  if (blockIdx.x == 0 && tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_begin));
 
   uint32_t key[kKeysPerThread];
   bool valid[kKeysPerThread];
@@ -232,6 +234,7 @@ __global__ void __launch_bounds__(kBlock)
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (bad) atomicAdd(&counters->err_key_range, (unsigned long long)bad);
   if (blockIdx.x == 0 && tid < kNumGroup) counters->t_end[tid] = 0;  // re-armed for the gather's timestamps
+  if (blockIdx.x == 0 && tid == 0) counters->t_index = t_begin;
 
   // Group, count per warp with ballots.
   uint32_t group[kKeysPerThread], rank_in_warp[kKeysPerThread];
@@ -300,15 +303,14 @@ struct RecordIndex {  // rows described by 64-bit records
 };
 struct KeySlotIndex {  // fill: host row of a key -> cache slot
   const uint32_t* keys;
-  const uint32_t* slots;  // may be null: slot = slot_base + i
-  uint32_t slot_base;
+  SlotView slots;
   uint32_t host_mask;
   const char* host;
   char* slice;
   uint32_t row_bytes;
   __device__ __forceinline__ void get(uint32_t i, const char*& src, char*& dst) const {
     uint32_t k = keys[i] & host_mask;
-    uint32_t s = slots ? slots[i] : slot_base + i;
+    uint32_t s = slots.data ? slots.data[slot_pos(slots, i)] : slots.base + i;
     src = host + (size_t)k * row_bytes;
     dst = slice + (size_t)s * row_bytes;
   }
@@ -356,13 +358,25 @@ __device__ __forceinline__ int ceil_div_i(uint32_t a, uint32_t b) { return (int)
 // Splits the grid (>= 3 CTAs) into host / remote / local groups from the device-resident
 // counts.  CTAs [0, n_host) serve host rows, [n_host, n_host+n_remote) peer rows, the rest
 // local rows: the long-latency sources get the lowest block indices, which start first.
-// A non-empty group always gets at least one CTA.
+// A group's share of the CTAs follows the time its bytes need on its link (bytes / bandwidth,
+// the rule the reference's link tables encode as SM counts per link,
+// coll_cache_lib/coll_cache/asymm_link_desc.cc:247-289), limited by what keeps that link full
+// (the caps) and by the rows there are.  A non-empty group always gets at least one CTA.
 __device__ __forceinline__ void split_roles(const GatherParams& p, const uint32_t cnt[kNumGroup],
                                             int grid, int& n_host, int& n_remote) {
   const uint32_t rmin = (uint32_t)p.rows_per_cta_min;
-  n_host = cnt[kGroupHost] ? max(1, min(p.host_cta_cap, ceil_div_i(cnt[kGroupHost], rmin))) : 0;
-  n_remote =
-      cnt[kGroupRemote] ? max(1, min(p.remote_cta_cap, ceil_div_i(cnt[kGroupRemote], rmin))) : 0;
+  const float t_loc = (float)cnt[kGroupLocal] * 2.0f * p.t_byte[kGroupLocal];
+  const float t_rem = (float)cnt[kGroupRemote] * p.t_byte[kGroupRemote];
+  const float t_host = (float)cnt[kGroupHost] * p.t_byte[kGroupHost];
+  const float t_all = t_loc + t_rem + t_host;
+  auto share = [&](float t, uint32_t c, int cap) -> int {
+    if (c == 0) return 0;
+    int n = t_all > 0.f ? (int)ceilf((float)grid * t / t_all) : cap;
+    n = min(n, min(cap, ceil_div_i(c, rmin)));
+    return max(n, 1);
+  };
+  n_host = share(t_host, cnt[kGroupHost], p.host_cta_cap);
+  n_remote = share(t_rem, cnt[kGroupRemote], p.remote_cta_cap);
   const int avail = grid - (cnt[kGroupLocal] ? 1 : 0);
   while (n_host + n_remote > avail) {  // small grids only
     if (n_remote >= n_host && n_remote > 1) {
@@ -528,33 +542,90 @@ __global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
     first = n_host + n_remote;
     num = grid - first;
   }
-  if (cnt[g] != 0) {
-    RecordIndex ix;
-    ix.list = p.list[g];
-    ix.src_base = p.src_base;
-    ix.out = static_cast<char*>(p.out);
-    ix.row_bytes = p.row_bytes;
-    const bool bulk = (g == kGroupHost && (p.bulk_mask & 1)) || (g == kGroupRemote && (p.bulk_mask & 2));
-    if (bulk) {
-      const uint32_t warps_per_cta = blockDim.x >> 5;
-      const uint32_t warp = threadIdx.x >> 5;
-      uint64_t* bars = reinterpret_cast<uint64_t*>(dyn_smem) + (size_t)warp * kBulkSlots;
-      unsigned char* stage = dyn_smem + (size_t)warps_per_cta * kBulkSlots * sizeof(uint64_t) +
-                             (size_t)warp * kBulkSlots * p.row_bytes;
-      bool ok = copy_rows_bulk(ix, cnt[g], (uint32_t)(b - first) * warps_per_cta + warp,
-                               (uint32_t)num * warps_per_cta, stage, bars);
-      if (!ok && (threadIdx.x & 31) == 0) atomicAdd(&p.counters->err_table, 1ull);
-    } else if (VEC == 32 && g == kGroupHost) {
+  RecordIndex ix;
+  ix.src_base = p.src_base;
+  ix.out = static_cast<char*>(p.out);
+  ix.row_bytes = p.row_bytes;
+  // rows [lo, lo + len) of list `gg`, shared among `n_ctas` CTAs of which this one is `cta`
+  auto copy_span = [&](int gg, uint32_t lo, uint32_t len, uint32_t cta, uint32_t n_ctas) {
+    ix.list = (gg == kGroupLocal ? p.list[kGroupLocal]
+                                 : (gg == kGroupRemote ? p.list[kGroupRemote] : p.list[kGroupHost])) + lo;
+    if (VEC == 32 && gg == kGroupHost) {
       // host rows always move as 16-byte vectors, 4 rows in flight per lane group: 32-byte
       // loads from pinned host memory were slower on every machine measured
       constexpr int kHostLpr = LPR * 2 > 32 ? 32 : LPR * 2;
       const uint32_t wpc = blockDim.x / kHostLpr;
-      copy_rows<16, kHostLpr, 4, true>(ix, cnt[g], (uint32_t)(b - first) * wpc + threadIdx.x / kHostLpr,
-                                       (uint32_t)num * wpc, threadIdx.x % kHostLpr, p.row_bytes / 16);
+      copy_rows<16, kHostLpr, 4, true>(ix, len, cta * wpc + threadIdx.x / kHostLpr, n_ctas * wpc,
+                                       threadIdx.x % kHostLpr, p.row_bytes / 16);
     } else {
-      const uint32_t worker = (uint32_t)(b - first) * workers_per_cta + worker_in_cta;
-      const uint32_t n_workers = (uint32_t)num * workers_per_cta;
-      copy_rows<VEC, LPR, UNROLL, true>(ix, cnt[g], worker, n_workers, sublane, vecs_per_row);
+      copy_rows<VEC, LPR, UNROLL, true>(ix, len, cta * workers_per_cta + worker_in_cta,
+                                        n_ctas * workers_per_cta, sublane, vecs_per_row);
+    }
+  };
+  if (!p.dynamic || p.bulk_mask != 0) {
+    // fixed striding: every CTA of a group takes rows b-first, b-first+num, ... of its list
+    if (cnt[g] != 0) {
+      const bool bulk = (g == kGroupHost && (p.bulk_mask & 1)) || (g == kGroupRemote && (p.bulk_mask & 2));
+      if (bulk) {
+        ix.list = p.list[g];
+        const uint32_t warps_per_cta = blockDim.x >> 5;
+        const uint32_t warp = threadIdx.x >> 5;
+        uint64_t* bars = reinterpret_cast<uint64_t*>(dyn_smem) + (size_t)warp * kBulkSlots;
+        unsigned char* stage = dyn_smem + (size_t)warps_per_cta * kBulkSlots * sizeof(uint64_t) +
+                               (size_t)warp * kBulkSlots * p.row_bytes;
+        bool ok = copy_rows_bulk(ix, cnt[g], (uint32_t)(b - first) * warps_per_cta + warp,
+                                 (uint32_t)num * warps_per_cta, stage, bars);
+        if (!ok && (threadIdx.x & 31) == 0) atomicAdd(&p.counters->err_table, 1ull);
+      } else {
+        copy_span(g, 0, cnt[g], (uint32_t)(b - first), (uint32_t)num);
+      }
+    }
+  } else {
+    // Chunked hand-out.  Chunk i < (CTAs of the group) of a list belongs to the group's i-th
+    // CTA without any atomic; further chunks come from the list's cursor, fetched one chunk
+    // ahead so that the atomic's latency overlaps the copy.  A CTA that finds its own list
+    // drained moves on to the other lists (far sources first), so no CTA idles while rows
+    // are left anywhere.
+    __shared__ uint32_t s_next;
+    const uint32_t chunk = workers_per_cta * UNROLL * 2;
+    const int o1 = g == kGroupRemote ? kGroupHost : kGroupRemote;
+    const int o2 = g == kGroupLocal ? kGroupHost : kGroupLocal;
+#pragma unroll
+    for (int k = 0; k < kNumGroup; k++) {
+      const int gg = k == 0 ? g : (k == 1 ? o1 : o2);
+      const uint32_t total =
+          gg == kGroupLocal ? cnt[kGroupLocal] : (gg == kGroupRemote ? cnt[kGroupRemote] : cnt[kGroupHost]);
+      if (total == 0) continue;
+      const int ctas_gg = gg == kGroupLocal ? grid - n_host - n_remote : (gg == kGroupRemote ? n_remote : n_host);
+      const uint32_t owned = (uint32_t)ctas_gg * chunk;  // rows covered by the first chunks
+      if (k > 0 && owned >= total) continue;             // nothing beyond them to take
+      uint32_t* cursor = &p.counters->cursor[0] + gg;
+      uint32_t base, fetched = 0;
+      if (k == 0) {
+        base = (uint32_t)(b - first) * chunk;
+        if (threadIdx.x == 0 && owned < total) fetched = atomicAdd(cursor, chunk);
+      } else {
+        if (threadIdx.x == 0) s_next = atomicAdd(cursor, chunk);
+        __syncthreads();
+        base = owned + s_next;
+        __syncthreads();
+        if (threadIdx.x == 0 && base < total) fetched = atomicAdd(cursor, chunk);
+      }
+      bool did = false;
+      while (base < total) {
+        copy_span(gg, base, min(chunk, total - base), 0u, 1u);
+        did = true;
+        if (threadIdx.x == 0) s_next = fetched;
+        __syncthreads();
+        base = owned + s_next;
+        __syncthreads();
+        if (threadIdx.x == 0 && base < total) fetched = atomicAdd(cursor, chunk);
+      }
+      if (did && k > 0 && threadIdx.x == 0) {  // finish time of a group this CTA helped
+        unsigned long long th;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(th));
+        atomicMax(&p.counters->t_end[0] + gg, th);
+      }
     }
   }
 
@@ -576,6 +647,8 @@ __global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
       }
       p.counters->last_keys = p.n_keys;
       p.counters->done_ctas = 0;
+#pragma unroll
+      for (int g2 = 0; g2 < kNumGroup; g2++) p.counters->cursor[g2] = 0;
       publish_feedback(p.feedback, p.n_keys, cnt, ++p.counters->seq);
       __threadfence();
     }
@@ -585,7 +658,10 @@ __global__ void __launch_bounds__(1024) gather_roles_kernel(GatherParams p) {
 // ------------------------------------------------------------------------------------
 // direct extraction: table probe and row copy in ONE kernel, no index lists
 // ------------------------------------------------------------------------------------
-// A warp owns tiles of 32 consecutive keys.  Lane l probes the table for key l of the tile;
+// A warp owns tiles of 32 (or 16, or 8) consecutive keys -- the launcher picks the largest
+// size that leaves every warp nearly the same number of tiles; with 32-key tiles a batch of
+// 212,992 keys is 1.4 tiles per warp, so 40 % of the warps would carry twice the work of the
+// rest.  Lane l probes the table for key l of the tile;
 // the row addresses then travel by shuffle to the lane groups that copy the rows, so the
 // destination of a tile is one contiguous piece of the output.  Rows of every source (local
 // slice, peer slice over NVLink, pinned host memory) are copied where they come up, which
@@ -630,13 +706,14 @@ __device__ __forceinline__ uint32_t probe_resolve(const TableView& t, const Prob
   return probe_rest(t.slots, t.line_mask, key, murmur3_32(key) & t.line_mask);
 }
 
-// Key `lane` of tile `tl`; ids outside [0, num_keys) are counted and dropped.
+// Key `lane` of tile `tl` (tiles of 1 << shift keys; lanes beyond the tile hold no key); ids
+// outside [0, num_keys) are counted and dropped.
 template <typename KeyT>
 __device__ __forceinline__ void fetch_key(const KeyT* __restrict__ keys, uint32_t tl, uint32_t n_tiles,
-                                          uint32_t n_keys, uint64_t num_keys, uint32_t lane,
-                                          uint32_t& key, bool& valid, uint32_t& bad) {
-  const uint32_t idx = (tl << 5) + lane;
-  valid = tl < n_tiles && idx < n_keys;
+                                          uint32_t shift, uint32_t n_keys, uint64_t num_keys,
+                                          uint32_t lane, uint32_t& key, bool& valid, uint32_t& bad) {
+  const uint32_t idx = (tl << shift) + lane;
+  valid = tl < n_tiles && (lane >> shift) == 0 && idx < n_keys;
   uint64_t k = valid ? (uint64_t)keys[idx] : 0;
   if (k >= num_keys) {  // also catches negative int64 ids
     valid = false;
@@ -646,10 +723,12 @@ __device__ __forceinline__ void fetch_key(const KeyT* __restrict__ keys, uint32_
   key = (uint32_t)k;
 }
 
-template <typename KeyT, int VEC>
-__global__ void __launch_bounds__(kBlock, 4) extract_direct_kernel(const KeyT* __restrict__ keys,
-                                                                  DirectParams p) {
-  constexpr int UNROLL = VEC == 32 ? 2 : 4;
+template <typename KeyT, int VEC, bool DEEP>
+__global__ void __launch_bounds__(kBlock, DEEP ? 3 : 4)
+    extract_direct_kernel(const KeyT* __restrict__ keys, DirectParams p) {
+  // rows in flight per lane group: 4 (2 with 32-byte vectors) at 4 CTAs per SM, or twice that
+  // at 3 CTAs per SM
+  constexpr int UNROLL = (VEC == 32 ? 2 : 4) * (DEEP ? 2 : 1);
   __shared__ uint32_t s_cnt[kNumGroup];
   __shared__ const char* s_src[kMaxLocation];
   if (threadIdx.x == 0) {
@@ -658,7 +737,9 @@ __global__ void __launch_bounds__(kBlock, 4) extract_direct_kernel(const KeyT* _
   }
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t n_warps = gridDim.x * kWarpsPerBlock;
-  const uint32_t n_tiles = (p.n_keys + 31) >> 5;
+  const uint32_t tshift = p.tile_shift;
+  const uint32_t tile_keys = 1u << tshift;
+  const uint32_t n_tiles = (p.n_keys + tile_keys - 1) >> tshift;
   uint32_t tile = (threadIdx.x >> 5) * gridDim.x + blockIdx.x;
   if (threadIdx.x < kNumGroup) s_cnt[threadIdx.x] = 0;
 
@@ -671,8 +752,8 @@ __global__ void __launch_bounds__(kBlock, 4) extract_direct_kernel(const KeyT* _
   // first two key loads and the first probe run before the dependency wait.
   uint32_t key_cur, key_nxt;
   bool ok_cur, ok_nxt;
-  fetch_key(keys, tile, n_tiles, p.n_keys, p.table.num_keys, lane, key_cur, ok_cur, bad);
-  fetch_key(keys, tile + n_warps, n_tiles, p.n_keys, p.table.num_keys, lane, key_nxt, ok_nxt, bad);
+  fetch_key(keys, tile, n_tiles, tshift, p.n_keys, p.table.num_keys, lane, key_cur, ok_cur, bad);
+  fetch_key(keys, tile + n_warps, n_tiles, tshift, p.n_keys, p.table.num_keys, lane, key_nxt, ok_nxt, bad);
   Probe pr;
   probe_issue(p.table, key_cur, ok_cur, pr);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -692,7 +773,7 @@ __global__ void __launch_bounds__(kBlock, 4) extract_direct_kernel(const KeyT* _
     probe_issue(p.table, key_nxt, ok_nxt, pr);
     uint32_t key_nn;
     bool ok_nn;
-    fetch_key(keys, tile + 2 * n_warps, n_tiles, p.n_keys, p.table.num_keys, lane, key_nn, ok_nn, bad);
+    fetch_key(keys, tile + 2 * n_warps, n_tiles, tshift, p.n_keys, p.table.num_keys, lane, key_nn, ok_nn, bad);
 
     // this lane's key: source address and group
     const char* src = nullptr;
@@ -714,16 +795,16 @@ __global__ void __launch_bounds__(kBlock, 4) extract_direct_kernel(const KeyT* _
     n_remote += __popc(__ballot_sync(kFull, group == (uint32_t)kGroupRemote));
     n_host += __popc(__ballot_sync(kFull, group == (uint32_t)kGroupHost));
 
-    char* out_tile = static_cast<char*>(p.out) + (size_t)tile * 32 * p.row_bytes;
+    char* out_tile = static_cast<char*>(p.out) + ((size_t)tile << tshift) * p.row_bytes;
     const unsigned long long src_bits = reinterpret_cast<unsigned long long>(src);
     const size_t row_step = (size_t)rpi * p.row_bytes;  // between the rows of one lane group
-    for (uint32_t rb = 0; rb < 32; rb += UNROLL * rpi) {
+    for (uint32_t rb = 0; rb < tile_keys; rb += UNROLL * rpi) {
       const char* s[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; u++) {
         const uint32_t r = rb + u * rpi + rsel;
         const unsigned long long a = __shfl_sync(kFull, src_bits, r & 31);
-        s[u] = r < 32 ? reinterpret_cast<const char*>(a) : nullptr;
+        s[u] = r < tile_keys ? reinterpret_cast<const char*>(a) : nullptr;
       }
       char* d0 = out_tile + (size_t)(rb + rsel) * p.row_bytes;
       for (uint32_t c = sub; c < vecs_per_row; c += lpr) {
@@ -758,7 +839,10 @@ __global__ void __launch_bounds__(kBlock, 4) extract_direct_kernel(const KeyT* _
       if (s_cnt[g]) atomicAdd(&p.counters->count[g], s_cnt[g]);
     unsigned long long t1;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (blockIdx.x == 0) p.counters->t_start = t0;
+    if (blockIdx.x == 0) {
+      p.counters->t_start = t0;
+      p.counters->t_index = 0;
+    }
     atomicMax(&p.counters->t_end[kGroupLocal], t1);  // one span for the whole kernel
     __threadfence();
     const uint32_t done = atomicAdd(&p.counters->done_ctas, 1u);
@@ -820,13 +904,12 @@ __device__ __forceinline__ bool insert_hashed(const TableView& t, uint32_t key, 
 }
 
 __global__ void __launch_bounds__(kBlock)
-    table_insert_kernel(TableView t, const uint32_t* __restrict__ keys,
-                        const uint32_t* __restrict__ offs, uint32_t off_base, uint32_t loc,
+    table_insert_kernel(TableView t, const uint32_t* __restrict__ keys, SlotView offs, uint32_t loc,
                         uint32_t n, Counters* counters) {
   uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   uint32_t key = keys[i];
-  uint32_t word = pack_word(loc, offs ? offs[i] : off_base + i);
+  uint32_t word = pack_word(loc, offs.data ? offs.data[slot_pos(offs, i)] : offs.base + i);
   bool ok;
   if (key >= t.num_keys) {
     ok = false;
@@ -880,17 +963,24 @@ __global__ void __launch_bounds__(kBlock)
 
 __global__ void __launch_bounds__(kBlock)
     table_resolve_kernel(TableView peer, const uint32_t* __restrict__ keys, uint32_t n,
-                         uint32_t expect_loc, uint32_t* __restrict__ offs, Counters* counters) {
+                         uint32_t expect_loc, SlotView offs, Counters* counters) {
   uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   uint32_t key = keys[i];
   uint32_t w = key < peer.num_keys ? table_lookup(peer, key) : kEmptyWord;
+  uint32_t* dst = offs.data + slot_pos(offs, i);
   if (w == kEmptyWord || word_loc(w) != expect_loc) {
     atomicAdd(&counters->err_table, 1ull);
-    offs[i] = 0;
+    *dst = 0;
   } else {
-    offs[i] = word_off(w);
+    *dst = word_off(w);
   }
+}
+
+__global__ void iota_kernel(uint32_t* dst, uint32_t start, uint32_t n) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[i] = start + i;
 }
 
 // ------------------------------------------------------------------------------------
@@ -1189,18 +1279,40 @@ int usable_vec_bytes(uint32_t row_bytes, int want, const void* out, const void* 
 }
 
 cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectParams& p_in, int grid,
-                                  int vec_bytes, bool pdl, cudaStream_t stream) {
+                                  int vec_bytes, bool deep, bool pdl, cudaStream_t stream) {
   if (p_in.n_keys == 0) return cudaSuccess;
   DirectParams p = p_in;
   const int vec = usable_vec_bytes(p.row_bytes, vec_bytes, p.out, p.src_base, kMaxLocation);
   const int lpr = lanes_per_row(p.row_bytes, vec);
   p.lpr_shift = 0;
   while ((1 << p.lpr_shift) < lpr) p.lpr_shift++;
-  const int tiles = (int)((p.n_keys + 31) / 32);
+  // Tile size: the largest of 32 / 16 / 8 keys (never less than the rows one pass of a warp
+  // copies) with which the warps' tile counts differ by less than a tenth; forced by
+  // p.tile_shift when that is set.
+  const int unroll = (vec == 32 ? 2 : 4) * (deep ? 2 : 1);
+  const int rows_per_pass = std::min(32, unroll * (32 / lpr));
+  const long long n_warps = (long long)grid * kWarpsPerBlock;
+  uint32_t shift = p_in.tile_shift;
+  if (shift < 3 || shift > 5) {
+    shift = 5;
+    while (shift > 3 && (1 << (shift - 1)) >= rows_per_pass) {
+      const long long tiles = ((long long)p.n_keys + (1ll << shift) - 1) >> shift;
+      const long long rounds = (tiles + n_warps - 1) / n_warps;
+      if (tiles <= n_warps || (double)tiles / (double)(rounds * n_warps) >= 0.9) break;
+      shift--;
+    }
+  }
+  p.tile_shift = shift;
+  const int tiles = (int)(((long long)p.n_keys + (1ll << shift) - 1) >> shift);
   grid = std::max(1, std::min(grid, (tiles + kWarpsPerBlock - 1) / kWarpsPerBlock));
 #define UGC_LAUNCH_DIRECT(KEYT, VEC)                                                              \
-  return launch_pdl(extract_direct_kernel<KEYT, VEC>, grid, kBlock, 0, stream, pdl,                \
-                    static_cast<const KEYT*>(keys), p)
+  do {                                                                                            \
+    if (deep)                                                                                     \
+      return launch_pdl(extract_direct_kernel<KEYT, VEC, true>, grid, kBlock, 0, stream, pdl,      \
+                        static_cast<const KEYT*>(keys), p);                                       \
+    return launch_pdl(extract_direct_kernel<KEYT, VEC, false>, grid, kBlock, 0, stream, pdl,       \
+                      static_cast<const KEYT*>(keys), p);                                         \
+  } while (0)
   if (key_bytes == 8) {
     if (vec == 32) UGC_LAUNCH_DIRECT(long long, 32);
     if (vec == 16) UGC_LAUNCH_DIRECT(long long, 16);
@@ -1235,13 +1347,12 @@ cudaError_t launch_gather_roles(const GatherParams& p_in, int grid, int block, i
 }
 
 cudaError_t launch_fill_scatter(const void* host_table, void* slice, const uint32_t* keys,
-                                const uint32_t* slots, uint32_t slot_base, uint32_t n,
-                                uint32_t row_bytes, int empty_feat, int grid, cudaStream_t stream) {
+                                const SlotView& slots, uint32_t n, uint32_t row_bytes,
+                                int empty_feat, int grid, cudaStream_t stream) {
   if (n == 0) return cudaSuccess;
   KeySlotIndex ix;
   ix.keys = keys;
   ix.slots = slots;
-  ix.slot_base = slot_base;
   ix.host_mask = host_mask_of(empty_feat);
   ix.host = static_cast<const char*>(host_table);
   ix.slice = static_cast<char*>(slice);
@@ -1262,11 +1373,16 @@ cudaError_t launch_table_clear(const TableView& t, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_table_insert(const TableView& t, const uint32_t* keys, const uint32_t* offs,
-                                uint32_t off_base, uint32_t loc, uint32_t n, Counters* counters,
-                                cudaStream_t stream) {
+cudaError_t launch_table_insert(const TableView& t, const uint32_t* keys, const SlotView& offs,
+                                uint32_t loc, uint32_t n, Counters* counters, cudaStream_t stream) {
   if (n == 0) return cudaSuccess;
-  table_insert_kernel<<<grid_for(n), kBlock, 0, stream>>>(t, keys, offs, off_base, loc, n, counters);
+  table_insert_kernel<<<grid_for(n), kBlock, 0, stream>>>(t, keys, offs, loc, n, counters);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_iota(uint32_t* dst, uint32_t start, uint32_t n, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  iota_kernel<<<std::min(grid_for(n), 148 * 8), kBlock, 0, stream>>>(dst, start, n);
   return cudaGetLastError();
 }
 
@@ -1285,7 +1401,7 @@ cudaError_t launch_table_words(const TableView& t, const uint32_t* keys, uint32_
 }
 
 cudaError_t launch_table_resolve(const TableView& peer, const uint32_t* keys, uint32_t n,
-                                 uint32_t expect_loc, uint32_t* offs, Counters* counters,
+                                 uint32_t expect_loc, const SlotView& offs, Counters* counters,
                                  cudaStream_t stream) {
   if (n == 0) return cudaSuccess;
   table_resolve_kernel<<<grid_for(n), kBlock, 0, stream>>>(peer, keys, n, expect_loc, offs, counters);

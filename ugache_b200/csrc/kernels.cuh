@@ -31,31 +31,35 @@ cudaError_t launch_gather_roles(const GatherParams& p, int grid, int block, int 
 
 // Lookup and row copy in one kernel (no index lists): out[i] = row of keys[i].  `grid` is
 // the most CTAs to use (a multiple of the SM count); fewer are launched for small batches.
+// `deep`: twice the rows in flight per warp at 3 instead of 4 CTAs per SM.  p.tile_shift 3..5
+// forces tiles of 8 / 16 / 32 keys; anything else lets the launcher choose.
 cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectParams& p, int grid,
-                                  int vec_bytes, bool pdl, cudaStream_t stream);
+                                  int vec_bytes, bool deep, bool pdl, cudaStream_t stream);
 
 // Widest of 32 / 16 / 4 bytes, not above `want`, that divides row_bytes and the address of
 // `out` and of every non-null source base: rows then start on a multiple of it on both sides.
 int usable_vec_bytes(uint32_t row_bytes, int want, const void* out, const void* const* src_base,
                      int n_src);
 
-// slice[slot(j)] = host[key(j) & mask]; slots == nullptr means slot(j) = slot_base + j.
+// slice[slot(j)] = host[key(j) & mask]; slot(j) as SlotView describes.
 cudaError_t launch_fill_scatter(const void* host_table, void* slice, const uint32_t* keys,
-                                const uint32_t* slots, uint32_t slot_base, uint32_t n,
-                                uint32_t row_bytes, int empty_feat, int grid, cudaStream_t stream);
+                                const SlotView& slots, uint32_t n, uint32_t row_bytes,
+                                int empty_feat, int grid, cudaStream_t stream);
+// dst[i] = start + i
+cudaError_t launch_iota(uint32_t* dst, uint32_t start, uint32_t n, cudaStream_t stream);
 
 cudaError_t launch_table_clear(const TableView& t, cudaStream_t stream);
-// word(j) = pack(loc, offs ? offs[j] : off_base + j)
-cudaError_t launch_table_insert(const TableView& t, const uint32_t* keys, const uint32_t* offs,
-                                uint32_t off_base, uint32_t loc, uint32_t n, Counters* counters,
-                                cudaStream_t stream);
+// word(j) = pack(loc, slot(j)), slot(j) as SlotView describes
+cudaError_t launch_table_insert(const TableView& t, const uint32_t* keys, const SlotView& offs,
+                                uint32_t loc, uint32_t n, Counters* counters, cudaStream_t stream);
 cudaError_t launch_table_evict(const TableView& t, const uint32_t* keys, uint32_t n,
                                Counters* counters, cudaStream_t stream);
 cudaError_t launch_table_words(const TableView& t, const uint32_t* keys, uint32_t n,
                                uint32_t* words, cudaStream_t stream);
-// offs[j] = offset the peer's table holds for keys[j] (must be stored on `expect_loc`).
+// Entry j of `offs` (a plain array or a window of the free-slot ring) = offset the peer's
+// table holds for keys[j] (must be stored on `expect_loc`).
 cudaError_t launch_table_resolve(const TableView& peer, const uint32_t* keys, uint32_t n,
-                                 uint32_t expect_loc, uint32_t* offs, Counters* counters,
+                                 uint32_t expect_loc, const SlotView& offs, Counters* counters,
                                  cudaStream_t stream);
 
 // Whole-id-space classification into ascending key lists (see ClassifyParams).  Pass 1+2

@@ -40,6 +40,44 @@ void b200_link_model(int num_device, double* t_local, double* t_remote, double* 
   *t_cpu = 8000.0 / 64.0;
 }
 
+LinkDesc b200_link_desc(int num_device, uint32_t row_bytes, double bw_local_override,
+                        double bw_remote_override, double bw_host_override) {
+  LinkDesc d;
+  const int G = num_device < 1 ? 1 : num_device;
+  d.num_device = G;
+  // Nominal link rates of the platform; the host side of the machines measured sustains about
+  // 100 GB/s for all GPUs together (eight concurrent device-to-host copies: 94 GB/s), so with
+  // more than one GPU reading host rows each gets its share of that, not its own 64 GB/s.
+  d.bw_local_gbs = bw_local_override > 0 ? bw_local_override : 8000.0;
+  d.bw_remote_gbs = G > 1 ? (bw_remote_override > 0 ? bw_remote_override : 900.0) : 0.0;
+  d.host_total_gbs = 100.0;
+  d.host_rows_per_s = 30e6;  // scattered 128..512-byte rows of pinned memory, per GPU, measured
+  double host = bw_host_override > 0 ? bw_host_override : 64.0;
+  if (bw_host_override <= 0) {
+    host = std::min(host, d.host_total_gbs / G);
+    if (row_bytes) host = std::min(host, d.host_rows_per_s * row_bytes / 1e9);
+  }
+  d.bw_host_gbs = host;
+  d.lat_local_us = 0.8;
+  d.lat_remote_us = 2.0;
+  d.lat_host_us = 2.5;
+  // placement ratios keep the nominal rates (what the reference's tables hold: local / link)
+  d.t_local = 1.0;
+  d.t_remote = G > 1 ? d.bw_local_gbs / d.bw_remote_gbs : 0.0;
+  d.t_cpu = d.bw_local_gbs / d.bw_host_gbs;
+  // Little's law: bytes in flight = bandwidth x latency; one 256-thread CTA of the gather keeps
+  // 256 x 16 B x 4 rows = 16 KiB in flight.  Twice that many CTAs as a margin for uneven rows.
+  const double inflight = 256.0 * 16.0 * 4.0;
+  auto ctas = [&](double bw_gbs, double lat_us) {
+    int n = (int)std::ceil(bw_gbs * 1e3 * lat_us / inflight) * 2;
+    return n < 2 ? 2 : n;
+  };
+  d.host_ctas = ctas(std::min(64.0, d.bw_host_gbs > 0 ? 64.0 : 0.0), d.lat_host_us);
+  d.remote_ctas = G > 1 ? ctas(d.bw_remote_gbs, d.lat_remote_us) : 2;
+  d.per_peer_ctas = G > 1 ? std::max(1, d.remote_ctas / (G - 1)) : 0;
+  return d;
+}
+
 bool reference_prefers_flat_table(uint64_t num, uint64_t N) {
   uint64_t e = (uint64_t)(1.0 + std::log2((double)(num >> 1)));
   uint64_t table_size = ((uint64_t)1 << e) << 2;

@@ -38,6 +38,26 @@ std::string validate_placement(const Placement& p, int num_device, uint64_t num_
 // 900 GB/s port, so no division applies here).
 void b200_link_model(int num_device, double* t_local, double* t_remote, double* t_cpu);
 
+// What one GPU of an NVSwitch-connected B200 box can pull from each kind of source while all
+// `num_device` GPUs of the job do the same, and what it takes to keep each link busy: the
+// B200 counterpart of the reference's per-platform link table with its SM counts per link
+// (AsymmLinkDesc::AutoBuild, coll_cache_lib/coll_cache/asymm_link_desc.cc:242-392).
+struct LinkDesc {
+  int num_device;
+  double bw_local_gbs;     // HBM3e, read or write
+  double bw_remote_gbs;    // all peers together into this GPU: one NVLink port; 0 with one GPU
+  double bw_host_gbs;      // host rows into this GPU (link, shared host side, scattered-row rate)
+  double lat_local_us, lat_remote_us, lat_host_us;  // load-to-use latencies, for Little's law
+  double host_rows_per_s;  // scattered rows of pinned host memory per second per GPU
+  double host_total_gbs;   // what the host side sustains for all GPUs together
+  double t_local, t_remote, t_cpu;  // time-per-byte ratios for the placement solvers
+  int host_ctas, remote_ctas, per_peer_ctas;  // 256-thread CTAs that keep each far link full
+};
+// row_bytes == 0: bandwidth figures only (no scattered-row term).  Zero / negative overrides
+// are ignored.
+LinkDesc b200_link_desc(int num_device, uint32_t row_bytes, double bw_local_override = 0,
+                        double bw_remote_override = 0, double bw_host_override = 0);
+
 // IntuitiveSolver / RepSolver / CliquePartSolver of the reference
 // (coll_cache_lib/coll_cache/optimal_solver_class.cc:1251-1404, :1869-1924, :1926-2058).
 // plus UGC_POLICY_SPLIT_SEARCH, which has no counterpart among them: it stands in for the

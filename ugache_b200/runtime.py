@@ -38,21 +38,25 @@ def _ptr(a):
     return a.ctypes.data_as(C.c_void_p)
 
 
-# Scattered rows of pinned host memory arrive at about this rate on the B200 machines measured,
-# whatever the row size up to 512 B; the host link is then slower than its bandwidth says.
-HOST_ROWS_PER_S = 30e6
+def link_desc(num_device, row_bytes=0):
+    """The library's B200 link description as a dict (bandwidths, latencies, the scattered
+    host-row rate, time-per-byte ratios, CTA budgets of the far links)."""
+    d = _lib.LinkDesc()
+    d.struct_size = C.sizeof(_lib.LinkDesc)
+    check(_lib.lib().ugc_link_desc(num_device, row_bytes or 0, C.byref(d)))
+    return {name: getattr(d, name) for name, _ in d._fields_ if name != "struct_size"}
 
 
 def link_model(num_device, row_bytes=None):
     """(t_local, t_remote, t_cpu) time-per-byte ratios of the library's B200 link model.  With
-    ``row_bytes`` the host term is raised to what scattered row reads really cost
-    (``HOST_ROWS_PER_S`` rows per second) when that is slower than the link bandwidth."""
+    ``row_bytes`` the host term is what scattered row reads really cost (the row rate and the
+    host side shared by ``num_device`` GPUs) when that is slower than the link bandwidth."""
+    if row_bytes:
+        d = link_desc(num_device, row_bytes)
+        return d["t_local"], d["t_remote"] if num_device > 1 else 8000.0 / 900.0, d["t_cpu"]
     tl, tr, tc = C.c_double(), C.c_double(), C.c_double()
     check(_lib.lib().ugc_link_model(num_device, C.byref(tl), C.byref(tr), C.byref(tc)))
-    t_cpu = tc.value
-    if row_bytes:
-        t_cpu = max(t_cpu, tl.value * 8000e9 / (HOST_ROWS_PER_S * row_bytes))
-    return tl.value, tr.value, t_cpu
+    return tl.value, tr.value, tc.value
 
 
 def solve_placement(policy, num_device, rank_ids, rank_freqs, cache_percent, t_local=None,
