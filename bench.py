@@ -93,6 +93,11 @@ def parse_args():
                          "skew and capacity sweep over one host table; prints one JSON line with a "
                          "point per (alpha, ratio) instead of the benchmark line")
     ap.add_argument("--sweep-out", default="", help="write extra per-phase numbers here (json)")
+    ap.add_argument("--in-process", type=int, default=0,
+                    help="G > 1: all G replicas in THIS process on devices 0..G-1 (peers wired by "
+                         "ugc_connect_local), lookups enqueued device after device from one "
+                         "thread; prints one JSON line.  The shape a profiler of one process sees "
+                         "with real NVLink traffic in it")
     ap.add_argument("--host-probe", action="store_true",
                     help="one GPU, nothing cached: rate of scattered host rows (zero-copy reads of "
                          "the pinned table) against rows per lookup, random or ascending key "
@@ -621,6 +626,95 @@ def connect_ranks(cache, rank, world, dev, stream):
     barrier()
     cache.attach_peers(rank, stream)
     barrier()
+
+
+# ---------------------------------------------------------------------------------------
+def run_in_process(a):
+    """All replicas of the job in one process, one per device.  Each step enqueues one lookup
+    per device; device time per lookup is taken with events on each device's stream."""
+    import torch
+    from ugache_b200 import build as ubuild
+    ubuild.build()
+    from ugache_b200 import runtime as rt, workload as wl
+    G = a.in_process
+    if torch.cuda.device_count() < G:
+        print(json.dumps({"in_process": G, "unavailable": "needs %d GPUs, %d visible"
+                          % (G, torch.cuda.device_count())}), flush=True)
+        return
+    elem = 4 if a.dtype == "float32" else 2
+    row_bytes = a.dim * elem
+    torch.cuda.set_device(0)
+    table = HostTable(a.rows, row_bytes, 0, 1, "inproc", library_owned=True)
+    s0 = torch.cuda.current_stream().cuda_stream
+    rt.gen_table(table.map_for_gpu(), a.seed, 0, a.rows, a.dim, elem, s0)
+    torch.cuda.synchronize()
+    ids, freqs = wl.analytic_hotness(a.rows, a.alpha)
+    placement = rt.solve_placement(a.policy, G, ids, freqs, a.cache_pct * 100.0)
+    del ids, freqs
+    cache = rt.Cache(G, a.rows, row_bytes, a.cache_pct, max_batch=a.batch, register_host=False)
+    cache.set_placement(placement)
+    for r in range(G):
+        with torch.cuda.device(r):
+            cache.build(r, r, table.ptr, torch.cuda.current_stream().cuda_stream)
+    cache.connect_local()
+    for r in range(G):
+        with torch.cuda.device(r):
+            cache.attach_peers(r, torch.cuda.current_stream().cuda_stream)
+    mode = {"": None, "auto": 0, "grouped": 1, "direct": 2}[a.extract_mode]
+    total = a.warmup + a.steps
+    keys_np = [make_keys(a, r, total) for r in range(G)]
+    keys_dev, outs, streams = [], [], []
+    for r in range(G):
+        dev = torch.device("cuda", r)
+        if mode is not None:
+            cache.tune(r, extract_mode=mode)
+        keys_dev.append(torch.from_numpy(keys_np[r]).to(dev))
+        outs.append(torch.empty((a.batch, row_bytes), dtype=torch.uint8, device=dev))
+        streams.append(torch.cuda.current_stream(dev).cuda_stream)
+
+    def step(i):
+        for r in range(G):
+            cache.lookup_ptr(r, keys_dev[r][i].data_ptr(), 8, a.batch, outs[r].data_ptr(), streams[r])
+
+    for i in range(a.warmup):
+        step(i)
+    ev = []
+    for r in range(G):
+        with torch.cuda.device(r):
+            torch.cuda.synchronize()
+            ev.append((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
+    for r in range(G):
+        with torch.cuda.device(r):
+            ev[r][0].record()
+    for i in range(a.warmup, total):
+        step(i)
+    for r in range(G):
+        with torch.cuda.device(r):
+            ev[r][1].record()
+    step_us = []
+    for r in range(G):
+        with torch.cuda.device(r):
+            torch.cuda.synchronize()
+            step_us.append(ev[r][0].elapsed_time(ev[r][1]) / a.steps * 1e3)
+    ok = None
+    if a.verify:
+        from oracle import oracle as orc
+        ok = True
+        for r in range(G):
+            want = orc.gen_rows_for_keys(a.seed, keys_np[r][total - 1], a.dim,
+                                         np.float32 if elem == 4 else np.float16)
+            ok = ok and bool(outs[r].cpu().numpy().tobytes() == want.tobytes())
+    stats = [cache.stats(r) for r in range(G)]
+    print(json.dumps({
+        "in_process": G, "config": config_block(a, row_bytes), "steps": a.steps, "warmup": a.warmup,
+        "step_us_per_device": step_us,
+        "gbs_per_device": [a.batch * row_bytes / u / 1e3 for u in step_us],
+        "last_split": [{"local": st["last_local"], "remote": st["last_remote"], "host": st["last_host"]}
+                       for st in stats],
+        "direct_share": [st["lookups_direct"] / max(st["lookups"], 1) for st in stats],
+        "verified_vs_oracle": ok}), flush=True)
+    cache.close()
+    table.release()
 
 
 # ---------------------------------------------------------------------------------------
@@ -1215,6 +1309,8 @@ def main():
         run_reference(a)
     elif a.impl == "reference-gpu":
         run_reference_gpu(a)
+    elif a.in_process > 1:
+        run_in_process(a)
     elif a.host_probe:
         run_host_probe(a)
     elif a.sweep:

@@ -3,6 +3,7 @@
 // aborts: every entry point returns a ugc_status and records a per-thread message.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <omp.h>
 #include <sys/socket.h>
 #include <sys/time.h>
 #include <sys/un.h>
@@ -574,7 +575,7 @@ struct Replica {
   // the host-row share of the last finished lookup, read from the pinned mirror below
   int extract_mode = UGC_EXTRACT_AUTO;
   int direct_grid = 0;
-  double direct_host_share = 0.05;
+  double direct_host_share = 0.10;
   Feedback* feedback = nullptr;      // pinned host memory, written by the kernels
   Feedback* feedback_dev = nullptr;  // the same memory as the device addresses it
   uint64_t lookups_direct = 0;
@@ -1140,17 +1141,35 @@ static int load_placement(ugc_ctx* c, Placement* dst, const uint32_t* n2b, const
   if (!n2b || !bp || !ba || B <= 0) return fail(UGC_ERR_INVALID, "null placement array");
   const int G = c->cfg.num_device;
   const uint64_t N = c->cfg.num_total_item;
-  Placement p;
+  // The per-key array is the large one (4 bytes per id: 1.6 GB at 4*10^8 ids).  It is copied
+  // into storage that is kept from one refresh to the next (no fresh pages to fault in), by
+  // several threads, and its block ids are range-checked in the same pass.
+  Placement& p = *dst;
+  p.valid = false;
   p.num_block = B;
   p.num_device = G;
-  p.nid_to_block.assign(n2b, n2b + N);
+  if (p.nid_to_block.size() != N) p.nid_to_block.resize(N);
+  uint32_t* copy = p.nid_to_block.data();
+  const uint32_t nb = (uint32_t)B;
+  int bad = 0;
+  const int threads = std::max(1, std::min(16, omp_get_num_procs()));
+#pragma omp parallel for schedule(static) num_threads(threads) reduction(| : bad)
+  for (int64_t i = 0; i < (int64_t)N; i++) {
+    const uint32_t b = n2b[i];
+    copy[i] = b;
+    bad |= (b >= nb);
+  }
+  if (bad) return fail(UGC_ERR_INVALID, "placement rejected: nid_to_block holds a block id >= num_block");
   p.block_placement.assign(bp, bp + B);
   p.block_access_from.assign(ba, ba + (size_t)G * B);
-  if (bd) p.block_density.assign(bd, bd + B);
-  std::string err = validate_placement(p, G, N);
+  if (bd) {
+    p.block_density.assign(bd, bd + B);
+  } else {
+    p.block_density.clear();
+  }
+  std::string err = validate_placement(p, G, N, false);
   if (!err.empty()) return fail(UGC_ERR_INVALID, "placement rejected: %s", err.c_str());
   p.valid = true;
-  *dst = std::move(p);
   return UGC_OK;
 }
 
@@ -1780,8 +1799,8 @@ int ugc_refresh_commit(ugc_ctx* c) {
   for (auto& r : c->reps)
     if (r.built && r.refresh_open)
       return fail(UGC_ERR_STATE, "replica %d has not finished its refresh", r.id);
-  c->cur = std::move(c->next);
-  c->next = Placement{};
+  std::swap(c->cur, c->next);  // the old placement's storage serves the next refresh
+  c->next.valid = false;
   return UGC_OK;
 }
 

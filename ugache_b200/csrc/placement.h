@@ -29,7 +29,10 @@ struct Placement {
 // Checks that the arrays describe a placement the runtime can serve: every reader's
 // source for a block stores that block, and a GPU that stores a block reads its own copy.
 // Returns an empty string or the reason.
-std::string validate_placement(const Placement& p, int num_device, uint64_t num_total_item);
+// `check_block_ids` = false skips the pass over nid_to_block (for callers that range-checked
+// the ids while copying them).
+std::string validate_placement(const Placement& p, int num_device, uint64_t num_total_item,
+                               bool check_block_ids = true);
 
 // Time-per-byte ratios local : peer : host on an NVSwitch-connected B200 box (HBM3e ~8 TB/s,
 // NVLink 5 900 GB/s per direction, PCIe Gen5 ~64 GB/s).  With G-1 peers read concurrently the
