@@ -93,6 +93,9 @@ def parse_args():
                          "skew and capacity sweep over one host table; prints one JSON line with a "
                          "point per (alpha, ratio) instead of the benchmark line")
     ap.add_argument("--sweep-out", default="", help="write extra per-phase numbers here (json)")
+    ap.add_argument("--suite", default="",
+                    help="';'-separated workloads run one after the other over one host-table "
+                         "allocation: c2, sweep, gnn, c4 (e.g. 'c2;sweep;gnn;c4'); one JSON line each")
     ap.add_argument("--in-process", type=int, default=0,
                     help="G > 1: all G replicas in THIS process on devices 0..G-1 (peers wired by "
                          "ugc_connect_local), lookups enqueued device after device from one "
@@ -480,35 +483,23 @@ def run_reference_gpu(a):
 
 
 # ---------------------------------------------------------------------------------------
-def run_sweep(a):
+def run_sweep(a, job=None):
     """Skew and capacity sweep at 1, 2, 4 or 8 GPUs (one rank per GPU under
     torch.distributed.run): for every (alpha, cache ratio) a fresh cache is built over the same
     host table on every rank, peers are attached, and `--steps` lookups of `--batch` keys per
     rank are timed (max over ranks).  Every point is checked against the oracle on every rank."""
     import torch
-    from ugache_b200 import build as ubuild
-    ubuild.build()
     from ugache_b200 import runtime as rt, workload as wl
     alphas, ratios = [[float(x) for x in part.split(",") if x] for part in a.sweep.split(";")]
-    rank, world, local = dist_env()
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-        _DIST["on"] = True
+    own_job = job is None
+    if own_job:
+        job = open_job()
+    rank, world, local, dev = job["rank"], job["world"], job["local"], job["dev"]
     G = world
     elem = 4 if a.dtype == "float32" else 2
     row_bytes = a.dim * elem
-    host_rows = (1 << a.empty_feat) if a.empty_feat else a.rows
-    table = HostTable(host_rows, row_bytes, rank, world, os.environ.get("MASTER_PORT", "0") + "s",
-                      library_owned=True)
-    table_dev = table.map_for_gpu()
+    table, host_rows = job_table(a, job, {})
     stream = torch.cuda.current_stream().cuda_stream
-    if rank == 0:
-        rt.gen_table(table_dev, a.seed, 0, host_rows, a.dim, elem, stream)
-        torch.cuda.synchronize()
-    barrier()
     hbm_peak, peak_kind = measured_peaks()
     out = torch.empty((a.batch, row_bytes), dtype=torch.uint8, device=dev)
     total = a.warmup + a.steps
@@ -599,12 +590,43 @@ def run_sweep(a):
         if a.sweep_out:
             with open(a.sweep_out, "w") as f:
                 json.dump(line, f)
-    table.release()
-    barrier()
-    table.unlink()
-    if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+    del out
+    torch.cuda.empty_cache()
+    if own_job:
+        close_job(job)
+    return line
+
+
+def run_suite(a):
+    """Several workloads in one run over ONE host-table allocation (allocating and registering
+    51 GB per process is most of a run's set-up time): 'c2' the default DLR workload, 'sweep'
+    the skew and capacity sweep, 'gnn' the sampled-graph workload, 'c4' the 400 M x 64 fp16
+    workload with a refresh.  One JSON line per workload on rank 0."""
+    import copy
+    job = open_job()
+    for name in [x for x in a.suite.split(";") if x]:
+        b = copy.copy(a)
+        b.suite = ""
+        if name == "c2":
+            run_ours(b, job)
+        elif name == "sweep":
+            b.sweep = a.sweep or "0.8,1.0,1.2,1.4;0.02,0.05,0.10,0.20"
+            b.steps, b.warmup = min(a.steps, 30), min(a.warmup, 3)
+            run_sweep(b, job)
+        elif name == "gnn":
+            b.workload, b.cache_pct = "gnn", 0.05
+            b.steps, b.warmup, b.no_e2e, b.no_cpu_baseline = min(a.steps, 20), min(a.warmup, 3), True, True
+            run_ours(b, job)
+        elif name == "c4":
+            b.rows, b.dim, b.dtype, b.cache_pct, b.alpha = 400_000_000, 64, "float16", 0.2, 1.05
+            b.batch = 65536 * 26
+            b.steps, b.warmup, b.no_cpu_baseline = min(a.steps, 30), min(a.warmup, 3), True
+            b.refresh = a.refresh or 0.02
+            run_ours(b, job)
+        else:
+            raise SystemExit("unknown suite entry %r" % name)
+        barrier()
+    close_job(job)
 
 
 def connect_ranks(cache, rank, world, dev, stream):
@@ -778,44 +800,92 @@ def run_host_probe(a):
 
 
 # ---------------------------------------------------------------------------------------
-def run_ours(a):
+def open_job():
+    """Device, process group and the host-table slot shared by the workloads of one run."""
     import torch
     from ugache_b200 import build as ubuild
     ubuild.build()
-    from ugache_b200 import runtime as rt, workload as wl
-
     rank, world, local = dist_env()
-    if world != a.gpus and world > 1:
-        a.gpus = world
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and not _DIST["on"]:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
         _DIST["on"] = True
+    return {"rank": rank, "world": world, "local": local, "dev": dev, "table": None}
+
+
+def close_job(job):
+    if job["table"] is not None:
+        job["table"].release()
+        barrier()
+        job["table"].unlink()
+        job["table"] = None
+    if job["world"] > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+        _DIST["on"] = False
+
+
+def job_table(a, job, note):
+    """The host table for workload `a`: allocated (and registered for the GPU) once per run and
+    refilled when a later workload of the same run has other contents but the same size."""
+    import torch
+    from ugache_b200 import runtime as rt
+    elem = 4 if a.dtype == "float32" else 2
+    row_bytes = a.dim * elem
+    rank, world = job["rank"], job["world"]
+    tag = os.environ.get("MASTER_PORT", "0")
+    host_rows = (1 << a.empty_feat) if a.empty_feat else a.rows
+    table = job["table"]
+    if table is not None and table.nbytes != host_rows * row_bytes:
+        table.release()
+        barrier()
+        table.unlink()
+        table = job["table"] = None
+    if table is None:
+        try:
+            table = HostTable(host_rows, row_bytes, rank, world, tag, library_owned=True)
+            table.map_for_gpu()
+        except Exception as e:  # not enough host memory: the reference's mock-table mode
+            note["host_table_fallback"] = "%s: %s" % (type(e).__name__, str(e)[:80])
+            a.empty_feat = 24
+            host_rows = 1 << 24
+            table = HostTable(host_rows, row_bytes, rank, world, tag + "m", library_owned=True)
+            table.map_for_gpu()
+        table.contents = None
+        job["table"] = table
+    contents = (a.seed, host_rows, a.dim, elem)
+    if table.contents != contents:
+        stream = torch.cuda.current_stream().cuda_stream
+        barrier()
+        if rank == 0:
+            rt.gen_table(table.map_for_gpu(), a.seed, 0, host_rows, a.dim, elem, stream)
+            torch.cuda.synchronize()
+        table.contents = contents
+        barrier()
+    return table, host_rows
+
+
+def run_ours(a, job=None):
+    import torch
+    from ugache_b200 import runtime as rt, workload as wl
+
+    own_job = job is None
+    if own_job:
+        job = open_job()
+    rank, world, local, dev = job["rank"], job["world"], job["local"], job["dev"]
+    if world != a.gpus and world > 1:
+        a.gpus = world
     G = world
     elem = 4 if a.dtype == "float32" else 2
     row_bytes = a.dim * elem
-    tag = os.environ.get("MASTER_PORT", "0")
     t_setup = time.time()
 
     # ---- host table ---------------------------------------------------------------
     note = {}
-    try:
-        host_rows = (1 << a.empty_feat) if a.empty_feat else a.rows
-        table = HostTable(host_rows, row_bytes, rank, world, tag, library_owned=True)
-        table_dev = table.map_for_gpu()
-    except Exception as e:  # not enough host memory: the reference's mock-table mode
-        note["host_table_fallback"] = "%s: %s" % (type(e).__name__, str(e)[:80])
-        a.empty_feat = 24
-        host_rows = 1 << 24
-        table = HostTable(host_rows, row_bytes, rank, world, tag + "m", library_owned=True)
-        table_dev = table.map_for_gpu()
+    table, host_rows = job_table(a, job, note)
     stream = torch.cuda.current_stream().cuda_stream
-    if rank == 0:
-        rt.gen_table(table_dev, a.seed, 0, host_rows, a.dim, elem, stream)
-        torch.cuda.synchronize()
-    barrier()
 
     # ---- hotness, placement, build ---------------------------------------------------
     gnn = None
@@ -1295,12 +1365,12 @@ def run_ours(a):
             with open(a.sweep_out, "w") as f:
                 json.dump(line, f)
     cache.close()
-    table.release()
+    del cache, keys_dev, out
+    torch.cuda.empty_cache()
     barrier()
-    table.unlink()
-    if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+    if own_job:
+        close_job(job)
+    return line
 
 
 def main():
@@ -1309,6 +1379,8 @@ def main():
         run_reference(a)
     elif a.impl == "reference-gpu":
         run_reference_gpu(a)
+    elif a.suite:
+        run_suite(a)
     elif a.in_process > 1:
         run_in_process(a)
     elif a.host_probe:

@@ -154,9 +154,15 @@ typedef struct {
   uint64_t last_index_ns;      /* grouped extraction: device-clock time from the start of
                                   the lookup kernel to the start of the gather kernel (the
                                   index-building phase); 0 for a direct extraction        */
+  uint64_t lookups_host_ordered; /* grouped lookups whose host list was put in address order */
   uint64_t lookups_direct;     /* lookups that took the direct (one-kernel) extraction  */
   uint64_t kernel_launches;    /* kernels launched by lookups: 2 per grouped, 1 per direct */
 } ugc_stats_t;
+
+/* sizeof of the structs of this header, in the order ugc_config, ugc_peer_handle,
+ * ugc_stats_t, ugc_tuning, ugc_link_desc_t: lets a binding in another language check its own
+ * declarations against the library it loaded.  No reference counterpart. */
+int ugc_abi_sizes(uint32_t sizes[5]);
 
 const char* ugc_version(void);
 const char* ugc_last_error(void);
@@ -287,6 +293,25 @@ int ugc_lookup_i64(ugc_ctx* ctx, int replica_id, const int64_t* keys, size_t n, 
 int ugc_lookup_i64_static(ugc_ctx* ctx, int replica_id, const int64_t* keys, size_t n, void* out,
                           void* stream);
 
+/* Deduplicated lookup, all on the GPU: finds the distinct keys of the batch, extracts each of
+ * their rows once and returns the index that reassembles the batch.  A recommendation batch
+ * under a skewed distribution repeats its hottest ids thousands of times; a consumer that
+ * pools or scatters by index anyway (embedding-bag forward, sparse-gradient backward) then
+ * needs every distinct row once, which also spares most of the output write.
+ *   unique_keys[0 .. *n_unique)  the distinct keys (same width as keys), in order of discovery;
+ *   out_rows[j, :]               row of unique_keys[j];
+ *   inverse[i]                   index of keys[i] in unique_keys (-1 for an id outside the key
+ *                                space, which is counted in err_key_range);
+ *   *n_unique                    their number -- device memory like the rest, so nothing here
+ *                                synchronises; capacity of out_rows / unique_keys: n entries.
+ * keys: key_bytes 4 or 8.  Uses one 32-bit stamp per id of the key space (allocated on the
+ * first call); at most 2^24-2 keys per call.  After the call ugc_stats' last_local/remote/host
+ * add up to the number of distinct keys.  The reference has no such call; its applications
+ * deduplicate before they look up (example/dlr and the GNN samplers hand over unique ids). */
+int ugc_lookup_unique(ugc_ctx* ctx, int replica_id, const void* keys, int key_bytes, size_t n,
+                      void* out_rows, void* unique_keys, int32_t* inverse, uint32_t* n_unique,
+                      void* stream);
+
 /* Grows the per-replica lookup scratch so that batches of up to max_batch keys are accepted
  * (the reference re-allocates its output buffer when a larger batch shows up,
  * python/collcache/torch/adapter.cc:213-224).  Must not run while a lookup of that replica
@@ -374,6 +399,10 @@ typedef struct {
                                      16 or 32; 0 = the largest that balances the warps      */
   int32_t direct_deep;            /* direct kernel: 1 = twice the rows in flight per warp at
                                      3 instead of 4 CTAs per SM                             */
+  int32_t host_order_min_rows;    /* grouped extraction: order the host list by address (two
+                                     small kernels between lookup and gather) when the last
+                                     finished lookup took at least this many rows from the
+                                     host table; 0 = never                                  */
   int32_t gather_dynamic;         /* grouped gather: 1 = lists are handed out in chunks and a
                                      CTA whose own list is drained takes chunks of the other
                                      groups' lists; 0 = fixed striding inside each group     */

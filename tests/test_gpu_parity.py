@@ -27,7 +27,8 @@ def extract_mode(request, monkeypatch):
     # and the mode switch (keeps the suite short)
     wide = {"test_golden_cases_bit_exact", "test_ragged_batch_sizes", "test_auto_mode_follows_the_host_share",
             "test_duplicates_and_single_source_batches", "test_out_of_range_keys_are_counted_and_skipped",
-            "test_unaligned_output_and_host_table", "test_refresh_keeps_results_identical"}
+            "test_unaligned_output_and_host_table", "test_refresh_keeps_results_identical",
+            "test_host_list_in_address_order"}
     if request.param in ("auto", "grouped_static") and request.node.originalname not in wide:
         pytest.skip("covered by the grouped and direct runs")
     monkeypatch.setenv("UGC_EXTRACT_MODE", request.param)
@@ -560,7 +561,9 @@ def test_host_buffers_in_place_and_staged(built_lib, golden_cases):
 
 def test_auto_mode_follows_the_host_share(built_lib, extract_mode):
     """In auto mode the first lookup is grouped; later ones go direct once a finished lookup
-    has shown a small host share, and back when the share is large."""
+    has shown a small host share, and back when the share is large.  A direct lookup's counts
+    reach the library with the start of the next lookup, so the switch back takes one lookup
+    longer than the switch forth."""
     if extract_mode != "auto":
         pytest.skip("only meaningful in auto mode")
     from ugache_b200 import runtime as rt, workload as wl
@@ -581,10 +584,15 @@ def test_auto_mode_follows_the_host_share(built_lib, extract_mode):
         assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
     st = cache.stats(0)
     assert st["lookups"] == 3 and st["lookups_direct"] == 2 and st["kernel_launches"] == 4
-    for keys in (cold, cold):        # first of these still direct (decided by the last hot one)
-        assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
+    for keys in (cold, cold, cold):  # two more direct ones (the mirror still shows hot batches)
+        got = lookup_np(cache, 0, keys)
+        assert got.tobytes() == orc.gather(table, keys).tobytes()
+        st = cache.stats(0)
+        assert (st["last_local"], st["last_remote"], st["last_host"], st["last_keys"]) == (0, 0, 6000, 6000)
+    assert st["lookups_direct"] == 4 and st["kernel_launches"] == 8
+    assert lookup_np(cache, 0, hot).tobytes() == orc.gather(table, hot).tobytes()   # still grouped
     st = cache.stats(0)
-    assert st["lookups_direct"] == 3 and st["kernel_launches"] == 7
+    assert st["lookups_direct"] == 4 and st["kernel_launches"] == 10 and st["last_local"] == 6000
     cache.close()
 
 
@@ -607,3 +615,42 @@ def test_golden_cases_at_configuration_sizes(built_lib, golden_cases_large, extr
             if w.G == 1 and w.pct == 0.0:
                 assert (st["last_local"], st["last_remote"], st["last_host"]) == (0, 0, len(keys))
         cache.close()
+
+
+def test_host_list_in_address_order(built_lib, extract_mode):
+    """Grouped extraction with the host list put in address order (counting sort between lookup
+    and gather) once a finished lookup has shown enough host rows: same bytes, and the stats say
+    the ordered path ran.  Batches with duplicates, with one bucket only, and with no host row."""
+    if extract_mode not in ("grouped", "grouped_static"):
+        pytest.skip("the ordering belongs to the grouped path")
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim = 300_000, 32
+    table = wl.table(61, N, dim)
+    ids, freqs = wl.analytic_hotness(N, 1.05)
+    cache = rt.Cache(1, N, dim * 4, 0.05, max_batch=1 << 16)
+    p = rt.solve_placement("rep", 1, ids, freqs, 5.0)
+    cache.set_placement(p)
+    host = pinned_table(table)
+    cache.build(0, 0, host.data_ptr())
+    cache.tune(0, host_order_min_rows=100)
+    rng = np.random.default_rng(7)
+    missing = np.nonzero(np.asarray(p.block_access_from).reshape(1, -1)[0][p.nid_to_block] != 0)[0]
+    cached = np.nonzero(np.asarray(p.block_access_from).reshape(1, -1)[0][p.nid_to_block] == 0)[0]
+    batches = [wl.zipf_keys(1, 50_000, N, 1.05),                       # mixed, many host rows
+               wl.zipf_keys(2, 50_000, N, 1.05),
+               rng.choice(missing, 20_000).astype(np.int64),           # host only, duplicates
+               np.sort(rng.choice(missing[:500], 3_000)).astype(np.int64),   # one address bucket
+               rng.choice(cached, 5_000).astype(np.int64),             # no host row at all
+               wl.zipf_keys(3, 65_536, N, 1.05)]                       # follows a batch without host rows: not ordered
+    for i, keys in enumerate(batches):
+        got = lookup_np(cache, 0, keys)
+        assert got.tobytes() == orc.gather(table, keys).tobytes(), i
+    st = cache.stats(0)
+    assert st["err_table"] == 0 and st["err_key_range"] == 0
+    # lookups 2..5 followed a lookup with >= 100 host rows; the one after the cached-only batch did not
+    assert st["lookups_host_ordered"] == 4
+    cache.reserve_batch(0, 1 << 17)                                    # drops and re-makes the ordered buffer
+    keys = wl.zipf_keys(4, 100_000, N, 1.05)
+    assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
+    assert cache.stats(0)["lookups_host_ordered"] == 5
+    cache.close()

@@ -243,3 +243,31 @@ def test_link_description_follows_the_number_of_gpus(built_lib):
     tl, tr, tc = rt.link_model(8, 512)
     assert (tl, tr, tc) == (d8["t_local"], d8["t_remote"], d8["t_cpu"])
     assert rt.link_model(8) == (1.0, 8000.0 / 900.0, 8000.0 / 64.0)                  # solver defaults
+
+
+def test_ctypes_structs_follow_the_header(built_lib):
+    """Field names and order of every struct in include/ugache_b200.h against the ctypes
+    declarations, and their sizes against the loaded library (ugc_abi_sizes)."""
+    import ctypes as C
+    import os
+    import re
+    from tests.conftest import ROOT
+    from ugache_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "ugache_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    pairs = (("ugc_config", _lib.Config), ("ugc_peer_handle", _lib.PeerHandle), ("ugc_stats_t", _lib.Stats),
+             ("ugc_tuning", _lib.Tuning), ("ugc_link_desc_t", _lib.LinkDesc))
+    for cname, cls in pairs:
+        end = header.index("} %s;" % cname)
+        body = header[header.rindex("typedef struct {", 0, end) + len("typedef struct {"):end]
+        names = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            for part in decl.split(","):
+                names.append(re.sub(r"\[.*\]", "", part.strip().split()[-1].lstrip("*")))
+        assert names == [f[0] for f in cls._fields_], cname
+    sizes = (C.c_uint32 * 5)()
+    assert _lib.lib().ugc_abi_sizes(C.byref(sizes)) == 0
+    assert list(sizes) == [C.sizeof(cls) for _, cls in pairs]

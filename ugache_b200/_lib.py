@@ -78,6 +78,7 @@ class Stats(C.Structure):
         ("last_remote_ns", C.c_uint64),
         ("last_host_ns", C.c_uint64),
         ("last_index_ns", C.c_uint64),
+        ("lookups_host_ordered", C.c_uint64),
         ("lookups_direct", C.c_uint64),
         ("kernel_launches", C.c_uint64),
     ]
@@ -99,6 +100,7 @@ class Tuning(C.Structure):
         ("direct_host_permille", C.c_int32),
         ("direct_tile_keys", C.c_int32),
         ("direct_deep", C.c_int32),
+        ("host_order_min_rows", C.c_int32),
         ("gather_dynamic", C.c_int32),
         ("host_zero_copy", C.c_int32),
     ]
@@ -128,6 +130,7 @@ _lib = None
 # name -> (restype, argtypes); every symbol include/ugache_b200.h declares
 _P, _I, _U64, _SZ, _D = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t, C.c_double
 SIGNATURES = {
+    "ugc_abi_sizes": (_I, [C.POINTER(C.c_uint32 * 5)]),
     "ugc_version": (C.c_char_p, []),
     "ugc_last_error": (C.c_char_p, []),
     "ugc_status_string": (C.c_char_p, [_I]),
@@ -149,6 +152,7 @@ SIGNATURES = {
     "ugc_lookup_u32": (_I, [_P, _I, _P, _SZ, _P, _P]),
     "ugc_lookup_i64": (_I, [_P, _I, _P, _SZ, _P, _P]),
     "ugc_lookup_i64_static": (_I, [_P, _I, _P, _SZ, _P, _P]),
+    "ugc_lookup_unique": (_I, [_P, _I, _P, _I, _SZ, _P, _P, _P, _P, _P]),
     "ugc_reserve_batch": (_I, [_P, _I, C.c_uint32]),
     "ugc_lookup_host": (_I, [_P, _I, _P, _I, _SZ, _P, _P]),
     "ugc_refresh_set_placement": (_I, [_P, _P, _P, _P, _P, _I]),
@@ -187,6 +191,14 @@ def lib():
             fn = getattr(_lib, name)
             fn.restype = res
             fn.argtypes = args
+        sizes = (C.c_uint32 * 5)()
+        _lib.ugc_abi_sizes(C.byref(sizes))
+        mine = [C.sizeof(t) for t in (Config, PeerHandle, Stats, Tuning, LinkDesc)]
+        if list(sizes) != mine:
+            _lib = None
+            raise ImportError("libugache_b200.so does not match this binding (struct sizes %s, "
+                              "expected %s): rebuild with `python -m ugache_b200.build`"
+                              % (list(sizes), mine))
     return _lib
 
 

@@ -167,8 +167,38 @@ def coll_torch_lookup_unique(local_id, keys):
     skewed distribution repeats its hottest ids thousands of times): consumers that pool or
     scatter by ``inverse`` anyway (embedding-bag forward, sparse-gradient backward) need every
     distinct row once.  ``rows_unique[inverse]`` is what ``coll_torch_lookup_key_t_val_ret``
-    returns for the same keys.  No counterpart in the reference."""
-    return lookup_unique(keys, lambda u: coll_torch_lookup_key_t_val_ret(local_id, u, pad_to_8=False))
+    returns for the same keys.  The distinct keys are found on the GPU by the library
+    (``ugc_lookup_unique``: stamps per id, no sort) in the same stream as the extraction; they
+    come out in order of discovery, not ascending.  No counterpart in the reference."""
+    dev = _state["dev"][local_id]
+    keys = keys.reshape(-1).contiguous()
+    n = keys.numel()
+    if n == 0:
+        return (torch.empty((0, _state["dim"]), dtype=_state["dtype"], device="cuda:%d" % dev),
+                torch.empty(0, dtype=torch.int64, device="cuda:%d" % dev))
+    if keys.dtype not in (torch.int64, torch.int32):
+        keys = keys.to(torch.int64)
+    kb = 8 if keys.dtype == torch.int64 else 4
+    rows = torch.empty((n, _state["dim"]), dtype=_state["dtype"], device="cuda:%d" % dev)
+    uniq = torch.empty_like(keys)
+    inverse = torch.empty(n, dtype=torch.int32, device="cuda:%d" % dev)
+    n_unique = torch.zeros(1, dtype=torch.int32, device="cuda:%d" % dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ctx = _L().coll_cache_context()
+    L = _lib.lib()
+
+    def call():
+        return L.ugc_lookup_unique(ctx, local_id, ctypes.c_void_p(keys.data_ptr()), kb, n,
+                                   ctypes.c_void_p(rows.data_ptr()), ctypes.c_void_p(uniq.data_ptr()),
+                                   ctypes.c_void_p(inverse.data_ptr()),
+                                   ctypes.c_void_p(n_unique.data_ptr()), ctypes.c_void_p(stream))
+
+    rc = call()
+    if rc == 1:  # batch larger than the scratch: grow and retry
+        _lib.check(L.ugc_reserve_batch(ctx, local_id, int(n * 1.05) + 8))
+        rc = call()
+    _lib.check(rc)
+    return rows[:int(n_unique.item())], inverse.to(torch.int64)
 
 
 class _RefreshJob:

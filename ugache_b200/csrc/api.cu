@@ -547,6 +547,17 @@ struct Replica {
   int gather_dynamic = 1;
   cudaStream_t copy_stream = nullptr;      // host-buffer lookups: rows leave on this stream
   std::vector<cudaEvent_t> copy_events;
+  uint32_t* stamp = nullptr;               // deduplicated lookups: one stamp per id (first use)
+  uint32_t stamp_epoch = 0;
+  uint64_t* host_sorted = nullptr;         // host list in address order (allocated on first use)
+  uint32_t* host_hist = nullptr;
+  int host_order_min_rows = 16384;
+  uint64_t lookups_host_ordered = 0;
+  uint32_t direct_slot = 0, last_slot = 0; // count slot of the next / the last direct launch
+  bool last_was_direct = false;
+  uint32_t last_n = 0, last_seq = 0;
+  cudaStream_t recent_streams[4] = {nullptr, nullptr, nullptr, nullptr};  // streams lookups ran on
+  bool recent_valid[4] = {false, false, false, false};
   int direct_tile_shift = 0;               // 0: chosen per launch
   int direct_deep = 0;
   uint64_t n_local = 0;                    // rows stored here
@@ -705,12 +716,6 @@ int check_table_errors(Replica* r, cudaStream_t s, const char* what) {
   return UGC_OK;
 }
 
-int upload_u32(ugc_ctx* c, DevBuf& buf, const uint32_t* src, size_t n, cudaStream_t s) {
-  UGC_TRY(ensure(c, buf, n * sizeof(uint32_t)));
-  if (n) UGC_CUDA(cudaMemcpyAsync(buf.ptr, src, n * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
-  return UGC_OK;
-}
-
 // `entries`: rows the placement maps to GPUs now (drives the reference's flat-vs-probing
 // rule); `reserve`: entries the table must be able to hold over its lifetime.
 int alloc_table(ugc_ctx* c, Replica* r, uint64_t entries, uint64_t reserve, cudaStream_t s) {
@@ -819,6 +824,9 @@ void release_replica(ugc_ctx* c, Replica* r) {
   for (auto& l : r->list) ctx_free(c, l);
   ctx_free(c, r->counters);
   ctx_free(c, r->free_ring);
+  ctx_free(c, r->host_sorted);
+  ctx_free(c, r->host_hist);
+  ctx_free(c, r->stamp);
   ctx_free(c, r->hot_counts);
   ctx_free(c, r->n2b_dev);
   ctx_free(c, r->n2b_next);
@@ -846,6 +854,7 @@ GatherParams gather_params(ugc_ctx* c, Replica* r, void* out, uint32_t n) {
   p.host_cta_cap = r->host_ctas;
   p.rows_per_cta_min = 32;
   for (int g = 0; g < kNumGroup; g++) p.t_byte[g] = r->t_byte[g];
+  p.seq = (uint32_t)r->lookups;
   p.dynamic = r->gather_dynamic;
   p.bulk_mask = r->bulk_mask;
   p.pdl = (r->pdl & 2) ? 1 : 0;
@@ -863,33 +872,47 @@ void* mapped_device_pointer(const void* host) {
   return attr.devicePointer;
 }
 
-// Waits until every lookup of this replica enqueued so far has finished on the GPU.  The
-// kernels publish the number of finished lookups in the pinned mirror, so this polls host
-// memory and stalls no stream (the reference waits for the trainer's step counter in the same
-// spirit, coll_cache_lib/cache_context.cu:4045-4052).  Bounded: after `limit_s` seconds, or
-// when lookups were issued that do not report there, it falls back to a device-wide wait.
-int drain_lookups(Replica* r, double limit_s = 20.0) {
-  const uint32_t target = (uint32_t)__atomic_load_n(&r->lookups, __ATOMIC_SEQ_CST);
-  if (r->feedback && !r->static_used) {
-    const volatile Feedback* f = r->feedback;
-    timespec t0;
-    clock_gettime(CLOCK_MONOTONIC, &t0);
-    for (uint64_t spin = 0;; spin++) {
-      if ((int32_t)(f->seq - target) >= 0) return UGC_OK;
-      if ((spin & 63) == 63) {
-        timespec t1;
-        clock_gettime(CLOCK_MONOTONIC, &t1);
-        if ((t1.tv_sec - t0.tv_sec) + (t1.tv_nsec - t0.tv_nsec) * 1e-9 > limit_s) break;
-        usleep(20);
-      }
-    }
+// The last few streams lookups of this replica were enqueued on (most callers use one).
+void remember_stream(Replica* r, cudaStream_t s) {
+  for (int i = 0; i < 4; i++)
+    if (r->recent_valid[i] && r->recent_streams[i] == s) return;
+  for (int i = 3; i > 0; i--) {
+    r->recent_streams[i] = r->recent_streams[i - 1];
+    r->recent_valid[i] = r->recent_valid[i - 1];
   }
-  UGC_CUDA(cudaDeviceSynchronize());
+  r->recent_streams[0] = s;
+  r->recent_valid[0] = true;
+}
+
+// Waits until every lookup of this replica enqueued so far has finished on the GPU: the
+// streams those lookups ran on are synchronised, which blocks this host thread only and
+// stalls no other stream (the reference waits for the trainer's step counter in the same
+// spirit, coll_cache_lib/cache_context.cu:4045-4052).  Falls back to a device-wide wait when
+// a stream cannot be waited on (destroyed meanwhile) or lookups went through the fixed scratch
+// array, whose streams are not recorded.
+int drain_lookups(Replica* r) {
+  bool ok = !r->static_used;
+  for (int i = 0; ok && i < 4; i++)
+    if (r->recent_valid[i] && cudaStreamSynchronize(r->recent_streams[i]) != cudaSuccess) {
+      cudaGetLastError();
+      r->recent_valid[i] = false;
+      ok = false;
+    }
+  if (!ok) UGC_CUDA(cudaDeviceSynchronize());
   return UGC_OK;
 }
 
 uint32_t host_mask_value(int empty_feat) {
   return empty_feat > 0 && empty_feat < 32 ? ((1u << empty_feat) - 1u) : 0xffffffffu;
+}
+
+// Grouped mode: order the host list by address when the last finished lookup took at least
+// host_order_min_rows rows from the host (0 = never).  Read from the pinned mirror like the
+// mode choice.
+bool want_host_order(const Replica* r) {
+  if (r->host_order_min_rows <= 0 || !r->feedback) return false;
+  const volatile Feedback* f = r->feedback;
+  return f->seq != 0 && f->count[kGroupHost] >= (uint32_t)r->host_order_min_rows;
 }
 
 // Direct (one fused kernel) or grouped (index lists + per-source CTA groups) for the lookup
@@ -904,8 +927,11 @@ bool choose_direct(const Replica* r) {
   return (double)host <= r->direct_host_share * (double)keys;
 }
 
+// `n_dev` != nullptr: the key count is read on the device from there (at most n); such a lookup
+// always takes the direct extraction and is launched without programmatic overlap, because its
+// keys were produced by the kernels just ahead of it in the stream.
 int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n, void* out,
-              cudaStream_t s) {
+              cudaStream_t s, const uint32_t* n_dev = nullptr) {
   if (n == 0) return UGC_OK;
   if (!keys || !out) return fail(UGC_ERR_INVALID, "keys and out must be non-null");
   if (n > r->max_batch)
@@ -916,9 +942,10 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used], s));
   // counted before the launch: drain_lookups() must never miss a lookup that could be running
   __atomic_fetch_add(&r->lookups, 1, __ATOMIC_SEQ_CST);
-  if (choose_direct(r)) {
+  if (n_dev != nullptr || choose_direct(r)) {
     if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 1], s));
     DirectParams d{};
+    d.n_dev = n_dev;
     for (int i = 0; i < kMaxLocation; i++) d.src_base[i] = r->src_base[i];
     d.out = out;
     d.table = r->table;
@@ -930,14 +957,26 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
     d.host_loc = (uint32_t)c->cfg.num_device;
     d.host_mask = host_mask_value(c->cfg.empty_feat);
     d.tile_shift = (uint32_t)r->direct_tile_shift;
+    // count slots alternate from one direct launch to the next; a launch also hands on the
+    // counts of the direct launch before it
+    d.slot = r->direct_slot;
+    d.publish_prev = r->last_was_direct ? 1u : 0u;
+    d.prev_keys = r->last_n;
+    d.prev_seq = r->last_seq;
+    r->direct_slot ^= 1u;
+    r->last_slot = d.slot;
     UGC_CUDA(launch_extract_direct(keys, key_bytes, d, r->direct_grid, r->vec_bytes, r->direct_deep != 0,
-                                   (r->pdl & 1) != 0, s));
+                                   (r->pdl & 1) != 0 && n_dev == nullptr, s));
     if (prof) {
       UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 2], s));
       r->prof_used += 3;
     }
     r->lookups_direct++;
     r->kernel_launches += 1;
+    r->last_was_direct = true;
+    r->last_n = (uint32_t)n;
+    r->last_seq = (uint32_t)r->lookups;
+    remember_stream(r, s);
     return UGC_OK;
   }
   UGC_CUDA(launch_lookup_group(keys, key_bytes, (uint32_t)n, r->table, (uint32_t)r->id,
@@ -945,12 +984,31 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
                                r->list[kGroupRemote], r->list[kGroupHost], r->counters, r->lookup_kpt, (r->pdl & 1) != 0, s));
   if (prof) UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 1], s));
   GatherParams p = gather_params(c, r, out, (uint32_t)n);
+  if (want_host_order(r)) {
+    // many host rows last time: order this lookup's host list by address before the gather
+    if (!r->host_sorted) {
+      r->host_sorted = static_cast<uint64_t*>(ctx_alloc(c, (size_t)r->max_batch * sizeof(uint64_t)));
+      r->host_hist = static_cast<uint32_t*>(ctx_alloc(c, host_order_scratch_bytes()));
+    }
+    if (r->host_sorted && r->host_hist) {
+      const uint64_t host_rows = c->cfg.empty_feat > 0 ? ((uint64_t)1 << c->cfg.empty_feat) : c->cfg.num_total_item;
+      UGC_CUDA(launch_host_order(r->list[kGroupHost], r->host_sorted, r->counters, r->host_hist, host_rows,
+                                 r->sm_count, s));
+      p.list[kGroupHost] = r->host_sorted;
+      r->kernel_launches += 2;
+      r->lookups_host_ordered++;
+    }
+  }
   UGC_CUDA(launch_gather_roles(p, r->gather_grid, r->block_threads, r->vec_bytes, s));
   if (prof) {
     UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 2], s));
     r->prof_used += 3;
   }
   r->kernel_launches += 2;
+  r->last_was_direct = false;
+  r->last_n = (uint32_t)n;
+  r->last_seq = (uint32_t)r->lookups;
+  remember_stream(r, s);
   return UGC_OK;
 }
 
@@ -1002,7 +1060,17 @@ int static_scratch_address(int device, void** out) {
 // --------------------------------------------------------------------------------------
 extern "C" {
 
-const char* ugc_version(void) { return "ugache_b200 0.1 (sm_100a)"; }
+const char* ugc_version(void) { return "ugache_b200 0.2 (sm_100a)"; }
+
+int ugc_abi_sizes(uint32_t sizes[5]) {
+  if (!sizes) return fail(UGC_ERR_INVALID, "null output");
+  sizes[0] = sizeof(ugc_config);
+  sizes[1] = sizeof(ugc_peer_handle);
+  sizes[2] = sizeof(ugc_stats_t);
+  sizes[3] = sizeof(ugc_tuning);
+  sizes[4] = sizeof(ugc_link_desc_t);
+  return UGC_OK;
+}
 const char* ugc_last_error(void) { return g_last_error.c_str(); }
 
 const char* ugc_status_string(int s) {
@@ -1581,6 +1649,39 @@ int ugc_lookup_i64_static(ugc_ctx* c, int replica_id, const int64_t* keys, size_
   return UGC_OK;
 }
 
+int ugc_lookup_unique(ugc_ctx* c, int replica_id, const void* keys, int key_bytes, size_t n, void* out_rows,
+                      void* unique_keys, int32_t* inverse, uint32_t* n_unique, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (key_bytes != 4 && key_bytes != 8) return fail(UGC_ERR_INVALID, "key_bytes must be 4 or 8");
+  if (!n_unique) return fail(UGC_ERR_INVALID, "n_unique must be non-null");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  UGC_CUDA(cudaSetDevice(r->device));
+  if (n == 0) {
+    UGC_CUDA(cudaMemsetAsync(n_unique, 0, sizeof(uint32_t), s));
+    return UGC_OK;
+  }
+  if (!keys || !out_rows || !unique_keys || !inverse) return fail(UGC_ERR_INVALID, "null argument");
+  if (n > r->max_batch) return fail(UGC_ERR_INVALID, "batch of %zu keys exceeds max_batch %u", n, r->max_batch);
+  if (n >= 0x00ffffffu) return fail(UGC_ERR_UNSUPPORTED, "at most 2^24-2 keys per deduplicated lookup");
+  if (c->cfg.num_device > 1 && !r->attached)
+    return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
+  const size_t stamp_bytes = (size_t)c->cfg.num_total_item * sizeof(uint32_t);
+  if (!r->stamp) {
+    r->stamp = static_cast<uint32_t*>(ctx_alloc(c, stamp_bytes));
+    if (!r->stamp) return fail(UGC_ERR_NOMEM, "stamp array (%zu bytes) could not be allocated", stamp_bytes);
+    r->stamp_epoch = 255;  // forces the clearing below
+  }
+  if (++r->stamp_epoch > 255) {  // all stamps back to epoch 0 before an epoch value is reused
+    UGC_CUDA(cudaMemsetAsync(r->stamp, 0, stamp_bytes, s));
+    r->stamp_epoch = 1;
+  }
+  UGC_CUDA(launch_unique(keys, key_bytes, (uint32_t)n, c->cfg.num_total_item, r->stamp_epoch, r->stamp,
+                         unique_keys, inverse, n_unique, r->counters, s));
+  r->kernel_launches += 2;
+  return do_lookup(c, r, unique_keys, key_bytes, n, out_rows, s, n_unique);
+}
+
 int ugc_reserve_batch(ugc_ctx* c, int replica_id, uint32_t max_batch) {
   Replica* r;
   UGC_TRY(get_replica(c, replica_id, true, &r));
@@ -1600,6 +1701,8 @@ int ugc_reserve_batch(ugc_ctx* c, int replica_id, uint32_t max_batch) {
     ctx_free(c, r->list[g]);
     r->list[g] = fresh[g];
   }
+  ctx_free(c, r->host_sorted);  // sized by max_batch: re-made on the next ordered lookup
+  r->host_sorted = nullptr;
   r->max_batch = max_batch;
   return UGC_OK;
 }
@@ -1848,7 +1951,6 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   Counters h;
   UGC_TRY(read_counters(r, &h));
   memset(out, 0, sizeof(*out));
-  const int G = c->cfg.num_device;
   out->num_local_rows = r->n_local;
   out->num_remote_keys = r->n_remote;
   out->num_host_keys = c->cfg.num_total_item - out->num_local_rows - out->num_remote_keys;
@@ -1857,10 +1959,17 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   out->table_kind = r->table.kind;
   out->table_bytes = r->table_bytes;
   out->slice_bytes = r->slice_bytes;
-  out->last_keys = h.last_keys;
-  out->last_local = h.last_count[kGroupLocal];
-  out->last_remote = h.last_count[kGroupRemote];
-  out->last_host = h.last_count[kGroupHost];
+  if (r->last_was_direct) {  // counts of a direct launch sit in the slot it owned
+    out->last_keys = r->last_n;
+    out->last_local = h.dcount[r->last_slot][kGroupLocal];
+    out->last_remote = h.dcount[r->last_slot][kGroupRemote];
+    out->last_host = h.dcount[r->last_slot][kGroupHost];
+  } else {
+    out->last_keys = h.last_keys;
+    out->last_local = h.last_count[kGroupLocal];
+    out->last_remote = h.last_count[kGroupRemote];
+    out->last_host = h.last_count[kGroupHost];
+  }
   out->err_key_range = h.err_key_range;
   out->err_table = h.err_table;
   out->lookups = r->lookups;
@@ -1871,6 +1980,7 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   out->last_remote_ns = span(kGroupRemote);
   out->last_host_ns = span(kGroupHost);
   out->last_index_ns = (h.t_index && h.t_start > h.t_index) ? (uint64_t)(h.t_start - h.t_index) : 0;
+  out->lookups_host_ordered = r->lookups_host_ordered;
   out->lookups_direct = r->lookups_direct;
   out->kernel_launches = r->kernel_launches;
   return UGC_OK;
@@ -1897,6 +2007,7 @@ int ugc_get_tuning(ugc_ctx* c, int replica_id, ugc_tuning* out) {
   out->gather_dynamic = r->gather_dynamic;
   out->direct_tile_keys = r->direct_tile_shift ? (1 << r->direct_tile_shift) : 0;
   out->direct_deep = r->direct_deep;
+  out->host_order_min_rows = r->host_order_min_rows;
   return UGC_OK;
 }
 
@@ -1927,6 +2038,7 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   r->gather_dynamic = t->gather_dynamic ? 1 : 0;
   r->direct_tile_shift = t->direct_tile_keys == 8 ? 3 : t->direct_tile_keys == 16 ? 4 : t->direct_tile_keys == 32 ? 5 : 0;
   r->direct_deep = t->direct_deep ? 1 : 0;
+  r->host_order_min_rows = t->host_order_min_rows < 0 ? 0 : t->host_order_min_rows;
   return UGC_OK;
 }
 

@@ -65,13 +65,16 @@ struct Counters {
   // device clock (ns) of the last gather: earliest CTA start and, per group, latest CTA end
   unsigned long long t_start;
   unsigned long long t_end[kNumGroup];
-  uint32_t seq;                  // extractions finished on these counters
-  uint32_t reserved;
+  uint32_t reserved0[2];
   // grouped gather: rows of each list handed out so far beyond every CTA's first chunk
   // (zeroed by the last CTA of the gather)
   uint32_t cursor[kNumGroup];
   uint32_t reserved2;
   unsigned long long t_index;    // device clock (ns) when the lookup kernel started; 0 = direct
+  // direct extraction: per-source counts of the launches that own slot 0 / slot 1 in turn; a
+  // launch adds to its slot and clears the other one (whose launch is complete by then)
+  uint32_t dcount[2][kNumGroup];
+  uint32_t reserved3[2];
 };
 
 // Written by the last CTA of every extraction into pinned host memory: the host reads it
@@ -79,7 +82,7 @@ struct Counters {
 struct Feedback {
   uint32_t keys;
   uint32_t count[kNumGroup];
-  uint32_t seq;  // lookups finished so far (written last)
+  uint32_t seq;  // ordinal of the lookup these counts belong to (written last; 0 = none yet)
 };
 
 // Everything the role-partitioned gather needs.
@@ -98,6 +101,7 @@ struct GatherParams {
   // row read and row write both use HBM).  The CTAs of a launch are shared out in proportion
   // to rows * row_bytes * t_byte of the groups, within the caps above.
   float t_byte[kNumGroup];
+  uint32_t seq;         // ordinal of this lookup among the replica's lookups (for the mirror)
   int dynamic;          // 1: lists are handed out in chunks; a CTA whose own list is drained
                         //    takes chunks of the other groups' lists.  0: fixed striding.
   int pdl;              // launched with programmatic stream serialization
@@ -111,6 +115,7 @@ struct DirectParams {
   TableView table;
   Counters* counters;
   Feedback* feedback;   // pinned host mirror of the last lookup's counts, or nullptr
+  const uint32_t* n_dev;  // if set: the number of keys, in device memory (never above n_keys)
   uint32_t n_keys;
   uint32_t row_bytes;
   uint32_t local_loc;
@@ -118,6 +123,10 @@ struct DirectParams {
   uint32_t host_mask;
   uint32_t lpr_shift;   // log2 of the lanes that share one row
   uint32_t tile_shift;  // log2 of the keys one warp probes at a time (3..5)
+  uint32_t slot;        // which of Counters::dcount this launch adds to (launches alternate)
+  uint32_t publish_prev;  // 1: the launch before this one was a direct one; hand its counts on
+  uint32_t prev_keys;     // its batch size
+  uint32_t prev_seq;      // its ordinal among the replica's lookups
 };
 
 // Slot (row offset) numbers for entries j = 0..n-1 of a build / refresh step:

@@ -29,6 +29,21 @@ cudaError_t launch_lookup_group(const void* keys, int key_bytes, uint32_t n, con
 cudaError_t launch_gather_roles(const GatherParams& p, int grid, int block, int vec_bytes,
                                 cudaStream_t stream);
 
+// Distinct keys of a batch: unique_keys[0 .. *n_unique) (order of discovery), inverse[i] = index
+// of keys[i] among them (-1 for an id outside [0, num_keys)).  `stamp` is one uint32 per id of
+// the key space, zeroed once; `epoch` (1..255) must differ from the one of the previous call on
+// the same stamp array and the array be zeroed again before an epoch value comes round.
+cudaError_t launch_unique(const void* keys, int key_bytes, uint32_t n, uint64_t num_keys, uint32_t epoch,
+                          uint32_t* stamp, void* unique_keys, int32_t* inverse, uint32_t* n_unique,
+                          Counters* counters, cudaStream_t stream);
+
+// Orders the host list of the lookup just enqueued by address range (counting sort into 256
+// buckets over `host_rows` rows) into `sorted`; `hist` is host_order_scratch_bytes() of scratch.
+// Enqueue between launch_lookup_group and launch_gather_roles and hand `sorted` to the gather.
+size_t host_order_scratch_bytes();
+cudaError_t launch_host_order(const uint64_t* list_host, uint64_t* sorted, const Counters* counters,
+                              uint32_t* hist, uint64_t host_rows, int sm_count, cudaStream_t stream);
+
 // Lookup and row copy in one kernel (no index lists): out[i] = row of keys[i].  `grid` is
 // the most CTAs to use (a multiple of the SM count); fewer are launched for small batches.
 // `deep`: twice the rows in flight per warp at 3 instead of 4 CTAs per SM.  p.tile_shift 3..5

@@ -202,6 +202,27 @@ class Cache:
         self.lookup_ptr(replica_id, keys.data_ptr(), kb, n, out.data_ptr(), s)
         return out
 
+    def lookup_unique(self, replica_id, keys, stream=None):
+        """Deduplicated lookup on the GPU.  keys: CUDA tensor (int64 / int32).  Returns
+        ``(rows, unique_keys, inverse, n_unique)``: uint8 ``rows[n, row_bytes]`` of which the
+        first ``n_unique`` are filled, ``unique_keys[n]`` likewise, int32 ``inverse[n]`` and a
+        one-element int32 tensor ``n_unique`` -- all on the device, nothing synchronises."""
+        import torch
+        keys = keys.reshape(-1)
+        n = keys.numel()
+        kb = 8 if keys.dtype == torch.int64 else 4
+        dev = keys.device
+        rows = torch.empty((n, self.cfg.row_bytes), dtype=torch.uint8, device=dev)
+        uniq = torch.empty_like(keys)
+        inverse = torch.empty(n, dtype=torch.int32, device=dev)
+        n_unique = torch.zeros(1, dtype=torch.int32, device=dev)
+        s = torch.cuda.current_stream(dev).cuda_stream if stream is None else stream
+        check(_lib.lib().ugc_lookup_unique(self._h, replica_id, C.c_void_p(keys.data_ptr()), kb, n,
+                                           C.c_void_p(rows.data_ptr()), C.c_void_p(uniq.data_ptr()),
+                                           C.c_void_p(inverse.data_ptr()), C.c_void_p(n_unique.data_ptr()),
+                                           C.c_void_p(s)))
+        return rows, uniq, inverse, n_unique
+
     def reserve_batch(self, replica_id, max_batch):
         check(_lib.lib().ugc_reserve_batch(self._h, replica_id, max_batch))
 
