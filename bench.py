@@ -96,6 +96,9 @@ def parse_args():
     ap.add_argument("--suite", default="",
                     help="';'-separated workloads run one after the other over one host-table "
                          "allocation: c2, sweep, gnn, c4 (e.g. 'c2;sweep;gnn;c4'); one JSON line each")
+    ap.add_argument("--c4-rows", type=int, default=400_000_000,
+                    help="rows of the suite's 'c4' workload (the configuration's 400 M; smaller "
+                         "for a quick check of the suite itself)")
     ap.add_argument("--in-process", type=int, default=0,
                     help="G > 1: all G replicas in THIS process on devices 0..G-1 (peers wired by "
                          "ugc_connect_local), lookups enqueued device after device from one "
@@ -618,8 +621,8 @@ def run_suite(a):
             b.steps, b.warmup, b.no_e2e, b.no_cpu_baseline = min(a.steps, 20), min(a.warmup, 3), True, True
             run_ours(b, job)
         elif name == "c4":
-            b.rows, b.dim, b.dtype, b.cache_pct, b.alpha = 400_000_000, 64, "float16", 0.2, 1.05
-            b.batch = 65536 * 26
+            b.rows, b.dim, b.dtype, b.cache_pct, b.alpha = a.c4_rows, 64, "float16", 0.2, 1.05
+            b.batch = min(65536 * 26, max(1024, a.c4_rows // 200))
             b.steps, b.warmup, b.no_cpu_baseline = min(a.steps, 30), min(a.warmup, 3), True
             b.refresh = a.refresh or 0.02
             run_ours(b, job)

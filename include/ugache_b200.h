@@ -67,7 +67,7 @@ typedef enum { UGC_TABLE_AUTO = 0, UGC_TABLE_FLAT = 1, UGC_TABLE_HASHED = 2 } ug
  *   DIRECT   one kernel probes the table and copies each row from wherever it is, with no
  *            index lists: best when nearly all rows come from GPU memory;
  *   AUTO     DIRECT while the last finished lookup of the replica took no more than
- *            ugc_tuning.direct_host_permille of its rows from the host table, else GROUPED
+ *            ugc_tuning.direct_max_host_rows rows from the host table, else GROUPED
  *            (the library reads those counts from a pinned mirror the kernels write; no
  *            synchronisation). */
 typedef enum { UGC_EXTRACT_AUTO = 0, UGC_EXTRACT_GROUPED = 1, UGC_EXTRACT_DIRECT = 2 } ugc_extract_mode;
@@ -154,6 +154,10 @@ typedef struct {
   uint64_t last_index_ns;      /* grouped extraction: device-clock time from the start of
                                   the lookup kernel to the start of the gather kernel (the
                                   index-building phase); 0 for a direct extraction        */
+  /* device memory this context (all its replicas in this process) holds now: obtained through
+     the caller's allocator callbacks / by the library itself (cudaMalloc, or virtual-memory
+     blocks that other processes can map), i.e. outside the caller's pool */
+  uint64_t device_bytes_from_allocator, device_bytes_own;
   uint64_t lookups_host_ordered; /* grouped lookups whose host list was put in address order */
   uint64_t lookups_direct;     /* lookups that took the direct (one-kernel) extraction  */
   uint64_t kernel_launches;    /* kernels launched by lookups: 2 per grouped, 1 per direct */
@@ -323,7 +327,7 @@ int ugc_reserve_batch(ugc_ctx* ctx, int replica_id, uint32_t max_batch);
  * cudaHostRegister with the mapped flag, or ugc_host_alloc) can be used in place, as
  * ugc_tuning.host_zero_copy says: by default the kernel reads the keys across PCIe itself,
  * while the rows are staged in device memory and leave through the copy engine (measured
- * faster than stores from the SMs: 56 against 51 GB/s), in eight pieces for batches of 65,536
+ * faster than stores from the SMs: 56 against 51 GB/s), in four pieces for batches of 65,536
  * keys or more so that one piece crosses PCIe while the next is being extracted.  After such
  * a call ugc_stats' last_* fields describe the last piece only.  Pageable buffers always go
  * through staging copies. */
@@ -392,9 +396,10 @@ typedef struct {
                                      the previous gather), bit 1 for the gather kernel (it is
                                      scheduled while the lookup kernel drains)              */
   int32_t extract_mode;           /* ugc_extract_mode                                       */
-  int32_t direct_ctas_per_sm;     /* CTAs of the direct extraction kernel per SM, 1..8      */
-  int32_t direct_host_permille;   /* auto mode: direct while the last finished lookup took at
-                                     most this many of 1000 rows from the host table        */
+  int32_t direct_ctas_per_sm;     /* CTAs of the direct extraction kernel per SM, 1..16     */
+  int32_t direct_max_host_rows;   /* auto mode: direct while the last finished lookup took at
+                                     most this many rows from the host table                */
+  int32_t direct_block_threads;   /* threads per CTA of the direct kernel: 128 or 256       */
   int32_t direct_tile_keys;       /* keys one warp of the direct kernel probes at a time: 8,
                                      16 or 32; 0 = the largest that balances the warps      */
   int32_t direct_deep;            /* direct kernel: 1 = twice the rows in flight per warp at

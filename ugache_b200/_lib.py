@@ -78,6 +78,8 @@ class Stats(C.Structure):
         ("last_remote_ns", C.c_uint64),
         ("last_host_ns", C.c_uint64),
         ("last_index_ns", C.c_uint64),
+        ("device_bytes_from_allocator", C.c_uint64),
+        ("device_bytes_own", C.c_uint64),
         ("lookups_host_ordered", C.c_uint64),
         ("lookups_direct", C.c_uint64),
         ("kernel_launches", C.c_uint64),
@@ -97,7 +99,8 @@ class Tuning(C.Structure):
         ("programmatic_launch", C.c_int32),
         ("extract_mode", C.c_int32),
         ("direct_ctas_per_sm", C.c_int32),
-        ("direct_host_permille", C.c_int32),
+        ("direct_max_host_rows", C.c_int32),
+        ("direct_block_threads", C.c_int32),
         ("direct_tile_keys", C.c_int32),
         ("direct_deep", C.c_int32),
         ("host_order_min_rows", C.c_int32),

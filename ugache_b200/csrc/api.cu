@@ -551,13 +551,15 @@ struct Replica {
   uint32_t stamp_epoch = 0;
   uint64_t* host_sorted = nullptr;         // host list in address order (allocated on first use)
   uint32_t* host_hist = nullptr;
-  int host_order_min_rows = 16384;
+  int host_order_min_rows = 8192;
   uint64_t lookups_host_ordered = 0;
   uint32_t direct_slot = 0, last_slot = 0; // count slot of the next / the last direct launch
   bool last_was_direct = false;
   uint32_t last_n = 0, last_seq = 0;
   cudaStream_t recent_streams[4] = {nullptr, nullptr, nullptr, nullptr};  // streams lookups ran on
   bool recent_valid[4] = {false, false, false, false};
+  int direct_block = 256;
+  int direct_max_host_rows = 8192;
   int direct_tile_shift = 0;               // 0: chosen per launch
   int direct_deep = 0;
   uint64_t n_local = 0;                    // rows stored here
@@ -586,7 +588,6 @@ struct Replica {
   // the host-row share of the last finished lookup, read from the pinned mirror below
   int extract_mode = UGC_EXTRACT_AUTO;
   int direct_grid = 0;
-  double direct_host_share = 0.10;
   Feedback* feedback = nullptr;      // pinned host memory, written by the kernels
   Feedback* feedback_dev = nullptr;  // the same memory as the device addresses it
   uint64_t lookups_direct = 0;
@@ -609,25 +610,50 @@ struct ugc_ctx {
   bool host_registered_here = false;
   size_t host_registered_bytes = 0;
   std::mutex mu;
+  // device memory held now: through the caller's allocator / obtained by the library itself
+  // (cudaMalloc or virtual-memory blocks), for ugc_stats
+  std::mutex acct_mu;
+  std::map<void*, size_t> acct;
+  uint64_t bytes_from_allocator = 0, bytes_own = 0;
 };
 
 namespace {
 
+void account(ugc_ctx* c, void* p, size_t bytes, bool own) {
+  std::lock_guard<std::mutex> lock(c->acct_mu);
+  c->acct[p] = bytes;
+  (own ? c->bytes_own : c->bytes_from_allocator) += bytes;
+}
+void unaccount(ugc_ctx* c, void* p, bool own) {
+  std::lock_guard<std::mutex> lock(c->acct_mu);
+  auto it = c->acct.find(p);
+  if (it == c->acct.end()) return;
+  (own ? c->bytes_own : c->bytes_from_allocator) -= it->second;
+  c->acct.erase(it);
+}
+
 void* ctx_alloc(ugc_ctx* c, size_t bytes) {
   bytes = round_up(std::max<size_t>(bytes, 256), 256);
-  if (c->cfg.alloc) return c->cfg.alloc(bytes, c->cfg.alloc_user);
+  if (c->cfg.alloc) {
+    void* q = c->cfg.alloc(bytes, c->cfg.alloc_user);
+    if (q) account(c, q, bytes, false);
+    return q;
+  }
   void* p = nullptr;
   if (cudaMalloc(&p, bytes) != cudaSuccess) {
     cudaGetLastError();
     return nullptr;
   }
+  account(c, p, bytes, true);
   return p;
 }
 void ctx_free(ugc_ctx* c, void* p) {
   if (!p) return;
   if (c->cfg.free) {
+    unaccount(c, p, false);
     c->cfg.free(p, c->cfg.alloc_user);
   } else if (!c->cfg.alloc) {
+    unaccount(c, p, true);
     cudaFree(p);
   }
 }
@@ -637,12 +663,18 @@ void ctx_free(ugc_ctx* c, void* p) {
 void* ctx_alloc_shared(ugc_ctx* c, size_t bytes) {
   if (!c->cfg.alloc && !getenv("UGC_NO_VMM")) {
     void* p = dev_shareable_alloc(std::max<size_t>(bytes, 256));
-    if (p) return p;
+    if (p) {
+      DevBlock b;
+      account(c, p, dev_block_find(p, &b) ? b.size : bytes, true);
+      return p;
+    }
   }
   return ctx_alloc(c, bytes);
 }
 void ctx_free_shared(ugc_ctx* c, void* p) {
   if (!p) return;
+  DevBlock b;
+  if (dev_block_find(p, &b)) unaccount(c, p, true);
   if (dev_block_free(p)) return;
   ctx_free(c, p);
 }
@@ -922,9 +954,8 @@ bool choose_direct(const Replica* r) {
   if (r->extract_mode == UGC_EXTRACT_DIRECT) return true;
   if (r->extract_mode == UGC_EXTRACT_GROUPED || !r->feedback) return false;
   const volatile Feedback* f = r->feedback;
-  const uint32_t keys = f->keys, host = f->count[kGroupHost];
-  if (f->seq == 0 || keys == 0) return false;
-  return (double)host <= r->direct_host_share * (double)keys;
+  if (f->seq == 0) return false;
+  return f->count[kGroupHost] <= (uint32_t)r->direct_max_host_rows;
 }
 
 // `n_dev` != nullptr: the key count is read on the device from there (at most n); such a lookup
@@ -965,7 +996,7 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
     d.prev_seq = r->last_seq;
     r->direct_slot ^= 1u;
     r->last_slot = d.slot;
-    UGC_CUDA(launch_extract_direct(keys, key_bytes, d, r->direct_grid, r->vec_bytes, r->direct_deep != 0,
+    UGC_CUDA(launch_extract_direct(keys, key_bytes, d, r->direct_grid, r->direct_block, r->vec_bytes, r->direct_deep != 0,
                                    (r->pdl & 1) != 0 && n_dev == nullptr, s));
     if (prof) {
       UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 2], s));
@@ -1164,13 +1195,14 @@ int ugc_placement_cost(int num_device, uint64_t N, const uint32_t* rank_ids, con
   Placement p;
   p.num_device = num_device;
   p.num_block = num_block;
-  p.nid_to_block.assign(nid_to_block, nid_to_block + N);
   p.block_access_from.assign(block_access_from, block_access_from + (size_t)num_device * num_block);
-  for (uint64_t k = 0; k < N; k++)
-    if (p.nid_to_block[k] >= (uint32_t)num_block) return fail(UGC_ERR_INVALID, "block id out of range");
+  int bad = 0;  // the per-key array is read in place (4 bytes per id: no copy per call)
+#pragma omp parallel for schedule(static) reduction(| : bad)
+  for (int64_t k = 0; k < (int64_t)N; k++) bad |= (nid_to_block[k] >= (uint32_t)num_block);
+  if (bad) return fail(UGC_ERR_INVALID, "block id out of range");
   for (uint8_t a : p.block_access_from)
     if (a > num_device) return fail(UGC_ERR_INVALID, "source location out of range");
-  std::string err = placement_cost(p, N, rank_ids, rank_freqs, t_local, t_remote, t_cpu, cost);
+  std::string err = placement_cost(p, N, rank_ids, rank_freqs, t_local, t_remote, t_cpu, cost, nid_to_block);
   if (!err.empty()) return fail(UGC_ERR_INVALID, "%s", err.c_str());
   return UGC_OK;
 }
@@ -1735,11 +1767,14 @@ int ugc_lookup_host(ugc_ctx* c, int replica_id, const void* keys, int key_bytes,
   // PCIe on a second stream, piece i+1 is being extracted.
   const size_t rb = c->cfg.row_bytes;
   UGC_TRY(ensure(c, r->stage_out, n * rb));
-  size_t pieces = n >= (1u << 16) ? 8 : 1;
-  const size_t piece = (n / pieces + 31) / 32 * 32;  // multiples of 32 keys keep every piece aligned
+  // four pieces, the first half the size of the others: the copy engine starts early and then
+  // runs few, large copies (each copy costs about 10 us of its own)
+  const size_t pieces = n >= (1u << 16) ? 4 : 1;
+  const size_t first = pieces > 1 ? (n / 7 + 31) / 32 * 32 : n;          // multiples of 32 keys keep
+  const size_t piece = pieces > 1 ? ((n - first) / 3 + 31) / 32 * 32 : n;  // every piece aligned
   if (pieces > 1) {
     if (!r->copy_stream) UGC_CUDA(cudaStreamCreateWithFlags(&r->copy_stream, cudaStreamNonBlocking));
-    while (r->copy_events.size() < pieces) {
+    while (r->copy_events.size() < pieces + 1) {
       cudaEvent_t e;
       UGC_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
       r->copy_events.push_back(e);
@@ -1748,8 +1783,8 @@ int ugc_lookup_host(ugc_ctx* c, int replica_id, const void* keys, int key_bytes,
   const char* kp = static_cast<const char*>(keys_dev);
   char* stage = static_cast<char*>(r->stage_out.ptr);
   size_t idx = 0;
-  for (size_t off = 0; off < n; off += piece, idx++) {
-    const size_t m = std::min(piece, n - off);
+  for (size_t off = 0; off < n; idx++) {
+    const size_t m = std::min(idx == 0 ? first : piece, n - off);
     UGC_TRY(do_lookup(c, r, kp + off * (size_t)key_bytes, key_bytes, m, stage + off * rb, s));
     if (pieces > 1) {
       UGC_CUDA(cudaEventRecord(r->copy_events[idx], s));
@@ -1759,6 +1794,7 @@ int ugc_lookup_host(ugc_ctx* c, int replica_id, const void* keys, int key_bytes,
     } else {
       UGC_CUDA(cudaMemcpyAsync(out, stage, m * rb, cudaMemcpyDeviceToHost, s));
     }
+    off += m;
   }
   if (pieces > 1) UGC_CUDA(cudaStreamSynchronize(r->copy_stream));
   UGC_CUDA(cudaStreamSynchronize(s));
@@ -1980,6 +2016,11 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   out->last_remote_ns = span(kGroupRemote);
   out->last_host_ns = span(kGroupHost);
   out->last_index_ns = (h.t_index && h.t_start > h.t_index) ? (uint64_t)(h.t_start - h.t_index) : 0;
+  {
+    std::lock_guard<std::mutex> lock(c->acct_mu);
+    out->device_bytes_from_allocator = c->bytes_from_allocator;
+    out->device_bytes_own = c->bytes_own;
+  }
   out->lookups_host_ordered = r->lookups_host_ordered;
   out->lookups_direct = r->lookups_direct;
   out->kernel_launches = r->kernel_launches;
@@ -2002,7 +2043,8 @@ int ugc_get_tuning(ugc_ctx* c, int replica_id, ugc_tuning* out) {
   out->programmatic_launch = r->pdl;
   out->extract_mode = r->extract_mode;
   out->direct_ctas_per_sm = r->direct_grid / std::max(r->sm_count, 1);
-  out->direct_host_permille = (int)(r->direct_host_share * 1000.0 + 0.5);
+  out->direct_max_host_rows = r->direct_max_host_rows;
+  out->direct_block_threads = r->direct_block;
   out->host_zero_copy = r->host_zero_copy;
   out->gather_dynamic = r->gather_dynamic;
   out->direct_tile_keys = r->direct_tile_shift ? (1 << r->direct_tile_shift) : 0;
@@ -2019,9 +2061,9 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   if (t->gather_ctas_per_sm < 1 || t->gather_ctas_per_sm > 32 || (bt != 256 && bt != 512 && bt != 1024) ||
       (vec != 16 && vec != 32) || t->host_ctas < 1 || t->remote_ctas < 1 || t->bulk_mask < 0 ||
       t->bulk_mask > 3 || (kpt != 1 && kpt != 2 && kpt != 4) || t->extract_mode < UGC_EXTRACT_AUTO ||
-      t->extract_mode > UGC_EXTRACT_DIRECT || t->direct_ctas_per_sm < 1 || t->direct_ctas_per_sm > 8 ||
-      t->direct_host_permille < 0 || t->direct_host_permille > 1000 || t->host_zero_copy < 0 ||
-      t->host_zero_copy > 3)
+      t->extract_mode > UGC_EXTRACT_DIRECT || t->direct_ctas_per_sm < 1 || t->direct_ctas_per_sm > 16 ||
+      t->direct_max_host_rows < 0 || (t->direct_block_threads != 128 && t->direct_block_threads != 256) ||
+      t->host_zero_copy < 0 || t->host_zero_copy > 3)
     return fail(UGC_ERR_INVALID, "ugc_tuning holds a value outside its range");
   r->gather_grid = r->sm_count * t->gather_ctas_per_sm;
   r->block_threads = bt;
@@ -2033,7 +2075,8 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   r->pdl = t->programmatic_launch & 3;
   r->extract_mode = t->extract_mode;
   r->direct_grid = r->sm_count * t->direct_ctas_per_sm;
-  r->direct_host_share = t->direct_host_permille / 1000.0;
+  r->direct_max_host_rows = t->direct_max_host_rows;
+  r->direct_block = t->direct_block_threads;
   r->host_zero_copy = t->host_zero_copy;
   r->gather_dynamic = t->gather_dynamic ? 1 : 0;
   r->direct_tile_shift = t->direct_tile_keys == 8 ? 3 : t->direct_tile_keys == 16 ? 4 : t->direct_tile_keys == 32 ? 5 : 0;

@@ -846,7 +846,7 @@ __global__ void __launch_bounds__(kBlock, DEEP ? 3 : 4)
     for (int i = 0; i < kMaxLocation; i++) s_src[i] = static_cast<const char*>(p.src_base[i]);
   }
   const uint32_t lane = threadIdx.x & 31;
-  const uint32_t n_warps = gridDim.x * kWarpsPerBlock;
+  const uint32_t n_warps = gridDim.x * (blockDim.x >> 5);
   const uint32_t tshift = p.tile_shift;
   const uint32_t tile_keys = 1u << tshift;
   // the number of keys may live in device memory (distinct keys of a batch, counted on the GPU)
@@ -1391,7 +1391,9 @@ int usable_vec_bytes(uint32_t row_bytes, int want, const void* out, const void* 
 }
 
 cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectParams& p_in, int grid,
-                                  int vec_bytes, bool deep, bool pdl, cudaStream_t stream) {
+                                  int block, int vec_bytes, bool deep, bool pdl, cudaStream_t stream) {
+  if (block != 128 && block != 256) block = kBlock;
+  const int warps_per_block = block / 32;
   if (p_in.n_keys == 0) return cudaSuccess;
   DirectParams p = p_in;
   const int vec = usable_vec_bytes(p.row_bytes, vec_bytes, p.out, p.src_base, kMaxLocation);
@@ -1403,7 +1405,7 @@ cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectP
   // p.tile_shift when that is set.
   const int unroll = (vec == 32 ? 2 : 4) * (deep ? 2 : 1);
   const int rows_per_pass = std::min(32, unroll * (32 / lpr));
-  const long long n_warps = (long long)grid * kWarpsPerBlock;
+  const long long n_warps = (long long)grid * warps_per_block;
   uint32_t shift = p_in.tile_shift;
   if (shift < 3 || shift > 5) {
     shift = 5;
@@ -1416,13 +1418,13 @@ cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectP
   }
   p.tile_shift = shift;
   const int tiles = (int)(((long long)p.n_keys + (1ll << shift) - 1) >> shift);
-  grid = std::max(1, std::min(grid, (tiles + kWarpsPerBlock - 1) / kWarpsPerBlock));
+  grid = std::max(1, std::min(grid, (tiles + warps_per_block - 1) / warps_per_block));
 #define UGC_LAUNCH_DIRECT(KEYT, VEC)                                                              \
   do {                                                                                            \
     if (deep)                                                                                     \
-      return launch_pdl(extract_direct_kernel<KEYT, VEC, true>, grid, kBlock, 0, stream, pdl,      \
+      return launch_pdl(extract_direct_kernel<KEYT, VEC, true>, grid, block, 0, stream, pdl,       \
                         static_cast<const KEYT*>(keys), p);                                       \
-    return launch_pdl(extract_direct_kernel<KEYT, VEC, false>, grid, kBlock, 0, stream, pdl,       \
+    return launch_pdl(extract_direct_kernel<KEYT, VEC, false>, grid, block, 0, stream, pdl,        \
                       static_cast<const KEYT*>(keys), p);                                         \
   } while (0)
   if (key_bytes == 8) {

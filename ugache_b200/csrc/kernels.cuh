@@ -49,7 +49,7 @@ cudaError_t launch_host_order(const uint64_t* list_host, uint64_t* sorted, const
 // `deep`: twice the rows in flight per warp at 3 instead of 4 CTAs per SM.  p.tile_shift 3..5
 // forces tiles of 8 / 16 / 32 keys; anything else lets the launcher choose.
 cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectParams& p, int grid,
-                                  int vec_bytes, bool deep, bool pdl, cudaStream_t stream);
+                                  int block, int vec_bytes, bool deep, bool pdl, cudaStream_t stream);
 
 // Widest of 32 / 16 / 4 bytes, not above `want`, that divides row_bytes and the address of
 // `out` and of every non-null source base: rows then start on a multiple of it on both sides.

@@ -296,10 +296,12 @@ std::string solve_placement(int policy, int G, uint64_t N, const uint32_t* ids, 
 }
 
 std::string placement_cost(const Placement& p, uint64_t N, const uint32_t* ids, const uint32_t* freq,
-                           double T_local, double T_remote, double T_cpu, double* cost_per_reader) {
+                           double T_local, double T_remote, double T_cpu, double* cost_per_reader,
+                           const uint32_t* n2b_in_place) {
   const int G = p.num_device, B = p.num_block;
   if (!ids || !freq || !cost_per_reader) return "rank_ids, rank_freqs and the output are required";
-  if (p.nid_to_block.size() < N) return "placement is smaller than the id space";
+  if (!n2b_in_place && p.nid_to_block.size() < N) return "placement is smaller than the id space";
+  const uint32_t* n2b = n2b_in_place ? n2b_in_place : p.nid_to_block.data();
   std::vector<double> mass((size_t)B, 0.0);
   {
     const int T = omp_get_max_threads();
@@ -308,7 +310,7 @@ std::string placement_cost(const Placement& p, uint64_t N, const uint32_t* ids, 
     {
       double* mine = &priv[(size_t)omp_get_thread_num() * B];
 #pragma omp for schedule(static)
-      for (int64_t r = 0; r < (int64_t)N; r++) mine[p.nid_to_block[ids[r]]] += (double)freq[r];
+      for (int64_t r = 0; r < (int64_t)N; r++) mine[n2b[ids[r]]] += (double)freq[r];
     }
     for (int t = 0; t < T; t++)
       for (int b = 0; b < B; b++) mass[(size_t)b] += priv[(size_t)t * B + b];

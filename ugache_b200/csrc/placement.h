@@ -2,15 +2,39 @@
 // placement heuristics, the B200 link model and the per-reader key classification.
 #pragma once
 #include <cstdint>
+#include <memory>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace ugc {
 
+// Allocator whose resize() leaves new elements uninitialised: the per-key array of a placement
+// is 4 bytes per id (1.6 GB at 4*10^8 ids) and is always overwritten in full right after it is
+// sized, by several threads; value-initialising it first would touch every page from one thread.
+template <class T>
+struct NoInitAlloc : std::allocator<T> {
+  template <class U>
+  struct rebind {
+    using other = NoInitAlloc<U>;
+  };
+  NoInitAlloc() = default;
+  template <class U>
+  NoInitAlloc(const NoInitAlloc<U>&) {}
+  template <class U, class... Args>
+  void construct(U* p, Args&&... args) {
+    if constexpr (sizeof...(Args) == 0) {
+      ::new (static_cast<void*>(p)) U;
+    } else {
+      ::new (static_cast<void*>(p)) U(std::forward<Args>(args)...);
+    }
+  }
+};
+
 // The four arrays the policy hands to the cache runtime
 // (coll_cache_lib/facade.cc:238-261, coll_cache_lib/coll_cache/optimal_solver_class.h:34-70).
 struct Placement {
-  std::vector<uint32_t> nid_to_block;       // [N]
+  std::vector<uint32_t, NoInitAlloc<uint32_t>> nid_to_block;  // [N]
   std::vector<uint8_t> block_placement;     // [B] bit g: rows of the block are stored on GPU g
   std::vector<uint8_t> block_access_from;   // [G][B] source location per reader (G = host)
   std::vector<double> block_density;        // [B] percent of N
@@ -75,9 +99,11 @@ std::string solve_placement(int policy, int num_device, uint64_t num_total_item,
 // Modelled cost of a placement per reader under the concurrent-source model the split-search
 // policy minimises: max((local + served to peers + 1) * t_local, peers * t_remote, host * t_cpu),
 // the fractions being shares of the recorded hotness.  Lets callers compare policies before building.
+// `nid_to_block_in_place`, if given, is read instead of p.nid_to_block (spares the caller a copy
+// of the per-key array).
 std::string placement_cost(const Placement& p, uint64_t num_total_item, const uint32_t* rank_ids,
                            const uint32_t* rank_freqs, double t_local, double t_remote, double t_cpu,
-                           double* cost_per_reader);
+                           double* cost_per_reader, const uint32_t* nid_to_block_in_place = nullptr);
 
 // Keys served to `reader` by each GPU source, ascending key order
 // (replaces coll_cache_lib/cuda/cache_hashtable.cuh:741-835).  counts has G+1 entries
