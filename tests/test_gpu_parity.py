@@ -561,7 +561,7 @@ def test_host_buffers_in_place_and_staged(built_lib, golden_cases):
 
 def test_auto_mode_follows_the_host_share(built_lib, extract_mode):
     """In auto mode the first lookup is grouped; later ones go direct once a finished lookup
-    has shown a small host share, and back when the share is large.  A direct lookup's counts
+    has shown few host rows, and back when there are many.  A direct lookup's counts
     reach the library with the start of the next lookup, so the switch back takes one lookup
     longer than the switch forth."""
     if extract_mode != "auto":
@@ -575,6 +575,7 @@ def test_auto_mode_follows_the_host_share(built_lib, extract_mode):
     cache.set_placement(p)
     host = pinned_table(table)
     cache.build(0, 0, host.data_ptr())
+    cache.tune(0, direct_max_host_rows=1000)      # direct while a lookup took <= 1000 host rows
     cached = np.nonzero(np.asarray(p.block_access_from).reshape(1, -1)[0][p.nid_to_block] == 0)[0]
     missing = np.nonzero(np.asarray(p.block_access_from).reshape(1, -1)[0][p.nid_to_block] != 0)[0]
     rng = np.random.default_rng(1)
