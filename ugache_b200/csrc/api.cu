@@ -543,6 +543,8 @@ struct Replica {
   uint64_t free_head = 0, free_count = 0;
   bool static_used = false;                // lookups through the fixed scratch array were issued
   int refresh_fill_ctas = 20;              // grid of the refresh-time fill kernel
+  cudaStream_t fill_stream = nullptr;      // lowest-priority stream the refresh-time fill runs on
+  cudaEvent_t fill_ev[2] = {nullptr, nullptr};
   float t_byte[kNumGroup] = {0, 0, 0};     // seconds per byte (any common scale) per source group
   int gather_dynamic = 1;
   cudaStream_t copy_stream = nullptr;      // host-buffer lookups: rows leave on this stream
@@ -849,6 +851,11 @@ void release_replica(ugc_ctx* c, Replica* r) {
   for (cudaEvent_t e : r->prof_events) cudaEventDestroy(e);
   for (cudaEvent_t e : r->copy_events) cudaEventDestroy(e);
   if (r->copy_stream) cudaStreamDestroy(r->copy_stream);
+  if (r->fill_stream) {
+    cudaStreamDestroy(r->fill_stream);
+    cudaEventDestroy(r->fill_ev[0]);
+    cudaEventDestroy(r->fill_ev[1]);
+  }
   for (int i = 0; i < r->n_ipc_opened; i++)
     if (!dev_block_free(r->ipc_opened[i])) cudaIpcCloseMemHandle(r->ipc_opened[i]);
   ctx_free_shared(c, r->slice);
@@ -1894,10 +1901,31 @@ int ugc_refresh_fill(ugc_ctx* c, int replica_id, void* stream) {
     // (coll_cache_lib/cuda/cache_hashtable.cuh:637-645)
     if (n > r->free_count) return fail(UGC_ERR_CAPACITY, "refresh fill: free slots ran out");
     const SlotView head{r->free_ring, (uint32_t)r->free_head, (uint32_t)r->capacity};
-    // A small grid keeps the refill from taking bandwidth from running lookups
-    // (the reference limits it to 20 blocks, coll_cache_lib/cache_context.cu:4067).
-    UGC_CUDA(launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, kListInsert), head, (uint32_t)n,
-                                 c->cfg.row_bytes, c->cfg.empty_feat, r->refresh_fill_ctas, s));
+    // The refill must not stand in the way of running lookups: a small grid (the reference
+    // limits it to 20 blocks, coll_cache_lib/cache_context.cu:4067), in batches of 32,768 rows
+    // so that no fill CTA stays resident for long, on a stream of the lowest priority (the
+    // reference's low_pri_stream, coll_cache_lib/facade.cc:376) tied to the caller's stream
+    // by events.  An extraction kernel that needs every SM slot of the GPU for its one wave
+    // then gets the slots between two batches.
+    if (!r->fill_stream) {
+      int lo = 0, hi = 0;
+      UGC_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+      UGC_CUDA(cudaStreamCreateWithPriority(&r->fill_stream, cudaStreamNonBlocking, lo));
+      UGC_CUDA(cudaEventCreateWithFlags(&r->fill_ev[0], cudaEventDisableTiming));
+      UGC_CUDA(cudaEventCreateWithFlags(&r->fill_ev[1], cudaEventDisableTiming));
+    }
+    UGC_CUDA(cudaEventRecord(r->fill_ev[0], s));
+    UGC_CUDA(cudaStreamWaitEvent(r->fill_stream, r->fill_ev[0], 0));
+    const size_t kFillBatch = 32768;
+    for (size_t off = 0; off < n; off += kFillBatch) {
+      const size_t m = std::min(kFillBatch, n - off);
+      SlotView part = head;
+      part.base = (uint32_t)((r->free_head + off) % r->capacity);
+      UGC_CUDA(launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, kListInsert) + off, part, (uint32_t)m,
+                                   c->cfg.row_bytes, c->cfg.empty_feat, r->refresh_fill_ctas, r->fill_stream));
+    }
+    UGC_CUDA(cudaEventRecord(r->fill_ev[1], r->fill_stream));
+    UGC_CUDA(cudaStreamWaitEvent(s, r->fill_ev[1], 0));
     UGC_CUDA(launch_table_insert(r->table, list_ptr(r, kListInsert), head, (uint32_t)replica_id, (uint32_t)n,
                                  r->counters, s));
     UGC_TRY(check_table_errors(r, s, "refresh insert"));
