@@ -655,3 +655,36 @@ def test_host_list_in_address_order(built_lib, extract_mode):
     assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
     assert cache.stats(0)["lookups_host_ordered"] == 5
     cache.close()
+
+
+def test_refresh_with_a_fill_of_several_batches(built_lib, extract_mode):
+    """A refresh that brings in more rows than one fill batch (32,768): the batches run on the
+    library's low-priority stream and take consecutive windows of the free-slot ring, also across
+    its wrap-around; lookups are exact afterwards and every stored row has its own slot."""
+    if extract_mode not in ("grouped", "direct"):
+        pytest.skip("one grouped and one direct run are enough")
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim = 600_000, 16
+    table = wl.table(91, N, dim)
+    rng = np.random.default_rng(17)
+    order = rng.permutation(N).astype(np.uint32)
+    cache = rt.Cache(1, N, dim * 4, 0.30, max_batch=1 << 15, table_kind=1)
+    cache.set_placement(rt.solve_placement("rep", 1, order, None, 30.0))
+    host = pinned_table(table)
+    cache.build(0, 0, host.data_ptr())
+    allk = torch.arange(N, dtype=torch.int32, device="cuda")
+    for round_ in range(3):                      # each round replaces 100,000 of the 180,000 rows
+        order = np.roll(order, 100_000)
+        p = rt.solve_placement("rep", 1, order, None, 30.0)
+        cache.refresh_all_local(p, [0])
+        words = cache.table_words(0, allk).cpu().numpy().view(np.uint32)
+        stored = p.nid_to_block == 0
+        assert np.array_equal(words != 0xFFFFFFFF, stored), round_
+        slots = words[stored] & 0x0FFFFFFF
+        assert len(np.unique(slots)) == int(stored.sum())
+        assert slots.max() < int(N * 0.301)
+        keys = rng.integers(0, N, 20_000).astype(np.int64)
+        assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
+        st = cache.stats(0)
+        assert st["err_table"] == 0 and st["free_rows"] == st["capacity_rows"] - int(stored.sum())
+    cache.close()
