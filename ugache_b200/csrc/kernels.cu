@@ -856,7 +856,7 @@ __global__ void __launch_bounds__(kBlock, DEEP ? 3 : 4)
   if (threadIdx.x < kNumGroup) s_cnt[threadIdx.x] = 0;
 
   unsigned long long t0 = 0;
-  if (threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  if ((threadIdx.x & 31) == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
 
   uint32_t bad = 0;
 
@@ -874,7 +874,9 @@ __global__ void __launch_bounds__(kBlock, DEEP ? 3 : 4)
   // The extraction ahead of this one is complete now.  One thread hands ITS counts on (they
   // sit in the other slot, final) -- to the pinned host mirror the library reads to choose
   // the mode of later lookups -- and clears that slot for the launch after this one.
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
+  // (the thread chosen for this belongs to the warp that is dealt the fewest tiles -- the last
+  // warp of the last CTA -- so that the writes across PCIe delay no warp the launch waits for)
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == blockDim.x - 32) {
     uint32_t* other = p.counters->dcount[p.slot ^ 1u];
     uint32_t prev[kNumGroup];
 #pragma unroll
