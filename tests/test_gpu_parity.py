@@ -658,7 +658,7 @@ def test_host_list_in_address_order(built_lib, extract_mode):
 
 
 def test_refresh_with_a_fill_of_several_batches(built_lib, extract_mode):
-    """A refresh that brings in more rows than one fill batch (32,768): the batches run on the
+    """A refresh that brings in more rows than one fill batch: the batches run on the
     library's low-priority stream and take consecutive windows of the free-slot ring, also across
     its wrap-around; lookups are exact afterwards and every stored row has its own slot."""
     if extract_mode not in ("grouped", "direct"):
@@ -673,8 +673,8 @@ def test_refresh_with_a_fill_of_several_batches(built_lib, extract_mode):
     host = pinned_table(table)
     cache.build(0, 0, host.data_ptr())
     allk = torch.arange(N, dtype=torch.int32, device="cuda")
-    for round_ in range(3):                      # each round replaces 100,000 of the 180,000 rows
-        order = np.roll(order, 100_000)
+    for round_ in range(3):                      # each round replaces 150,000 of the 180,000 rows
+        order = np.roll(order, 150_000)
         p = rt.solve_placement("rep", 1, order, None, 30.0)
         cache.refresh_all_local(p, [0])
         words = cache.table_words(0, allk).cpu().numpy().view(np.uint32)

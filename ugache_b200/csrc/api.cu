@@ -1902,7 +1902,7 @@ int ugc_refresh_fill(ugc_ctx* c, int replica_id, void* stream) {
     if (n > r->free_count) return fail(UGC_ERR_CAPACITY, "refresh fill: free slots ran out");
     const SlotView head{r->free_ring, (uint32_t)r->free_head, (uint32_t)r->capacity};
     // The refill must not stand in the way of running lookups: a small grid (the reference
-    // limits it to 20 blocks, coll_cache_lib/cache_context.cu:4067), in batches of 32,768 rows
+    // limits it to 20 blocks, coll_cache_lib/cache_context.cu:4067), in batches of 131,072 rows
     // so that no fill CTA stays resident for long, on a stream of the lowest priority (the
     // reference's low_pri_stream, coll_cache_lib/facade.cc:376) tied to the caller's stream
     // by events.  An extraction kernel that needs every SM slot of the GPU for its one wave
@@ -1916,7 +1916,7 @@ int ugc_refresh_fill(ugc_ctx* c, int replica_id, void* stream) {
     }
     UGC_CUDA(cudaEventRecord(r->fill_ev[0], s));
     UGC_CUDA(cudaStreamWaitEvent(r->fill_stream, r->fill_ev[0], 0));
-    const size_t kFillBatch = 32768;
+    const size_t kFillBatch = 131072;
     for (size_t off = 0; off < n; off += kFillBatch) {
       const size_t m = std::min(kFillBatch, n - off);
       SlotView part = head;
