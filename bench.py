@@ -72,6 +72,7 @@ def parse_args():
     ap.add_argument("--direct-ctas-per-sm", type=int, default=0)
     ap.add_argument("--cpu-threads", type=int, default=0,
                     help="threads of the CPU arms; 0 = every core this process may run on")
+    ap.add_argument("--tune", default="", help="ugc_tuning fields for the whole run: k=v,k=v")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--pdl", type=int, default=-1)
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 30)")
@@ -925,6 +926,9 @@ def run_ours(a, job=None):
         tune["extract_mode"] = {"auto": 0, "grouped": 1, "direct": 2}[a.extract_mode]
     if a.direct_ctas_per_sm:
         tune["direct_ctas_per_sm"] = a.direct_ctas_per_sm
+    for kv in filter(None, a.tune.split(",")):
+        k, v = kv.split("=")
+        tune[k.strip()] = int(v)
     if tune:
         cache.tune(rank, **tune)
     connect_ranks(cache, rank, world, dev, stream)

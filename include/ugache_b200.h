@@ -67,7 +67,8 @@ typedef enum { UGC_TABLE_AUTO = 0, UGC_TABLE_FLAT = 1, UGC_TABLE_HASHED = 2 } ug
  *   DIRECT   one kernel probes the table and copies each row from wherever it is, with no
  *            index lists: best when nearly all rows come from GPU memory;
  *   AUTO     DIRECT while the last finished lookup of the replica took no more than
- *            ugc_tuning.direct_max_host_rows rows from the host table, else GROUPED
+ *            ugc_tuning.direct_max_host_rows rows from the host table, or more rows from
+ *            peers than from the host; else GROUPED
  *            (the library reads those counts from a pinned mirror the kernels write; no
  *            synchronisation). */
 typedef enum { UGC_EXTRACT_AUTO = 0, UGC_EXTRACT_GROUPED = 1, UGC_EXTRACT_DIRECT = 2 } ugc_extract_mode;
@@ -408,6 +409,13 @@ typedef struct {
                                      small kernels between lookup and gather) when the last
                                      finished lookup took at least this many rows from the
                                      host table; 0 = never                                  */
+  int32_t refresh_fill_ctas;      /* refresh-time fill: CTAs per launch (20, as the reference,
+                                     coll_cache_lib/cache_context.cu:4067), rows per launch    */
+  int32_t refresh_fill_batch_rows; /* (131,072) and a host-side pause between launches in us    */
+  int32_t refresh_fill_pause_us;  /* (0).  The fill shares the host link and the host's row rate
+                                     with the lookups' host rows: a pause trades refresh time
+                                     for flatter lookup times while it runs (the reference
+                                     sleeps 3 ms between 4092-row batches, :4061-4070)       */
   int32_t gather_dynamic;         /* grouped gather: 1 = lists are handed out in chunks and a
                                      CTA whose own list is drained takes chunks of the other
                                      groups' lists; 0 = fixed striding inside each group     */

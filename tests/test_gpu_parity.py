@@ -26,6 +26,7 @@ def extract_mode(request, monkeypatch):
     # the two main shapes run everywhere; the other two on the tests that exercise the gather
     # and the mode switch (keeps the suite short)
     wide = {"test_golden_cases_bit_exact", "test_ragged_batch_sizes", "test_auto_mode_follows_the_host_share",
+            "test_auto_mode_stays_direct_when_peers_serve_more_rows_than_the_host",
             "test_duplicates_and_single_source_batches", "test_out_of_range_keys_are_counted_and_skipped",
             "test_unaligned_output_and_host_table", "test_refresh_keeps_results_identical",
             "test_host_list_in_address_order"}
@@ -594,6 +595,42 @@ def test_auto_mode_follows_the_host_share(built_lib, extract_mode):
     assert lookup_np(cache, 0, hot).tobytes() == orc.gather(table, hot).tobytes()   # still grouped
     st = cache.stats(0)
     assert st["lookups_direct"] == 4 and st["kernel_launches"] == 10 and st["last_local"] == 6000
+    cache.close()
+
+
+def test_auto_mode_stays_direct_when_peers_serve_more_rows_than_the_host(built_lib, extract_mode):
+    """Auto mode goes grouped only when the host rows of the last finished lookup exceed both the
+    threshold and the peer rows."""
+    if extract_mode != "auto":
+        pytest.skip("only meaningful in auto mode")
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim, G = 40000, 32, 2
+    table = wl.table(6, N, dim)
+    ids, freqs = wl.analytic_hotness(N, 1.2)
+    cache = rt.Cache(G, N, dim * 4, 0.25, max_batch=1 << 14)
+    p = rt.solve_placement("clique_part", G, ids, freqs, 25.0)
+    cache.set_placement(p)
+    host = pinned_table(table)
+    for r in range(G):
+        cache.build(r, 0, host.data_ptr())
+    cache.connect_local()
+    for r in range(G):
+        cache.attach_peers(r)
+    cache.tune(0, direct_max_host_rows=1000)
+    src = np.asarray(p.block_access_from).reshape(G, -1)[0][p.nid_to_block]
+    peer, far = np.nonzero(src == 1)[0], np.nonzero(src == G)[0]
+    assert len(peer) > 0 and len(far) > 0
+    rng = np.random.default_rng(2)
+    peer_heavy = np.concatenate([rng.choice(peer, 6000), rng.choice(far, 2000)]).astype(np.int64)
+    host_heavy = np.concatenate([rng.choice(peer, 500), rng.choice(far, 2000)]).astype(np.int64)
+    for keys in (peer_heavy,) * 3:      # grouped (no record yet), then direct twice
+        assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
+    st = cache.stats(0)
+    assert st["lookups_direct"] == 2 and (st["last_remote"], st["last_host"]) == (6000, 2000)
+    for keys in (host_heavy,) * 3:      # direct twice more (the record lags), then grouped
+        assert lookup_np(cache, 0, keys).tobytes() == orc.gather(table, keys).tobytes()
+    st = cache.stats(0)
+    assert st["lookups_direct"] == 4 and (st["last_remote"], st["last_host"]) == (500, 2000)
     cache.close()
 
 

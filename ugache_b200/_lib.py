@@ -104,6 +104,9 @@ class Tuning(C.Structure):
         ("direct_tile_keys", C.c_int32),
         ("direct_deep", C.c_int32),
         ("host_order_min_rows", C.c_int32),
+        ("refresh_fill_ctas", C.c_int32),
+        ("refresh_fill_batch_rows", C.c_int32),
+        ("refresh_fill_pause_us", C.c_int32),
         ("gather_dynamic", C.c_int32),
         ("host_zero_copy", C.c_int32),
     ]

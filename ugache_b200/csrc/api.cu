@@ -543,6 +543,8 @@ struct Replica {
   uint64_t free_head = 0, free_count = 0;
   bool static_used = false;                // lookups through the fixed scratch array were issued
   int refresh_fill_ctas = 20;              // grid of the refresh-time fill kernel
+  int refresh_fill_batch_rows = 131072;    // rows per launch of it
+  int refresh_fill_pause_us = 0;           // host-side pause between two launches
   cudaStream_t fill_stream = nullptr;      // lowest-priority stream the refresh-time fill runs on
   cudaEvent_t fill_ev[2] = {nullptr, nullptr};
   float t_byte[kNumGroup] = {0, 0, 0};     // seconds per byte (any common scale) per source group
@@ -962,7 +964,12 @@ bool choose_direct(const Replica* r) {
   if (r->extract_mode == UGC_EXTRACT_GROUPED || !r->feedback) return false;
   const volatile Feedback* f = r->feedback;
   if (f->seq == 0) return false;
-  return f->count[kGroupHost] <= (uint32_t)r->direct_max_host_rows;
+  // Grouped pays off when a batch takes many rows from the host (ordered host list, all CTAs
+  // helping) and few from peers; with peer rows in the mix the direct kernel was faster at
+  // every point measured (2 GPUs: 1078 against 1207 us with 49 k host / 93 k peer rows,
+  // 2376 against 2514 us with 128 k host / 317 k peer rows).
+  const uint32_t host = f->count[kGroupHost], remote = f->count[kGroupRemote];
+  return host <= (uint32_t)r->direct_max_host_rows || remote > host;
 }
 
 // `n_dev` != nullptr: the key count is read on the device from there (at most n); such a lookup
@@ -1916,13 +1923,20 @@ int ugc_refresh_fill(ugc_ctx* c, int replica_id, void* stream) {
     }
     UGC_CUDA(cudaEventRecord(r->fill_ev[0], s));
     UGC_CUDA(cudaStreamWaitEvent(r->fill_stream, r->fill_ev[0], 0));
-    const size_t kFillBatch = 131072;
-    for (size_t off = 0; off < n; off += kFillBatch) {
-      const size_t m = std::min(kFillBatch, n - off);
+    const size_t batch = (size_t)std::max(r->refresh_fill_batch_rows, 1024);
+    for (size_t off = 0; off < n; off += batch) {
+      const size_t m = std::min(batch, n - off);
       SlotView part = head;
       part.base = (uint32_t)((r->free_head + off) % r->capacity);
       UGC_CUDA(launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, kListInsert) + off, part, (uint32_t)m,
                                    c->cfg.row_bytes, c->cfg.empty_feat, r->refresh_fill_ctas, r->fill_stream));
+      if (r->refresh_fill_pause_us > 0 && off + batch < n) {
+        // pacing: the host link and the host's row rate are shared with the lookups' host rows
+        // (and with the other GPUs' fills); the reference sleeps 3 ms between its 4092-row
+        // batches for the same reason (coll_cache_lib/cache_context.cu:4061-4070)
+        UGC_CUDA(cudaStreamSynchronize(r->fill_stream));
+        usleep((useconds_t)r->refresh_fill_pause_us);
+      }
     }
     UGC_CUDA(cudaEventRecord(r->fill_ev[1], r->fill_stream));
     UGC_CUDA(cudaStreamWaitEvent(s, r->fill_ev[1], 0));
@@ -2078,6 +2092,9 @@ int ugc_get_tuning(ugc_ctx* c, int replica_id, ugc_tuning* out) {
   out->direct_tile_keys = r->direct_tile_shift ? (1 << r->direct_tile_shift) : 0;
   out->direct_deep = r->direct_deep;
   out->host_order_min_rows = r->host_order_min_rows;
+  out->refresh_fill_ctas = r->refresh_fill_ctas;
+  out->refresh_fill_batch_rows = r->refresh_fill_batch_rows;
+  out->refresh_fill_pause_us = r->refresh_fill_pause_us;
   return UGC_OK;
 }
 
@@ -2110,6 +2127,9 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   r->direct_tile_shift = t->direct_tile_keys == 8 ? 3 : t->direct_tile_keys == 16 ? 4 : t->direct_tile_keys == 32 ? 5 : 0;
   r->direct_deep = t->direct_deep ? 1 : 0;
   r->host_order_min_rows = t->host_order_min_rows < 0 ? 0 : t->host_order_min_rows;
+  if (t->refresh_fill_ctas > 0) r->refresh_fill_ctas = t->refresh_fill_ctas;
+  if (t->refresh_fill_batch_rows > 0) r->refresh_fill_batch_rows = t->refresh_fill_batch_rows;
+  r->refresh_fill_pause_us = t->refresh_fill_pause_us < 0 ? 0 : t->refresh_fill_pause_us;
   return UGC_OK;
 }
 
