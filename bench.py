@@ -73,6 +73,8 @@ def parse_args():
     ap.add_argument("--cpu-threads", type=int, default=0,
                     help="threads of the CPU arms; 0 = every core this process may run on")
     ap.add_argument("--tune", default="", help="ugc_tuning fields for the whole run: k=v,k=v")
+    ap.add_argument("--pool-bag", type=int, default=0,
+                    help="also time the pooled lookup with bags of this many consecutive keys")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--pdl", type=int, default=-1)
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 30)")
@@ -1035,6 +1037,45 @@ def run_ours(a, job=None):
                                                                  all_list(v0.elapsed_time(v1))]})
             cache.tune(rank, **base_tuning)
 
+    # ---- optional: the pooled lookup (bags of --pool-bag consecutive keys) on the same batches ----
+    pooled = None
+    if a.pool_bag > 0 and a.workload == "dlr":
+        from oracle import oracle as orc
+        n_bags = a.batch // a.pool_bag
+        pout = torch.empty((n_bags, a.dim), dtype=torch.float32, device=dev)
+        ename = "f32" if elem == 4 else "f16"
+
+        def pstep(i):
+            cache.lookup_pool(rank, keys_dev[i], bag_size=a.pool_bag, elem=ename, out=pout, stream=stream)
+
+        pstep(0)
+        torch.cuda.synchronize()
+        k0 = keys_np[0]
+        if a.empty_feat:
+            k0 = k0 & ((1 << a.empty_feat) - 1)
+        rows0 = orc.gen_rows_for_keys(a.seed, k0, a.dim, np.float32 if elem == 4 else np.float16)
+        want = orc.pool(rows0, np.arange(a.batch), bag_size=a.pool_bag)
+        p_ok = bool(pout.cpu().numpy().view(np.uint32).tobytes() == want.view(np.uint32).tobytes())
+        p_ranks = int(round(all_sum(1.0 if p_ok else 0.0)))
+        for i in range(a.warmup):
+            pstep(i)
+        barrier()
+        torch.cuda.synchronize()
+        v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        v0.record()
+        for i in range(a.warmup, total):
+            pstep(i)
+        v1.record()
+        torch.cuda.synchronize()
+        barrier()
+        p_us = [m / a.steps * 1e3 for m in all_list(v0.elapsed_time(v1))]
+        pooled = {"bag_size": a.pool_bag, "bags_per_step": n_bags, "step_us_per_rank": p_us,
+                  "rows_read_gbs_per_gpu": a.batch * row_bytes / (max(p_us) * 1e-6) / 1e9,
+                  "bytes_written_per_step": n_bags * a.dim * 4,
+                  "verified_ranks_bit_exact_vs_oracle": p_ranks,
+                  "note": "ugc_lookup_pool: lookup + fp32 sum per bag in one kernel; the rows are not written"}
+        del pout
+
     # ---- same steps again with per-kernel events (for the roofline of the gather) ------
     cache.profile_begin(rank, a.steps)
     for i in range(a.warmup, total):
@@ -1360,7 +1401,7 @@ def run_ours(a, job=None):
         "lookups_direct_share": st_last["lookups_direct"] / max(st_last["lookups"], 1),
         "per_rank": {"step_us": [m / a.steps * 1e3 for m in ms_all], "gather_us": ga_all,
                      "group_done_us": {"local": grp_all[0], "remote": grp_all[1], "host": grp_all[2]}},
-        "variants": variants, "refresh": refresh,
+        "variants": variants, "refresh": refresh, "pooled_lookup": pooled,
         "verified_vs_oracle": verified, "setup_s": setup_s, "tuning": cache.get_tuning(rank),
         "cache": {"local_rows": st["num_local_rows"], "remote_keys": st["num_remote_keys"],
                   "host_keys": st["num_host_keys"], "table_bytes": st["table_bytes"]},

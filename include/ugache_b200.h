@@ -162,6 +162,8 @@ typedef struct {
   uint64_t lookups_host_ordered; /* grouped lookups whose host list was put in address order */
   uint64_t lookups_direct;     /* lookups that took the direct (one-kernel) extraction  */
   uint64_t kernel_launches;    /* kernels launched by lookups: 2 per grouped, 1 per direct */
+  uint64_t lookups_pooled;     /* ugc_lookup_pool calls                                   */
+  uint64_t pool_rows[3];       /* rows they summed so far: local / peers / host           */
 } ugc_stats_t;
 
 /* sizeof of the structs of this header, in the order ugc_config, ugc_peer_handle,
@@ -317,6 +319,27 @@ int ugc_lookup_unique(ugc_ctx* ctx, int replica_id, const void* keys, int key_by
                       void* out_rows, void* unique_keys, int32_t* inverse, uint32_t* n_unique,
                       void* stream);
 
+/* Pooled lookup (embedding bag): out[b, :] = the sum, or the mean, of the rows of the keys of
+ * bag b, as fp32 -- lookup, row fetch and reduction in one kernel, so the looked-up rows never
+ * reach memory and the output is n_bags x dim x 4 bytes instead of n_keys x row_bytes.
+ *   keys      n_keys ids (key_bytes 4 or 8), device memory;
+ *   offsets   n_bags + 1 ascending positions into keys (device memory): bag b is
+ *             keys[offsets[b] .. offsets[b+1]); or NULL: bag b is keys[b*bag_size .. (b+1)*bag_size);
+ *   elem_type what a row holds (the library otherwise treats rows as bytes);
+ *   out       n_bags x dim fp32, dim = row_bytes / element size, 16-byte aligned.
+ * Defined bit for bit: every output element starts at +0 and takes its bag's rows in key order,
+ * one IEEE fp32 addition each (fp16 elements are widened first, which is exact); the mean
+ * divides that sum once by the bag's length (as fp32); an empty bag gives zeros.  Ids outside
+ * the key space are counted in err_key_range and add nothing.  Rows must be a multiple of 16
+ * bytes and the tables 16-byte aligned (UGC_ERR_UNSUPPORTED otherwise).  Ordered against a
+ * refresh like every lookup.  The reference has no such call: its applications hand the rows
+ * to the model, which pools them (example/dlr/main.py: `combiner`). */
+typedef enum { UGC_ELEM_F32 = 0, UGC_ELEM_F16 = 1 } ugc_elem_type;
+typedef enum { UGC_POOL_SUM = 0, UGC_POOL_MEAN = 1 } ugc_pool_mode;
+int ugc_lookup_pool(ugc_ctx* ctx, int replica_id, const void* keys, int key_bytes, size_t n_keys,
+                    const int64_t* offsets, size_t n_bags, size_t bag_size, int elem_type, int mode,
+                    float* out, void* stream);
+
 /* Grows the per-replica lookup scratch so that batches of up to max_batch keys are accepted
  * (the reference re-allocates its output buffer when a larger batch shows up,
  * python/collcache/torch/adapter.cc:213-224).  Must not run while a lookup of that replica
@@ -416,9 +439,15 @@ typedef struct {
                                      with the lookups' host rows: a pause trades refresh time
                                      for flatter lookup times while it runs (the reference
                                      sleeps 3 ms between 4092-row batches, :4061-4070)       */
+  int32_t refresh_early_repoint;  /* refresh: 1 (default) = a key whose new source is a peer that
+                                     holds the row already is re-pointed to it in place in the
+                                     evict phase; 0 = removed there and attached in the attach
+                                     phase, served by the host in between (the reference's order) */
   int32_t gather_dynamic;         /* grouped gather: 1 = lists are handed out in chunks and a
                                      CTA whose own list is drained takes chunks of the other
                                      groups' lists; 0 = fixed striding inside each group     */
+  int32_t split_fixed;            /* 1 = host_ctas and remote_ctas are the CTA counts of their
+                                     groups instead of caps on the derived split (sweeps)     */
   int32_t host_zero_copy;         /* ugc_lookup_host with GPU-mapped pinned buffers: bit 0 the
                                      kernel reads the keys in place, bit 1 it writes the rows
                                      in place; a cleared bit selects a staging copy          */

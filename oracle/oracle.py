@@ -137,6 +137,39 @@ def gather(table, keys, empty_feat=0, num_threads=0, out=None):
     return out
 
 
+def pool(table, keys, offsets=None, bag_size=0, mean=False, empty_feat=0, num_keys=None):
+    """Embedding-bag restatement: ``out[b] = sum over the keys of bag b of table[key]`` as fp32,
+    added in key order starting from +0 (one IEEE addition per row and element; fp16 elements
+    are widened first); ``mean`` divides once by the bag's length; ids outside the table add
+    nothing; an empty bag gives zeros.  No reference counterpart: the reference's applications
+    pool in the model (example/dlr/main.py).  numpy, position by position over all bags at once,
+    which keeps every bag's own order."""
+    table = np.ascontiguousarray(table)
+    keys = np.ascontiguousarray(keys, dtype=np.int64)
+    n = len(keys)
+    if offsets is None:
+        n_bags = n // bag_size
+        offsets = np.arange(n_bags + 1, dtype=np.int64) * bag_size
+    offsets = np.clip(np.asarray(offsets, dtype=np.int64), 0, n)
+    begin, end = offsets[:-1], np.maximum(offsets[1:], offsets[:-1])
+    length = end - begin
+    out = np.zeros((len(begin), table.shape[1]), dtype=np.float32)
+    mask_rows = (1 << empty_feat) - 1 if empty_feat else None
+    limit = table.shape[0] if num_keys is None else num_keys   # ids of the key space
+    for j in range(int(length.max()) if len(length) else 0):
+        bags = np.nonzero(length > j)[0]
+        k = keys[begin[bags] + j]
+        ok = (k >= 0) & (k < limit)
+        bags, k = bags[ok], k[ok]
+        if mask_rows is not None:
+            k = k & mask_rows
+        out[bags] = out[bags] + table[k].astype(np.float32)
+    if mean:
+        nz = length > 0
+        out[nz] = out[nz] / length[nz].astype(np.float32)[:, None]
+    return out
+
+
 def max_threads():
     return lib().orc_max_threads()
 

@@ -54,6 +54,14 @@ def test_collcache_torch_api_threads(built_lib):
                 out = co.coll_torch_lookup_key_t_val_ret(r, torch.from_numpy(k).to(dev).to(torch.int32),
                                                          pad_to_8=False)
                 assert out.cpu().numpy().tobytes() == orc.gather(table, k).tobytes()
+            # embedding-bag forward in one kernel: bit for bit the sequential fp32 sum of those rows
+            k = batches[r][0]
+            pooled = co.coll_torch_lookup_pool(r, torch.from_numpy(k).to(dev), bag_size=10, mode="sum")
+            assert pooled.cpu().numpy().tobytes() == orc.pool(table, k, bag_size=10).tobytes()
+            offs = torch.tensor([0, 3, 3, 1000, len(k)])
+            pooled = co.coll_torch_lookup_pool(r, torch.from_numpy(k).to(dev).to(torch.int32), offsets=offs,
+                                               mode="mean")
+            assert pooled.cpu().numpy().tobytes() == orc.pool(table, k, offsets=offs.numpy(), mean=True).tobytes()
             # a second refresh in the background while this thread keeps looking up
             for i in range(3):
                 co.coll_torch_record(r, torch.from_numpy(wl.zipf_keys(950 + i, 20000, N, 1.3)))
@@ -112,6 +120,9 @@ WORKER = textwrap.dedent("""
         out = co.coll_torch_lookup_key_t_val_ret(r, torch.from_numpy(k).to(dev).to(torch.int32), False)
         assert out.dtype == torch.float16
         assert out.cpu().numpy().tobytes() == orc.gather(table, k).tobytes()
+    pooled = co.coll_torch_lookup_pool(r, torch.from_numpy(k).to(dev), bag_size=6)
+    assert pooled.dtype == torch.float32 and pooled.shape == (1000, dim)
+    assert pooled.cpu().numpy().tobytes() == orc.pool(table, k, bag_size=6).tobytes()
     import ctypes
     from ugache_b200 import _lib
     st = _lib.Stats()

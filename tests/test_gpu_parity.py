@@ -280,6 +280,63 @@ def test_refresh_keeps_results_identical(built_lib):
         cache.close()
 
 
+def test_refresh_repoints_keys_that_move_to_a_peer_in_place(built_lib):
+    """A key that was stored here and is read from a peer under the new placement, the peer
+    holding the row already, never falls back to the host during the refresh: its entry is
+    re-pointed in the evict phase.  With the tuning field cleared it is removed there and
+    attached later (the reference's order), and is served by the host in between."""
+    from ugache_b200 import runtime as rt, workload as wl
+    N, dim, G = 40000, 32, 2
+    table = wl.table(41, N, dim)
+    ids, freqs = wl.analytic_hotness(N, 1.05)
+    p_old = rt.solve_placement("intuitive", G, ids, freqs, 20.0)
+    p_new = rt.solve_placement("intuitive", G, np.roll(ids, 800), freqs, 20.0)
+    src_old = np.asarray(p_old.block_access_from).reshape(G, -1)[0][p_old.nid_to_block]
+    src_new = np.asarray(p_new.block_access_from).reshape(G, -1)[0][p_new.nid_to_block]
+    held = (np.asarray(p_old.block_placement)[p_old.nid_to_block] >> 1) & 1
+    moved = np.nonzero((src_old == 0) & (src_new == 1) & (held == 1))[0]
+    assert len(moved) > 100                  # rows leaving the replicated set
+    keys = np.random.default_rng(3).choice(moved, 4000).astype(np.int64)
+    want = orc.gather(table, keys).tobytes()
+    for kind in (1, 2):
+        for early in (1, 0):
+            cache = rt.Cache(G, N, dim * 4, 0.2, max_batch=1 << 14, table_kind=kind)
+            cache.set_placement(p_old)
+            host = pinned_table(table)
+            for r in range(G):
+                cache.build(r, 0, host.data_ptr())
+            cache.connect_local()
+            for r in range(G):
+                cache.attach_peers(r)
+                cache.tune(r, refresh_early_repoint=early)
+            assert lookup_np(cache, 0, keys).tobytes() == want
+            assert cache.stats(0)["last_local"] == len(keys)
+            cache.refresh_set_placement(p_new)
+            for r in range(G):
+                cache.refresh_evict(r)
+            assert lookup_np(cache, 0, keys).tobytes() == want
+            st = cache.stats(0)
+            if early:
+                assert (st["last_remote"], st["last_host"]) == (len(keys), 0), (kind, st)
+            else:
+                assert (st["last_remote"], st["last_host"]) == (0, len(keys)), (kind, st)
+            for r in range(G):
+                cache.refresh_fill(r)
+            for r in range(G):
+                cache.refresh_attach(r)
+            cache.refresh_commit()
+            assert lookup_np(cache, 0, keys).tobytes() == want
+            st = cache.stats(0)
+            assert (st["last_remote"], st["last_host"], st["err_table"]) == (len(keys), 0, 0)
+            # every key has the source the new placement names
+            allk = torch.arange(N, dtype=torch.int32, device="cuda")
+            got = cache.table_words(0, allk).cpu().numpy().view(np.uint32)
+            live = got != 0xFFFFFFFF
+            assert np.array_equal(live, src_new < G)
+            assert np.array_equal(got[live] >> 28, src_new[live].astype(np.uint32))
+            cache.close()
+
+
 def test_gnn_shaped_batches(built_lib):
     """Deduplicated, variable-size node-id batches from the sampled R-MAT graph, cache ordered
     by degree (the GNN configuration at small scale)."""

@@ -83,6 +83,8 @@ class Stats(C.Structure):
         ("lookups_host_ordered", C.c_uint64),
         ("lookups_direct", C.c_uint64),
         ("kernel_launches", C.c_uint64),
+        ("lookups_pooled", C.c_uint64),
+        ("pool_rows", C.c_uint64 * 3),
     ]
 
 
@@ -107,7 +109,9 @@ class Tuning(C.Structure):
         ("refresh_fill_ctas", C.c_int32),
         ("refresh_fill_batch_rows", C.c_int32),
         ("refresh_fill_pause_us", C.c_int32),
+        ("refresh_early_repoint", C.c_int32),
         ("gather_dynamic", C.c_int32),
+        ("split_fixed", C.c_int32),
         ("host_zero_copy", C.c_int32),
     ]
 
@@ -159,6 +163,7 @@ SIGNATURES = {
     "ugc_lookup_i64": (_I, [_P, _I, _P, _SZ, _P, _P]),
     "ugc_lookup_i64_static": (_I, [_P, _I, _P, _SZ, _P, _P]),
     "ugc_lookup_unique": (_I, [_P, _I, _P, _I, _SZ, _P, _P, _P, _P, _P]),
+    "ugc_lookup_pool": (_I, [_P, _I, _P, _I, _SZ, _P, _SZ, _SZ, _I, _I, _P, _P]),
     "ugc_reserve_batch": (_I, [_P, _I, C.c_uint32]),
     "ugc_lookup_host": (_I, [_P, _I, _P, _I, _SZ, _P, _P]),
     "ugc_refresh_set_placement": (_I, [_P, _P, _P, _P, _P, _I]),

@@ -201,6 +201,37 @@ def coll_torch_lookup_unique(local_id, keys):
     return rows[:int(n_unique.item())], inverse.to(torch.int64)
 
 
+def coll_torch_lookup_pool(local_id, keys, offsets=None, bag_size=0, mode="sum"):
+    """Embedding-bag forward in one kernel (``ugc_lookup_pool``): ``out[b]`` = the sum or mean of
+    the rows of bag ``b`` as fp32 ``[n_bags, dim]``; bags are ``keys[offsets[b]:offsets[b+1]]``
+    (int64 ``offsets`` of ``n_bags + 1`` entries) or runs of ``bag_size`` keys.  Bit for bit the
+    result of a sequential fp32 sum over ``coll_torch_lookup_key_t_val_ret``'s rows in key order.
+    No counterpart in the reference, whose applications pool in the model."""
+    dev = _state["dev"][local_id]
+    device = "cuda:%d" % dev
+    keys = keys.reshape(-1).contiguous()
+    if keys.dtype not in (torch.int64, torch.int32):
+        keys = keys.to(torch.int64)
+    if _state["dtype"] not in (torch.float32, torch.float16):
+        raise ValueError("pooled lookup needs an fp32 or fp16 table")
+    kb = 8 if keys.dtype == torch.int64 else 4
+    if offsets is not None:
+        offsets = offsets.to(device=device, dtype=torch.int64).contiguous()
+        n_bags = offsets.numel() - 1
+    else:
+        if bag_size <= 0:
+            raise ValueError("give offsets or a bag size")
+        n_bags = keys.numel() // bag_size
+    out = torch.empty((max(n_bags, 0), _state["dim"]), dtype=torch.float32, device=device)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    _lib.check(_lib.lib().ugc_lookup_pool(
+        _L().coll_cache_context(), local_id, ctypes.c_void_p(keys.data_ptr()), kb, keys.numel(),
+        ctypes.c_void_p(offsets.data_ptr() if offsets is not None else None), max(n_bags, 0), bag_size,
+        0 if _state["dtype"] == torch.float32 else 1, {"sum": 0, "mean": 1}[mode],
+        ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(stream)))
+    return out
+
+
 class _RefreshJob:
     """Handle of a background refresh: ``wait()`` joins it and re-raises its failure."""
 

@@ -549,6 +549,8 @@ struct Replica {
   cudaEvent_t fill_ev[2] = {nullptr, nullptr};
   float t_byte[kNumGroup] = {0, 0, 0};     // seconds per byte (any common scale) per source group
   int gather_dynamic = 1;
+  int split_fixed = 0;                     // host_ctas / remote_ctas are counts, not caps
+  int early_repoint = 1;                   // refresh: re-point keys to a peer that holds them, in place
   cudaStream_t copy_stream = nullptr;      // host-buffer lookups: rows leave on this stream
   std::vector<cudaEvent_t> copy_events;
   uint32_t* stamp = nullptr;               // deduplicated lookups: one stamp per id (first use)
@@ -596,6 +598,7 @@ struct Replica {
   Feedback* feedback_dev = nullptr;  // the same memory as the device addresses it
   uint64_t lookups_direct = 0;
   uint64_t kernel_launches = 0;
+  uint64_t lookups_pooled = 0;
   int host_zero_copy = 1;  // keys read in place; rows staged (the copy engine beats SM stores over PCIe)
   // per-kernel profiling (three events per lookup)
   std::vector<cudaEvent_t> prof_events;
@@ -897,6 +900,7 @@ GatherParams gather_params(ugc_ctx* c, Replica* r, void* out, uint32_t n) {
   for (int g = 0; g < kNumGroup; g++) p.t_byte[g] = r->t_byte[g];
   p.seq = (uint32_t)r->lookups;
   p.dynamic = r->gather_dynamic;
+  p.fixed_split = r->split_fixed;
   p.bulk_mask = r->bulk_mask;
   p.pdl = (r->pdl & 2) ? 1 : 0;
   return p;
@@ -1617,7 +1621,8 @@ static int attach_keys(ugc_ctx* c, Replica* r, int src, const uint32_t* keys_dev
   UGC_TRY(ensure(c, r->stage_b, n * sizeof(uint32_t)));
   const SlotView offs{static_cast<uint32_t*>(r->stage_b.ptr), 0, 0};
   UGC_CUDA(launch_table_resolve(r->peer_table[src], keys_dev, (uint32_t)n, (uint32_t)src, offs, r->counters, s));
-  UGC_CUDA(launch_table_insert(r->table, keys_dev, offs, (uint32_t)src, (uint32_t)n, r->counters, s));
+  // (a refresh may have re-pointed some of these keys to `src` already, with the same word)
+  UGC_CUDA(launch_table_insert(r->table, keys_dev, offs, (uint32_t)src, (uint32_t)n, r->counters, s, true));
   // the offset buffer is reused by the next source
   return check_table_errors(r, s, "peer attach");
 }
@@ -1726,6 +1731,54 @@ int ugc_lookup_unique(ugc_ctx* c, int replica_id, const void* keys, int key_byte
                          unique_keys, inverse, n_unique, r->counters, s));
   r->kernel_launches += 2;
   return do_lookup(c, r, unique_keys, key_bytes, n, out_rows, s, n_unique);
+}
+
+int ugc_lookup_pool(ugc_ctx* c, int replica_id, const void* keys, int key_bytes, size_t n_keys,
+                    const int64_t* offsets, size_t n_bags, size_t bag_size, int elem_type, int mode,
+                    float* out, void* stream) {
+  Replica* r;
+  UGC_TRY(get_replica(c, replica_id, true, &r));
+  if (key_bytes != 4 && key_bytes != 8) return fail(UGC_ERR_INVALID, "key_bytes must be 4 or 8");
+  if (elem_type != UGC_ELEM_F32 && elem_type != UGC_ELEM_F16) return fail(UGC_ERR_INVALID, "unknown element type %d", elem_type);
+  if (mode != UGC_POOL_SUM && mode != UGC_POOL_MEAN) return fail(UGC_ERR_INVALID, "unknown pooling mode %d", mode);
+  if (n_bags == 0) return UGC_OK;
+  if (!out || (n_keys && !keys)) return fail(UGC_ERR_INVALID, "keys and out must be non-null");
+  if (!offsets && bag_size == 0) return fail(UGC_ERR_INVALID, "give offsets or a bag size");
+  if (!offsets && n_bags * bag_size > n_keys)
+    return fail(UGC_ERR_INVALID, "%zu bags of %zu keys need more than the %zu keys given", n_bags, bag_size, n_keys);
+  if (n_keys > kMaxBatch || n_bags > kMaxBatch) return fail(UGC_ERR_INVALID, "at most 2^28 keys and bags per call");
+  const uint32_t row_bytes = c->cfg.row_bytes;
+  const uint32_t elem = elem_type == UGC_ELEM_F16 ? 2u : 4u;
+  if (row_bytes % 16 != 0) return fail(UGC_ERR_UNSUPPORTED, "pooled lookup needs rows of a multiple of 16 bytes");
+  uintptr_t bits = reinterpret_cast<uintptr_t>(out);
+  for (int i = 0; i < kMaxLocation; i++) bits |= reinterpret_cast<uintptr_t>(r->src_base[i]);
+  if (bits & 15) return fail(UGC_ERR_UNSUPPORTED, "pooled lookup needs 16-byte aligned tables and output");
+  if (c->cfg.num_device > 1 && !r->attached)
+    return fail(UGC_ERR_STATE, "replica %d reads from peers: call ugc_attach_peers first", r->id);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  UGC_CUDA(cudaSetDevice(r->device));
+  // counted before the launch, like every lookup: a refresh waits for it before it reuses slots
+  __atomic_fetch_add(&r->lookups, 1, __ATOMIC_SEQ_CST);
+  PoolParams p{};
+  for (int i = 0; i < kMaxLocation; i++) p.src_base[i] = r->src_base[i];
+  p.out = out;
+  p.table = r->table;
+  p.counters = r->counters;
+  p.offsets = reinterpret_cast<const long long*>(offsets);
+  p.n_keys = (uint32_t)n_keys;
+  p.n_bags = (uint32_t)n_bags;
+  p.bag_size = (uint32_t)bag_size;
+  p.row_bytes = row_bytes;
+  p.dim = row_bytes / elem;
+  p.local_loc = (uint32_t)r->id;
+  p.host_loc = (uint32_t)c->cfg.num_device;
+  p.host_mask = host_mask_value(c->cfg.empty_feat);
+  p.mean = mode == UGC_POOL_MEAN ? 1u : 0u;
+  UGC_CUDA(launch_lookup_pool(keys, key_bytes, p, elem_type == UGC_ELEM_F16, r->sm_count * 8, s));
+  r->kernel_launches += 1;
+  r->lookups_pooled++;
+  remember_stream(r, s);
+  return UGC_OK;
 }
 
 int ugc_reserve_batch(ugc_ctx* c, int replica_id, uint32_t max_batch) {
@@ -1867,6 +1920,21 @@ int ugc_refresh_evict(ugc_ctx* c, int replica_id, void* stream) {
     return refuse(fail(UGC_ERR_CAPACITY, "refresh needs %llu free slots, %llu available",
                        (unsigned long long)n_insert, (unsigned long long)(r->free_count + n_evict)));
 
+  // Keys that leave their source for a peer that holds the row ALREADY (rows leaving the
+  // replicated set, typically the hottest keys a refresh moves) are re-pointed to that peer
+  // in place instead of being removed now and attached three phases later: between those two
+  // moments every lookup of such a key would go to the host table (measured at 2 GPUs on the
+  // 400 M x 64 configuration: 41 % of a batch, 5.2 ms per lookup against 1.1 ms).  The attach
+  // phase finds these entries in place and leaves them.  The reference removes first and
+  // inserts after its fill (coll_cache_lib/cache_context.cu:3103-3136, :4086-4100).
+  RepointParams rp{};
+  rp.own = r->table;
+  for (int p2 = 0; p2 < G; p2++)
+    if (p2 != me && r->peer_known[p2] && r->src_base[p2] && r->early_repoint) rp.peer[p2] = r->peer_table[p2];
+  rp.n2b_new = r->n2b_next;
+  rp.acc_new = static_cast<const uint8_t*>(r->acc_dev.ptr) + (size_t)c->cur.num_block;
+  rp.me = (uint32_t)me;
+  rp.num_device = (uint32_t)G;
   // step 3: evicted rows give their slots back (written by the resolve kernel straight to the
   // tail of the free ring; the slot numbers never visit the host), then leave the table
   if (n_evict) {
@@ -1874,13 +1942,13 @@ int ugc_refresh_evict(ugc_ctx* c, int replica_id, void* stream) {
                         (uint32_t)r->capacity};
     UGC_CUDA(launch_table_resolve(r->table, list_ptr(r, kListEvict), (uint32_t)n_evict, (uint32_t)me, tail,
                                   r->counters, s));
-    UGC_CUDA(launch_table_evict(r->table, list_ptr(r, kListEvict), (uint32_t)n_evict, r->counters, s));
+    UGC_CUDA(launch_table_repoint(rp, list_ptr(r, kListEvict), (uint32_t)n_evict, r->counters, s));
     UGC_TRY(check_table_errors(r, s, "refresh evict"));
     r->free_count += n_evict;
   }
   // step 4: remote entries whose source changed (coll_cache_lib/cache_context.cu:3103-3136)
   if (n_drop) {
-    UGC_CUDA(launch_table_evict(r->table, list_ptr(r, kListDropRemote), (uint32_t)n_drop, r->counters, s));
+    UGC_CUDA(launch_table_repoint(rp, list_ptr(r, kListDropRemote), (uint32_t)n_drop, r->counters, s));
     UGC_TRY(check_table_errors(r, s, "refresh evict remote"));
   }
   // Grace period.  A lookup that was enqueued before the evictions above completed may hold a
@@ -2066,6 +2134,8 @@ int ugc_stats(ugc_ctx* c, int replica_id, ugc_stats_t* out) {
   out->lookups_host_ordered = r->lookups_host_ordered;
   out->lookups_direct = r->lookups_direct;
   out->kernel_launches = r->kernel_launches;
+  out->lookups_pooled = r->lookups_pooled;
+  for (int g = 0; g < kNumGroup; g++) out->pool_rows[g] = h.pool_rows[g];
   return UGC_OK;
 }
 
@@ -2089,12 +2159,14 @@ int ugc_get_tuning(ugc_ctx* c, int replica_id, ugc_tuning* out) {
   out->direct_block_threads = r->direct_block;
   out->host_zero_copy = r->host_zero_copy;
   out->gather_dynamic = r->gather_dynamic;
+  out->split_fixed = r->split_fixed;
   out->direct_tile_keys = r->direct_tile_shift ? (1 << r->direct_tile_shift) : 0;
   out->direct_deep = r->direct_deep;
   out->host_order_min_rows = r->host_order_min_rows;
   out->refresh_fill_ctas = r->refresh_fill_ctas;
   out->refresh_fill_batch_rows = r->refresh_fill_batch_rows;
   out->refresh_fill_pause_us = r->refresh_fill_pause_us;
+  out->refresh_early_repoint = r->early_repoint;
   return UGC_OK;
 }
 
@@ -2124,12 +2196,14 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   r->direct_block = t->direct_block_threads;
   r->host_zero_copy = t->host_zero_copy;
   r->gather_dynamic = t->gather_dynamic ? 1 : 0;
+  r->split_fixed = t->split_fixed ? 1 : 0;
   r->direct_tile_shift = t->direct_tile_keys == 8 ? 3 : t->direct_tile_keys == 16 ? 4 : t->direct_tile_keys == 32 ? 5 : 0;
   r->direct_deep = t->direct_deep ? 1 : 0;
   r->host_order_min_rows = t->host_order_min_rows < 0 ? 0 : t->host_order_min_rows;
   if (t->refresh_fill_ctas > 0) r->refresh_fill_ctas = t->refresh_fill_ctas;
   if (t->refresh_fill_batch_rows > 0) r->refresh_fill_batch_rows = t->refresh_fill_batch_rows;
   r->refresh_fill_pause_us = t->refresh_fill_pause_us < 0 ? 0 : t->refresh_fill_pause_us;
+  r->early_repoint = t->refresh_early_repoint ? 1 : 0;
   return UGC_OK;
 }
 

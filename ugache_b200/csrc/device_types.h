@@ -75,6 +75,8 @@ struct Counters {
   // launch adds to its slot and clears the other one (whose launch is complete by then)
   uint32_t dcount[2][kNumGroup];
   uint32_t reserved3[2];
+  // pooled lookups: rows summed so far, per source group (cumulative)
+  unsigned long long pool_rows[kNumGroup];
 };
 
 // Written by the last CTA of every extraction into pinned host memory: the host reads it
@@ -97,6 +99,7 @@ struct GatherParams {
   int remote_cta_cap;   // most CTAs of the peer group: what keeps the NVLink port full
   int host_cta_cap;     // most CTAs of the host group: what keeps the host link full
   int rows_per_cta_min; // do not give a group more CTAs than count / this
+  int fixed_split;      // 1: the two caps ARE the CTA counts of their groups (for sweeps)
   // Seconds per byte over each group's link, scaled by any common factor (local counts twice:
   // row read and row write both use HBM).  The CTAs of a launch are shared out in proportion
   // to rows * row_bytes * t_byte of the groups, within the caps above.
@@ -106,6 +109,25 @@ struct GatherParams {
                         //    takes chunks of the other groups' lists.  0: fixed striding.
   int pdl;              // launched with programmatic stream serialization
   int bulk_mask;        // bit 0: host rows, bit 1: peer rows go through bulk-async staging
+};
+
+// Everything the pooled lookup (table probe, row fetch and per-bag sum in one kernel) needs.
+struct PoolParams {
+  const void* src_base[kMaxLocation];
+  float* out;                // [n_bags, dim] fp32
+  TableView table;
+  Counters* counters;
+  const long long* offsets;  // n_bags + 1 entries (device), or nullptr: bags of bag_size keys
+  uint32_t n_keys;
+  uint32_t n_bags;
+  uint32_t bag_size;
+  uint32_t row_bytes;
+  uint32_t dim;              // elements per row
+  uint32_t local_loc;
+  uint32_t host_loc;
+  uint32_t host_mask;
+  uint32_t lpr_shift;        // log2 of the lanes that share one bag
+  uint32_t mean;             // 1: the sum is divided by the bag's length
 };
 
 // Everything the direct extraction (lookup and row copy in one kernel, no index lists) needs.
@@ -150,6 +172,18 @@ __host__ __device__ inline uint32_t slot_pos(const SlotView& v, uint32_t j) {
 //                                kListAttach0+s  = read from peer s now, not before
 constexpr int kListEvict = 0, kListInsert = 1, kListDropRemote = 2, kListAttach0 = 3;
 constexpr int kMaxClassLists = kListAttach0 + kMaxDevice;  // 11
+// Refresh: keys leaving their present source.  A key whose new source is a peer that holds the
+// row already gets its entry re-pointed to that peer in place (no interval in which lookups
+// would fetch it from the host); every other key's entry is removed.
+struct RepointParams {
+  TableView own;
+  TableView peer[kMaxDevice];  // num_keys == 0: that peer's table is not known here
+  const uint32_t* n2b_new;     // device, N entries
+  const uint8_t* acc_new;      // device: this reader's source per block (new placement)
+  uint32_t me;
+  uint32_t num_device;
+};
+
 struct ClassifyParams {
   const uint32_t* n2b_old;   // device, N entries, or nullptr
   const uint32_t* n2b_new;   // device, N entries

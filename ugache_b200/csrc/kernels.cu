@@ -3,6 +3,8 @@
 // is not a multiple of 16).
 #include "kernels.cuh"
 
+#include <cuda_fp16.h>
+
 #include <algorithm>
 #include <cstring>
 
@@ -377,6 +379,10 @@ __device__ __forceinline__ void split_roles(const GatherParams& p, const uint32_
   };
   n_host = share(t_host, cnt[kGroupHost], p.host_cta_cap);
   n_remote = share(t_rem, cnt[kGroupRemote], p.remote_cta_cap);
+  if (p.fixed_split) {
+    n_host = cnt[kGroupHost] ? max(p.host_cta_cap, 1) : 0;
+    n_remote = cnt[kGroupRemote] ? max(p.remote_cta_cap, 1) : 0;
+  }
   const int avail = grid - (cnt[kGroupLocal] ? 1 : 0);
   while (n_host + n_remote > avail) {  // small grids only
     if (n_remote >= n_host && n_remote > 1) {
@@ -976,6 +982,152 @@ __global__ void __launch_bounds__(kBlock, DEEP ? 3 : 4)
   }
 }
 
+// ------------------------------------------------------------------------------------
+// pooled lookup: table probe, row fetch and per-bag sum in ONE kernel
+// ------------------------------------------------------------------------------------
+// A bag is a run of consecutive keys; its result is the sum (or mean) of its rows, one fp32
+// vector of `dim` elements.  The looked-up rows never reach memory: a group of lanes (as many
+// as a row has 16-byte pieces, at most 32) owns a bag, each lane probes the table for one key of
+// the bag, the row addresses travel by shuffle inside the group, and every lane adds up its
+// own 16-byte column of the rows.  The additions of one output element happen in key order,
+// in fp32, starting from +0, one rounding each (no fused multiply-add is involved), so the
+// result is bit-for-bit what a sequential fp32 loop over the bag gives on any machine.
+// Keys outside [0, num_keys) are counted and contribute nothing.  The reference leaves pooling
+// to the model that consumes the rows; this is the fused form of lookup + segment sum.
+template <bool F16>
+__device__ __forceinline__ void pool_add(float* acc, const Vec<16>& v) {
+  if (F16) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float2 f = __half22float2(h[i]);
+      acc[2 * i] = __fadd_rn(acc[2 * i], f.x);
+      acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], f.y);
+    }
+  } else {
+    const float* f = reinterpret_cast<const float*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) acc[i] = __fadd_rn(acc[i], f[i]);
+  }
+}
+
+template <typename KeyT, bool F16>
+__global__ void __launch_bounds__(kBlock) lookup_pool_kernel(const KeyT* __restrict__ keys, PoolParams p) {
+  constexpr int NF = F16 ? 8 : 4;  // elements per 16-byte piece of a row
+  constexpr int UNROLL = 8;        // rows in flight per lane
+  __shared__ const char* s_src[kMaxLocation];
+  if (threadIdx.x < kMaxLocation) s_src[threadIdx.x] = static_cast<const char*>(p.src_base[threadIdx.x]);
+  __syncthreads();
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t lpr = 1u << p.lpr_shift;
+  const uint32_t sub = lane & (lpr - 1);
+  const uint32_t gbase = lane & ~(lpr - 1);
+  const unsigned gmask = lpr == 32 ? kFull : (((1u << lpr) - 1u) << gbase);
+  const uint32_t workers_per_cta = blockDim.x >> p.lpr_shift;
+  const uint32_t n_workers = gridDim.x * workers_per_cta;
+  const uint32_t vecs = p.row_bytes / 16;
+  uint32_t bad = 0, n_local = 0, n_remote = 0, n_host = 0;
+
+  for (uint32_t bag = blockIdx.x * workers_per_cta + (threadIdx.x >> p.lpr_shift); bag < p.n_bags;
+       bag += n_workers) {
+    long long b0, b1;
+    if (p.offsets) {
+      b0 = p.offsets[bag];
+      b1 = p.offsets[bag + 1];
+    } else {
+      b0 = (long long)bag * p.bag_size;
+      b1 = b0 + p.bag_size;
+    }
+    b0 = min(max(b0, 0ll), (long long)p.n_keys);
+    b1 = min(max(b1, b0), (long long)p.n_keys);
+    const uint32_t len = (uint32_t)(b1 - b0);
+    // rows wider than 32 pieces take several passes over the bag, one per 32 pieces
+    for (uint32_t c0 = 0; c0 < vecs; c0 += lpr) {
+      const uint32_t c = c0 + sub;
+      const bool has = c < vecs;
+      float acc[NF];
+#pragma unroll
+      for (int i = 0; i < NF; i++) acc[i] = 0.f;
+      for (uint32_t k0 = 0; k0 < len; k0 += lpr) {
+        // this lane's key of the bag: source address of its row
+        const uint32_t idx = k0 + sub;
+        bool valid = idx < len;
+        unsigned long long k = valid ? (unsigned long long)keys[b0 + idx] : 0ull;
+        if (k >= p.table.num_keys) {  // also catches negative int64 ids
+          if (valid && c0 == 0) bad++;
+          valid = false;
+        }
+        const char* src = nullptr;
+        if (valid) {
+          const uint32_t w = table_lookup(p.table, (uint32_t)k);
+          uint32_t loc, off;
+          if (w == kEmptyWord) {
+            loc = p.host_loc;
+            off = (uint32_t)k & p.host_mask;
+            if (c0 == 0) n_host++;
+          } else {
+            loc = word_loc(w);
+            off = word_off(w);
+            if (c0 == 0) {
+              if (loc == p.local_loc) {
+                n_local++;
+              } else {
+                n_remote++;
+              }
+            }
+          }
+          src = s_src[loc] + (size_t)off * p.row_bytes;
+        }
+        const unsigned long long src_bits = reinterpret_cast<unsigned long long>(src);
+        const uint32_t cnt = min(lpr, len - k0);
+        for (uint32_t j = 0; j < cnt; j += UNROLL) {
+          Vec<16> v[UNROLL];
+          bool ok[UNROLL];
+#pragma unroll
+          for (int u = 0; u < UNROLL; u++) {
+            const unsigned long long a = __shfl_sync(gmask, src_bits, gbase + ((j + u) & (lpr - 1)));
+            ok[u] = has && j + u < cnt && a != 0ull;
+            if (ok[u]) ld_row(v[u], reinterpret_cast<const char*>(a) + (size_t)c * 16);
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; u++)
+            if (ok[u]) pool_add<F16>(acc, v[u]);
+        }
+      }
+      if (has) {
+        if (p.mean && len > 0) {
+          const float d = (float)len;
+#pragma unroll
+          for (int i = 0; i < NF; i++) acc[i] = __fdiv_rn(acc[i], d);
+        }
+        float4* dst = reinterpret_cast<float4*>(p.out + (size_t)bag * p.dim + (size_t)c * NF);
+        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        if (F16) dst[1] = make_float4(acc[NF - 4], acc[NF - 3], acc[NF - 2], acc[NF - 1]);
+      }
+    }
+  }
+  // counts: one global atomic per CTA and counter (an atomic per thread on one address would
+  // take longer than the kernel's memory traffic)
+  __shared__ uint32_t s_cnt[kNumGroup + 1];
+  if (threadIdx.x <= kNumGroup) s_cnt[threadIdx.x] = 0;
+  __syncthreads();
+  n_local = __reduce_add_sync(kFull, n_local);
+  n_remote = __reduce_add_sync(kFull, n_remote);
+  n_host = __reduce_add_sync(kFull, n_host);
+  bad = __reduce_add_sync(kFull, bad);
+  if (lane == 0) {
+    if (n_local) atomicAdd(&s_cnt[kGroupLocal], n_local);
+    if (n_remote) atomicAdd(&s_cnt[kGroupRemote], n_remote);
+    if (n_host) atomicAdd(&s_cnt[kGroupHost], n_host);
+    if (bad) atomicAdd(&s_cnt[kNumGroup], bad);
+  }
+  __syncthreads();
+  if (threadIdx.x < kNumGroup && s_cnt[threadIdx.x])
+    atomicAdd(&p.counters->pool_rows[threadIdx.x], (unsigned long long)s_cnt[threadIdx.x]);
+  if (threadIdx.x == kNumGroup && s_cnt[kNumGroup])
+    atomicAdd(&p.counters->err_key_range, (unsigned long long)s_cnt[kNumGroup]);
+}
+
 template <int VEC, int LPR, int UNROLL>
 __global__ void __launch_bounds__(kBlock) fill_scatter_kernel(KeySlotIndex ix, uint32_t n) {
   const uint32_t vecs_per_row = ix.row_bytes / VEC;
@@ -1020,7 +1172,7 @@ __device__ __forceinline__ bool insert_hashed(const TableView& t, uint32_t key, 
 
 __global__ void __launch_bounds__(kBlock)
     table_insert_kernel(TableView t, const uint32_t* __restrict__ keys, SlotView offs, uint32_t loc,
-                        uint32_t n, Counters* counters) {
+                        uint32_t n, Counters* counters, bool allow_same) {
   uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   uint32_t key = keys[i];
@@ -1029,9 +1181,62 @@ __global__ void __launch_bounds__(kBlock)
   if (key >= t.num_keys) {
     ok = false;
   } else if (t.kind == kTableFlat) {
-    ok = atomicExch(t.flat + key, word) == kEmptyWord;
+    const uint32_t old = atomicExch(t.flat + key, word);
+    ok = old == kEmptyWord || (allow_same && old == word);
+  } else if (allow_same) {
+    // The key may be live further along its probe sequence than the first free slot: look
+    // for it before a slot is claimed, or it would end up in the table twice.
+    const uint32_t w = table_lookup(t, key);
+    ok = w == word || (w == kEmptyWord && insert_hashed(t, key, word));
   } else {
     ok = insert_hashed(t, key, word);
+  }
+  if (!ok) atomicAdd(&counters->err_table, 1ull);
+}
+
+// Refresh: every key of the list leaves its present source.  If its new source is a peer whose
+// table shows the row there already, the entry's word is replaced in place by (peer, slot) --
+// one 32-bit store, so a concurrent lookup sees the old or the new source, both valid until the
+// grace period ends; otherwise the entry is removed (the key is served by the host until a later
+// phase of the refresh inserts it again).
+__global__ void __launch_bounds__(kBlock)
+    table_repoint_kernel(RepointParams p, const uint32_t* __restrict__ keys, uint32_t n, Counters* counters) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t key = keys[i];
+  const TableView& t = p.own;
+  bool ok = false;
+  if (key < t.num_keys) {
+    uint32_t word_new = kEmptyWord;
+    const uint32_t src_new = p.acc_new[p.n2b_new[key]];
+    if (src_new < p.num_device && src_new != p.me && p.peer[src_new].num_keys) {
+      const uint32_t w = table_lookup(p.peer[src_new], key);
+      if (w != kEmptyWord && word_loc(w) == src_new) word_new = w;
+    }
+    if (t.kind == kTableFlat) {
+      ok = atomicExch(t.flat + key, word_new) != kEmptyWord;
+    } else {
+      uint32_t line = murmur3_32(key) & t.line_mask;
+      for (uint32_t step = 0; step <= t.line_mask && !ok; step++) {
+        Line l = ld_line(t.slots, line);
+        bool stop = false;
+#pragma unroll
+        for (int s = 0; s < kSlotsPerLine; s++) {
+          if (l.key[s] == key && !ok) {
+            uint2* slot = &t.slots[(size_t)line * kSlotsPerLine + s];
+            if (word_new == kEmptyWord) {
+              atomicOr(&slot->x, kTombstone);
+            } else {
+              atomicExch(&slot->y, word_new);
+            }
+            ok = true;
+          }
+          stop |= (l.key[s] == kEmptyWord);
+        }
+        if (stop) break;
+        line = (line + 1) & t.line_mask;
+      }
+    }
   }
   if (!ok) atomicAdd(&counters->err_table, 1ull);
 }
@@ -1441,6 +1646,32 @@ cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectP
 #undef UGC_LAUNCH_DIRECT
 }
 
+cudaError_t launch_lookup_pool(const void* keys, int key_bytes, const PoolParams& p_in, bool f16,
+                               int max_ctas, cudaStream_t stream) {
+  if (p_in.n_bags == 0) return cudaSuccess;
+  PoolParams p = p_in;
+  const int lpr = lanes_per_row(p.row_bytes, 16);
+  p.lpr_shift = 0;
+  while ((1 << p.lpr_shift) < lpr) p.lpr_shift++;
+  const uint32_t bags_per_cta = (uint32_t)kBlock >> p.lpr_shift;
+  const int grid = (int)std::max<uint32_t>(1, std::min<uint32_t>((uint32_t)max_ctas,
+                                                                 (p.n_bags + bags_per_cta - 1) / bags_per_cta));
+  if (key_bytes == 8) {
+    if (f16) {
+      lookup_pool_kernel<long long, true><<<grid, kBlock, 0, stream>>>(static_cast<const long long*>(keys), p);
+    } else {
+      lookup_pool_kernel<long long, false><<<grid, kBlock, 0, stream>>>(static_cast<const long long*>(keys), p);
+    }
+  } else {
+    if (f16) {
+      lookup_pool_kernel<uint32_t, true><<<grid, kBlock, 0, stream>>>(static_cast<const uint32_t*>(keys), p);
+    } else {
+      lookup_pool_kernel<uint32_t, false><<<grid, kBlock, 0, stream>>>(static_cast<const uint32_t*>(keys), p);
+    }
+  }
+  return cudaGetLastError();
+}
+
 cudaError_t launch_unique(const void* keys, int key_bytes, uint32_t n, uint64_t num_keys, uint32_t epoch,
                           uint32_t* stamp, void* unique_keys, int32_t* inverse, uint32_t* n_unique,
                           Counters* counters, cudaStream_t stream) {
@@ -1525,9 +1756,17 @@ cudaError_t launch_table_clear(const TableView& t, cudaStream_t stream) {
 }
 
 cudaError_t launch_table_insert(const TableView& t, const uint32_t* keys, const SlotView& offs,
-                                uint32_t loc, uint32_t n, Counters* counters, cudaStream_t stream) {
+                                uint32_t loc, uint32_t n, Counters* counters, cudaStream_t stream,
+                                bool allow_same) {
   if (n == 0) return cudaSuccess;
-  table_insert_kernel<<<grid_for(n), kBlock, 0, stream>>>(t, keys, offs, loc, n, counters);
+  table_insert_kernel<<<grid_for(n), kBlock, 0, stream>>>(t, keys, offs, loc, n, counters, allow_same);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_table_repoint(const RepointParams& p, const uint32_t* keys, uint32_t n,
+                                 Counters* counters, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  table_repoint_kernel<<<grid_for(n), kBlock, 0, stream>>>(p, keys, n, counters);
   return cudaGetLastError();
 }
 

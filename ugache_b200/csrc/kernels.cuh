@@ -37,6 +37,11 @@ cudaError_t launch_unique(const void* keys, int key_bytes, uint32_t n, uint64_t 
                           uint32_t* stamp, void* unique_keys, int32_t* inverse, uint32_t* n_unique,
                           Counters* counters, cudaStream_t stream);
 
+// Pooled lookup: out[b] = sum (or mean) over the keys of bag b of their rows, fp32, added in key
+// order.  Rows must be a multiple of 16 bytes and every source and `out` 16-byte aligned.
+cudaError_t launch_lookup_pool(const void* keys, int key_bytes, const PoolParams& p, bool f16,
+                               int max_ctas, cudaStream_t stream);
+
 // Orders the host list of the lookup just enqueued by address range (counting sort into 256
 // buckets over `host_rows` rows) into `sorted`; `hist` is host_order_scratch_bytes() of scratch.
 // Enqueue between launch_lookup_group and launch_gather_roles and hand `sorted` to the gather.
@@ -65,8 +70,14 @@ cudaError_t launch_iota(uint32_t* dst, uint32_t start, uint32_t n, cudaStream_t 
 
 cudaError_t launch_table_clear(const TableView& t, cudaStream_t stream);
 // word(j) = pack(loc, slot(j)), slot(j) as SlotView describes
+// allow_same: a key that is live already with exactly this word is not an error
 cudaError_t launch_table_insert(const TableView& t, const uint32_t* keys, const SlotView& offs,
-                                uint32_t loc, uint32_t n, Counters* counters, cudaStream_t stream);
+                                uint32_t loc, uint32_t n, Counters* counters, cudaStream_t stream,
+                                bool allow_same = false);
+// Refresh: the keys leave their present source; entries whose new source is a peer that holds
+// the row already are re-pointed in place, the others removed.
+cudaError_t launch_table_repoint(const RepointParams& p, const uint32_t* keys, uint32_t n,
+                                 Counters* counters, cudaStream_t stream);
 cudaError_t launch_table_evict(const TableView& t, const uint32_t* keys, uint32_t n,
                                Counters* counters, cudaStream_t stream);
 cudaError_t launch_table_words(const TableView& t, const uint32_t* keys, uint32_t n,

@@ -223,6 +223,37 @@ class Cache:
                                            C.c_void_p(s)))
         return rows, uniq, inverse, n_unique
 
+    def lookup_pool(self, replica_id, keys, offsets=None, bag_size=0, elem="f32", mode="sum", out=None,
+                    stream=None):
+        """Pooled lookup (embedding bag): ``out[b] = sum / mean of the rows of bag b`` as fp32,
+        added in key order.  keys: CUDA tensor (int64 / int32); offsets: CUDA int64 tensor of
+        ``n_bags + 1`` positions, or None with ``bag_size`` keys per bag.  Returns the
+        ``[n_bags, dim]`` fp32 tensor."""
+        import torch
+        keys = keys.reshape(-1)
+        n = keys.numel()
+        kb = 8 if keys.dtype == torch.int64 else 4
+        dev = keys.device
+        if offsets is not None:
+            if offsets.dtype != torch.int64 or not offsets.is_cuda:
+                raise ValueError("offsets must be a CUDA int64 tensor")
+            offsets = offsets.contiguous()
+            n_bags = offsets.numel() - 1
+        else:
+            if bag_size <= 0:
+                raise ValueError("give offsets or a bag size")
+            n_bags = n // bag_size
+        elem_type = {"f32": 0, "f16": 1}[elem]
+        dim = self.cfg.row_bytes // (2 if elem_type else 4)
+        if out is None:
+            out = torch.empty((max(n_bags, 0), dim), dtype=torch.float32, device=dev)
+        s = torch.cuda.current_stream(dev).cuda_stream if stream is None else stream
+        check(_lib.lib().ugc_lookup_pool(self._h, replica_id, C.c_void_p(keys.data_ptr()), kb, n,
+                                         C.c_void_p(offsets.data_ptr() if offsets is not None else None),
+                                         max(n_bags, 0), bag_size, elem_type, {"sum": 0, "mean": 1}[mode],
+                                         C.c_void_p(out.data_ptr()), C.c_void_p(s)))
+        return out
+
     def reserve_batch(self, replica_id, max_batch):
         check(_lib.lib().ugc_reserve_batch(self._h, replica_id, max_batch))
 
@@ -293,7 +324,9 @@ class Cache:
     def stats(self, replica_id):
         s = _lib.Stats()
         check(_lib.lib().ugc_stats(self._h, replica_id, C.byref(s)))
-        return {name: getattr(s, name) for name, _ in s._fields_}
+        out = {name: getattr(s, name) for name, _ in s._fields_}
+        out["pool_rows"] = [int(x) for x in s.pool_rows]
+        return out
 
     def launches(self, replica_id):
         """Kernels launched by this replica's lookups so far."""
