@@ -65,10 +65,16 @@ def test_pooled_lookup_matches_the_oracle(built_lib, golden_cases, case_name, el
             got = _pool(cache, r, keys, dev, elem, tdt, offsets=offsets, mode=mode)
             want = orc.pool(w.table, keys, offsets=offsets, mean=mode == "mean")
             assert np.array_equal(_bits(got), _bits(want)), (case_name, r, "ragged", mode)
+        # many short ragged bags (a lane group walks through several bags per tile), empty ones among them
+        cuts = np.sort(rng.integers(0, n, n // 3))
+        small = np.concatenate([[0], cuts, [n]]).astype(np.int64)
+        got = _pool(cache, r, keys, dev, elem, tdt, offsets=small, mode="mean")
+        want = orc.pool(w.table, keys, offsets=small, mean=True)
+        assert np.array_equal(_bits(got), _bits(want)), (case_name, r, "short ragged")
         st = cache.stats(r)
-        assert st["lookups_pooled"] - before["lookups_pooled"] == 5
+        assert st["lookups_pooled"] - before["lookups_pooled"] == 6
         rows = [a - b for a, b in zip(st["pool_rows"], before["pool_rows"])]
-        assert sum(rows) == (n // 1) + (n // 4) * 4 + (n // 37) * 37 + 2 * n
+        assert sum(rows) == (n // 1) + (n // 4) * 4 + (n // 37) * 37 + 3 * n
         assert rows[0] > 0 and rows[2] > 0 and (w.G == 1 or rows[1] > 0)
         assert st["err_key_range"] == before["err_key_range"]
     cache.close()

@@ -127,6 +127,7 @@ struct PoolParams {
   uint32_t host_loc;
   uint32_t host_mask;
   uint32_t lpr_shift;        // log2 of the lanes that share one bag
+  uint32_t bags_per_tile;    // consecutive bags one lane group walks through
   uint32_t mean;             // 1: the sum is divided by the bag's length
 };
 

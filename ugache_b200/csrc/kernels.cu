@@ -1011,8 +1011,14 @@ __device__ __forceinline__ void pool_add(float* acc, const Vec<16>& v) {
   }
 }
 
+// Position in `keys` where bag b starts (b == n_bags: where the last one ends), inside [0, n_keys].
+__device__ __forceinline__ uint32_t pool_bag_start(const PoolParams& p, uint32_t b) {
+  const long long o = p.offsets ? p.offsets[b] : (long long)b * p.bag_size;
+  return (uint32_t)min(max(o, 0ll), (long long)p.n_keys);
+}
+
 template <typename KeyT, bool F16>
-__global__ void __launch_bounds__(kBlock) lookup_pool_kernel(const KeyT* __restrict__ keys, PoolParams p) {
+__global__ void __launch_bounds__(kBlock, 3) lookup_pool_kernel(const KeyT* __restrict__ keys, PoolParams p) {
   constexpr int NF = F16 ? 8 : 4;  // elements per 16-byte piece of a row
   constexpr int UNROLL = 8;        // rows in flight per lane
   __shared__ const char* s_src[kMaxLocation];
@@ -1026,33 +1032,53 @@ __global__ void __launch_bounds__(kBlock) lookup_pool_kernel(const KeyT* __restr
   const uint32_t workers_per_cta = blockDim.x >> p.lpr_shift;
   const uint32_t n_workers = gridDim.x * workers_per_cta;
   const uint32_t vecs = p.row_bytes / 16;
+  const uint32_t n_tiles = (p.n_bags + p.bags_per_tile - 1) / p.bags_per_tile;
   uint32_t bad = 0, n_local = 0, n_remote = 0, n_host = 0;
 
-  for (uint32_t bag = blockIdx.x * workers_per_cta + (threadIdx.x >> p.lpr_shift); bag < p.n_bags;
-       bag += n_workers) {
-    long long b0, b1;
-    if (p.offsets) {
-      b0 = p.offsets[bag];
-      b1 = p.offsets[bag + 1];
-    } else {
-      b0 = (long long)bag * p.bag_size;
-      b1 = b0 + p.bag_size;
-    }
-    b0 = min(max(b0, 0ll), (long long)p.n_keys);
-    b1 = min(max(b1, b0), (long long)p.n_keys);
-    const uint32_t len = (uint32_t)(b1 - b0);
-    // rows wider than 32 pieces take several passes over the bag, one per 32 pieces
+  // A lane group owns a tile of consecutive bags (several when bags are shorter than the group
+  // is wide, so that every lane has a key to probe) and walks the tile's keys in order: probe
+  // `lpr` keys, fetch their rows UNROLL at a time, add them up in key order, and write a bag out
+  // whenever the walk crosses into the next one.
+  for (uint32_t tile = blockIdx.x * workers_per_cta + (threadIdx.x >> p.lpr_shift); tile < n_tiles;
+       tile += n_workers) {
+    const uint32_t bag_lo = tile * p.bags_per_tile;
+    const uint32_t bag_hi = min(bag_lo + p.bags_per_tile, p.n_bags);
+    const uint32_t k_lo = pool_bag_start(p, bag_lo);
+    const uint32_t k_hi = max(k_lo, pool_bag_start(p, bag_hi));
+    // rows wider than 32 pieces take several passes over the tile, one per 32 pieces
     for (uint32_t c0 = 0; c0 < vecs; c0 += lpr) {
       const uint32_t c = c0 + sub;
       const bool has = c < vecs;
       float acc[NF];
 #pragma unroll
       for (int i = 0; i < NF; i++) acc[i] = 0.f;
-      for (uint32_t k0 = 0; k0 < len; k0 += lpr) {
-        // this lane's key of the bag: source address of its row
+      uint32_t bag = bag_lo;
+      uint32_t bag_begin = k_lo;
+      uint32_t bag_end = max(bag_begin, min(pool_bag_start(p, bag + 1), k_hi));
+      // writes bag `bag` out and moves on to the next one of the tile
+      auto flush = [&]() {
+        if (has) {
+          const uint32_t len = bag_end - bag_begin;
+          if (p.mean && len > 0) {
+            const float d = (float)len;
+#pragma unroll
+            for (int i = 0; i < NF; i++) acc[i] = __fdiv_rn(acc[i], d);
+          }
+          float4* dst = reinterpret_cast<float4*>(p.out + (size_t)bag * p.dim + (size_t)c * NF);
+          dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+          if (F16) dst[1] = make_float4(acc[NF - 4], acc[NF - 3], acc[NF - 2], acc[NF - 1]);
+        }
+#pragma unroll
+        for (int i = 0; i < NF; i++) acc[i] = 0.f;
+        bag++;
+        bag_begin = bag_end;
+        if (bag < bag_hi) bag_end = max(bag_begin, min(pool_bag_start(p, bag + 1), k_hi));
+      };
+      for (uint32_t k0 = k_lo; k0 < k_hi; k0 += lpr) {
+        // this lane's key: source address of its row
         const uint32_t idx = k0 + sub;
-        bool valid = idx < len;
-        unsigned long long k = valid ? (unsigned long long)keys[b0 + idx] : 0ull;
+        bool valid = idx < k_hi;
+        unsigned long long k = valid ? (unsigned long long)keys[idx] : 0ull;
         if (k >= p.table.num_keys) {  // also catches negative int64 ids
           if (valid && c0 == 0) bad++;
           valid = false;
@@ -1079,7 +1105,7 @@ __global__ void __launch_bounds__(kBlock) lookup_pool_kernel(const KeyT* __restr
           src = s_src[loc] + (size_t)off * p.row_bytes;
         }
         const unsigned long long src_bits = reinterpret_cast<unsigned long long>(src);
-        const uint32_t cnt = min(lpr, len - k0);
+        const uint32_t cnt = min(lpr, k_hi - k0);
         for (uint32_t j = 0; j < cnt; j += UNROLL) {
           Vec<16> v[UNROLL];
           bool ok[UNROLL];
@@ -1090,20 +1116,15 @@ __global__ void __launch_bounds__(kBlock) lookup_pool_kernel(const KeyT* __restr
             if (ok[u]) ld_row(v[u], reinterpret_cast<const char*>(a) + (size_t)c * 16);
           }
 #pragma unroll
-          for (int u = 0; u < UNROLL; u++)
-            if (ok[u]) pool_add<F16>(acc, v[u]);
+          for (int u = 0; u < UNROLL; u++) {
+            if (j + u < cnt) {
+              while (k0 + j + u >= bag_end && bag < bag_hi) flush();  // also passes empty bags
+              if (ok[u]) pool_add<F16>(acc, v[u]);
+            }
+          }
         }
       }
-      if (has) {
-        if (p.mean && len > 0) {
-          const float d = (float)len;
-#pragma unroll
-          for (int i = 0; i < NF; i++) acc[i] = __fdiv_rn(acc[i], d);
-        }
-        float4* dst = reinterpret_cast<float4*>(p.out + (size_t)bag * p.dim + (size_t)c * NF);
-        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        if (F16) dst[1] = make_float4(acc[NF - 4], acc[NF - 3], acc[NF - 2], acc[NF - 1]);
-      }
+      while (bag < bag_hi) flush();  // the last bag of the tile, and empty ones after it
     }
   }
   // counts: one global atomic per CTA and counter (an atomic per thread on one address would
@@ -1653,9 +1674,13 @@ cudaError_t launch_lookup_pool(const void* keys, int key_bytes, const PoolParams
   const int lpr = lanes_per_row(p.row_bytes, 16);
   p.lpr_shift = 0;
   while ((1 << p.lpr_shift) < lpr) p.lpr_shift++;
-  const uint32_t bags_per_cta = (uint32_t)kBlock >> p.lpr_shift;
+  // bags per lane group: as many as it takes to give every lane of the group a key to probe
+  const uint64_t avg_bag = std::max<uint64_t>(1, p.offsets ? (uint64_t)p.n_keys / p.n_bags : p.bag_size);
+  p.bags_per_tile = (uint32_t)std::max<uint64_t>(1, (uint64_t)lpr / avg_bag);
+  const uint32_t n_tiles = (p.n_bags + p.bags_per_tile - 1) / p.bags_per_tile;
+  const uint32_t tiles_per_cta = (uint32_t)kBlock >> p.lpr_shift;
   const int grid = (int)std::max<uint32_t>(1, std::min<uint32_t>((uint32_t)max_ctas,
-                                                                 (p.n_bags + bags_per_cta - 1) / bags_per_cta));
+                                                                 (n_tiles + tiles_per_cta - 1) / tiles_per_cta));
   if (key_bytes == 8) {
     if (f16) {
       lookup_pool_kernel<long long, true><<<grid, kBlock, 0, stream>>>(static_cast<const long long*>(keys), p);
