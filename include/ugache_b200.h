@@ -435,14 +435,18 @@ typedef struct {
   int32_t refresh_fill_ctas;      /* refresh-time fill: CTAs per launch (20, as the reference,
                                      coll_cache_lib/cache_context.cu:4067), rows per launch    */
   int32_t refresh_fill_batch_rows; /* (131,072) and a host-side pause between launches in us    */
-  int32_t refresh_fill_pause_us;  /* (0).  The fill shares the host link and the host's row rate
-                                     with the lookups' host rows: a pause trades refresh time
-                                     for flatter lookup times while it runs (the reference
-                                     sleeps 3 ms between 4092-row batches, :4061-4070)       */
+  int32_t refresh_fill_pause_us;  /* (0).  The reference sleeps 3 ms between 4092-row batches
+                                     (:4061-4070) to keep the fill out of the lookups' way; on
+                                     the B200 machines measured neither a pause nor a smaller
+                                     grid changed the lookup times during a refresh          */
   int32_t refresh_early_repoint;  /* refresh: 1 (default) = a key whose new source is a peer that
                                      holds the row already is re-pointed to it in place in the
                                      evict phase; 0 = removed there and attached in the attach
                                      phase, served by the host in between (the reference's order) */
+  int32_t pool_vec_bytes;         /* ugc_lookup_pool: bytes of a row one lane adds up, 16 or 4;
+                                     0 (default) = 16 unless the batch has so few bags (fewer
+                                     than two warps' worth per SM) that 4, with four times the
+                                     lane groups per bag, fills the GPU better                */
   int32_t gather_dynamic;         /* grouped gather: 1 = lists are handed out in chunks and a
                                      CTA whose own list is drained takes chunks of the other
                                      groups' lists; 0 = fixed striding inside each group     */

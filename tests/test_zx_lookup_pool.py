@@ -36,8 +36,8 @@ CASES = [
 
 
 @pytest.mark.parametrize("case_name,elem", CASES)
-@pytest.mark.parametrize("key_dtype", ["int64", "int32"])
-def test_pooled_lookup_matches_the_oracle(built_lib, golden_cases, case_name, elem, key_dtype):
+@pytest.mark.parametrize("key_dtype,piece", [("int64", 0), ("int32", 16), ("int64", 4)])
+def test_pooled_lookup_matches_the_oracle(built_lib, golden_cases, case_name, elem, key_dtype, piece):
     from tests.test_gpu_parity import make_cache
     case = next(c for c in golden_cases if c["name"] == case_name)
     w = case_workload(case)
@@ -48,6 +48,7 @@ def test_pooled_lookup_matches_the_oracle(built_lib, golden_cases, case_name, el
     rng = np.random.default_rng(7)
     for r in range(min(w.G, 3)):
         dev = torch.device("cuda", r % ndev)
+        cache.tune(r, pool_vec_bytes=piece)       # 16- or 4-byte pieces per lane, or the launcher's choice
         keys = w.keys(rank=r)
         n = len(keys)
         before = cache.stats(r)
@@ -103,11 +104,14 @@ def test_pooled_lookup_row_shapes(built_lib, dim, dtype):
     elem = "f16" if dt == np.float16 else "f32"
     keys = wl.zipf_keys(5, 20000, N, 1.1)
     keys[17], keys[4000], keys[19999] = -1, N, N + 12345
-    for bag, mode in ((8, "sum"), (50, "mean")):
-        got = _pool(cache, 1, keys, dev, elem, bag_size=bag, mode=mode)
-        want = orc.pool(table, keys, bag_size=bag, mean=mode == "mean")
-        assert np.array_equal(_bits(got), _bits(want)), (dim, dtype, bag, mode)
-    assert cache.stats(1)["err_key_range"] == 6
+    for piece in (16, 4):
+        cache.tune(1, pool_vec_bytes=piece)
+        for bag, mode in ((8, "sum"), (50, "mean")):
+            got = _pool(cache, 1, keys, dev, elem, bag_size=bag, mode=mode)
+            want = orc.pool(table, keys, bag_size=bag, mean=mode == "mean")
+            assert np.array_equal(_bits(got), _bits(want)), (dim, dtype, bag, mode, piece)
+    assert cache.stats(1)["err_key_range"] == 12
+    cache.tune(1, pool_vec_bytes=0)
     # the sum of bags of one key is the widened row itself
     got = _pool(cache, 1, keys[:1000], dev, elem, bag_size=1)
     ok = (keys[:1000] >= 0) & (keys[:1000] < N)

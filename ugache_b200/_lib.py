@@ -110,6 +110,7 @@ class Tuning(C.Structure):
         ("refresh_fill_batch_rows", C.c_int32),
         ("refresh_fill_pause_us", C.c_int32),
         ("refresh_early_repoint", C.c_int32),
+        ("pool_vec_bytes", C.c_int32),
         ("gather_dynamic", C.c_int32),
         ("split_fixed", C.c_int32),
         ("host_zero_copy", C.c_int32),

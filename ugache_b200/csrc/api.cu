@@ -551,6 +551,7 @@ struct Replica {
   int gather_dynamic = 1;
   int split_fixed = 0;                     // host_ctas / remote_ctas are counts, not caps
   int early_repoint = 1;                   // refresh: re-point keys to a peer that holds them, in place
+  int pool_vec_bytes = 0;                  // pooled lookup: 0 = chosen per launch, 16 or 4 forced
   cudaStream_t copy_stream = nullptr;      // host-buffer lookups: rows leave on this stream
   std::vector<cudaEvent_t> copy_events;
   uint32_t* stamp = nullptr;               // deduplicated lookups: one stamp per id (first use)
@@ -1774,7 +1775,7 @@ int ugc_lookup_pool(ugc_ctx* c, int replica_id, const void* keys, int key_bytes,
   p.host_loc = (uint32_t)c->cfg.num_device;
   p.host_mask = host_mask_value(c->cfg.empty_feat);
   p.mean = mode == UGC_POOL_MEAN ? 1u : 0u;
-  UGC_CUDA(launch_lookup_pool(keys, key_bytes, p, elem_type == UGC_ELEM_F16, r->sm_count * 8, s));
+  UGC_CUDA(launch_lookup_pool(keys, key_bytes, p, elem_type == UGC_ELEM_F16, r->sm_count * 8, r->pool_vec_bytes, s));
   r->kernel_launches += 1;
   r->lookups_pooled++;
   remember_stream(r, s);
@@ -1999,9 +2000,8 @@ int ugc_refresh_fill(ugc_ctx* c, int replica_id, void* stream) {
       UGC_CUDA(launch_fill_scatter(c->host_dev, r->slice, list_ptr(r, kListInsert) + off, part, (uint32_t)m,
                                    c->cfg.row_bytes, c->cfg.empty_feat, r->refresh_fill_ctas, r->fill_stream));
       if (r->refresh_fill_pause_us > 0 && off + batch < n) {
-        // pacing: the host link and the host's row rate are shared with the lookups' host rows
-        // (and with the other GPUs' fills); the reference sleeps 3 ms between its 4092-row
-        // batches for the same reason (coll_cache_lib/cache_context.cu:4061-4070)
+        // optional pacing, as the reference's 3 ms sleeps between its 4092-row batches
+        // (coll_cache_lib/cache_context.cu:4061-4070); off by default
         UGC_CUDA(cudaStreamSynchronize(r->fill_stream));
         usleep((useconds_t)r->refresh_fill_pause_us);
       }
@@ -2167,6 +2167,7 @@ int ugc_get_tuning(ugc_ctx* c, int replica_id, ugc_tuning* out) {
   out->refresh_fill_batch_rows = r->refresh_fill_batch_rows;
   out->refresh_fill_pause_us = r->refresh_fill_pause_us;
   out->refresh_early_repoint = r->early_repoint;
+  out->pool_vec_bytes = r->pool_vec_bytes;
   return UGC_OK;
 }
 
@@ -2204,6 +2205,7 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   if (t->refresh_fill_batch_rows > 0) r->refresh_fill_batch_rows = t->refresh_fill_batch_rows;
   r->refresh_fill_pause_us = t->refresh_fill_pause_us < 0 ? 0 : t->refresh_fill_pause_us;
   r->early_repoint = t->refresh_early_repoint ? 1 : 0;
+  r->pool_vec_bytes = (t->pool_vec_bytes == 16 || t->pool_vec_bytes == 4) ? t->pool_vec_bytes : 0;
   return UGC_OK;
 }
 

@@ -994,12 +994,12 @@ __global__ void __launch_bounds__(kBlock, DEEP ? 3 : 4)
 // result is bit-for-bit what a sequential fp32 loop over the bag gives on any machine.
 // Keys outside [0, num_keys) are counted and contribute nothing.  The reference leaves pooling
 // to the model that consumes the rows; this is the fused form of lookup + segment sum.
-template <bool F16>
-__device__ __forceinline__ void pool_add(float* acc, const Vec<16>& v) {
+template <bool F16, int VEC>
+__device__ __forceinline__ void pool_add(float* acc, const Vec<VEC>& v) {
   if (F16) {
     const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < VEC / 4; i++) {
       const float2 f = __half22float2(h[i]);
       acc[2 * i] = __fadd_rn(acc[2 * i], f.x);
       acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], f.y);
@@ -1007,7 +1007,7 @@ __device__ __forceinline__ void pool_add(float* acc, const Vec<16>& v) {
   } else {
     const float* f = reinterpret_cast<const float*>(&v);
 #pragma unroll
-    for (int i = 0; i < 4; i++) acc[i] = __fadd_rn(acc[i], f[i]);
+    for (int i = 0; i < VEC / 4; i++) acc[i] = __fadd_rn(acc[i], f[i]);
   }
 }
 
@@ -1017,10 +1017,10 @@ __device__ __forceinline__ uint32_t pool_bag_start(const PoolParams& p, uint32_t
   return (uint32_t)min(max(o, 0ll), (long long)p.n_keys);
 }
 
-template <typename KeyT, bool F16>
+template <typename KeyT, bool F16, int VEC>
 __global__ void __launch_bounds__(kBlock, 3) lookup_pool_kernel(const KeyT* __restrict__ keys, PoolParams p) {
-  constexpr int NF = F16 ? 8 : 4;  // elements per 16-byte piece of a row
-  constexpr int UNROLL = 8;        // rows in flight per lane
+  constexpr int NF = VEC / (F16 ? 2 : 4);  // elements per piece of a row (VEC bytes)
+  constexpr int UNROLL = VEC == 16 ? 8 : 16;  // rows in flight per lane
   __shared__ const char* s_src[kMaxLocation];
   if (threadIdx.x < kMaxLocation) s_src[threadIdx.x] = static_cast<const char*>(p.src_base[threadIdx.x]);
   __syncthreads();
@@ -1031,22 +1031,28 @@ __global__ void __launch_bounds__(kBlock, 3) lookup_pool_kernel(const KeyT* __re
   const unsigned gmask = lpr == 32 ? kFull : (((1u << lpr) - 1u) << gbase);
   const uint32_t workers_per_cta = blockDim.x >> p.lpr_shift;
   const uint32_t n_workers = gridDim.x * workers_per_cta;
-  const uint32_t vecs = p.row_bytes / 16;
+  const uint32_t vecs = p.row_bytes / VEC;
   const uint32_t n_tiles = (p.n_bags + p.bags_per_tile - 1) / p.bags_per_tile;
+  // rows wider than one lane group (32 pieces) are cut into column passes; a pass over a tile
+  // is the unit of work, so that wide rows (or, with 4-byte pieces, every row) spread a bag
+  // over several lane groups
+  const uint32_t n_pass = (vecs + lpr - 1) >> p.lpr_shift;
+  const uint32_t n_items = n_tiles * n_pass;
   uint32_t bad = 0, n_local = 0, n_remote = 0, n_host = 0;
 
   // A lane group owns a tile of consecutive bags (several when bags are shorter than the group
   // is wide, so that every lane has a key to probe) and walks the tile's keys in order: probe
   // `lpr` keys, fetch their rows UNROLL at a time, add them up in key order, and write a bag out
   // whenever the walk crosses into the next one.
-  for (uint32_t tile = blockIdx.x * workers_per_cta + (threadIdx.x >> p.lpr_shift); tile < n_tiles;
-       tile += n_workers) {
+  for (uint32_t item = blockIdx.x * workers_per_cta + (threadIdx.x >> p.lpr_shift); item < n_items;
+       item += n_workers) {
+    const uint32_t tile = item / n_pass;
+    const uint32_t c0 = (item - tile * n_pass) << p.lpr_shift;
     const uint32_t bag_lo = tile * p.bags_per_tile;
     const uint32_t bag_hi = min(bag_lo + p.bags_per_tile, p.n_bags);
     const uint32_t k_lo = pool_bag_start(p, bag_lo);
     const uint32_t k_hi = max(k_lo, pool_bag_start(p, bag_hi));
-    // rows wider than 32 pieces take several passes over the tile, one per 32 pieces
-    for (uint32_t c0 = 0; c0 < vecs; c0 += lpr) {
+    {
       const uint32_t c = c0 + sub;
       const bool has = c < vecs;
       float acc[NF];
@@ -1064,9 +1070,16 @@ __global__ void __launch_bounds__(kBlock, 3) lookup_pool_kernel(const KeyT* __re
 #pragma unroll
             for (int i = 0; i < NF; i++) acc[i] = __fdiv_rn(acc[i], d);
           }
-          float4* dst = reinterpret_cast<float4*>(p.out + (size_t)bag * p.dim + (size_t)c * NF);
-          dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-          if (F16) dst[1] = make_float4(acc[NF - 4], acc[NF - 3], acc[NF - 2], acc[NF - 1]);
+          float* dst = p.out + (size_t)bag * p.dim + (size_t)c * NF;
+          if (NF >= 4) {
+#pragma unroll
+            for (int i = 0; i + 3 < NF; i += 4)
+              reinterpret_cast<float4*>(dst)[i / 4] = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+          } else if (NF == 2) {
+            *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[NF - 1]);
+          } else {
+            dst[0] = acc[0];
+          }
         }
 #pragma unroll
         for (int i = 0; i < NF; i++) acc[i] = 0.f;
@@ -1107,19 +1120,19 @@ __global__ void __launch_bounds__(kBlock, 3) lookup_pool_kernel(const KeyT* __re
         const unsigned long long src_bits = reinterpret_cast<unsigned long long>(src);
         const uint32_t cnt = min(lpr, k_hi - k0);
         for (uint32_t j = 0; j < cnt; j += UNROLL) {
-          Vec<16> v[UNROLL];
+          Vec<VEC> v[UNROLL];
           bool ok[UNROLL];
 #pragma unroll
           for (int u = 0; u < UNROLL; u++) {
             const unsigned long long a = __shfl_sync(gmask, src_bits, gbase + ((j + u) & (lpr - 1)));
             ok[u] = has && j + u < cnt && a != 0ull;
-            if (ok[u]) ld_row(v[u], reinterpret_cast<const char*>(a) + (size_t)c * 16);
+            if (ok[u]) ld_row(v[u], reinterpret_cast<const char*>(a) + (size_t)c * VEC);
           }
 #pragma unroll
           for (int u = 0; u < UNROLL; u++) {
             if (j + u < cnt) {
               while (k0 + j + u >= bag_end && bag < bag_hi) flush();  // also passes empty bags
-              if (ok[u]) pool_add<F16>(acc, v[u]);
+              if (ok[u]) pool_add<F16, VEC>(acc, v[u]);
             }
           }
         }
@@ -1667,33 +1680,61 @@ cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectP
 #undef UGC_LAUNCH_DIRECT
 }
 
-cudaError_t launch_lookup_pool(const void* keys, int key_bytes, const PoolParams& p_in, bool f16,
-                               int max_ctas, cudaStream_t stream) {
-  if (p_in.n_bags == 0) return cudaSuccess;
-  PoolParams p = p_in;
-  const int lpr = lanes_per_row(p.row_bytes, 16);
-  p.lpr_shift = 0;
-  while ((1 << p.lpr_shift) < lpr) p.lpr_shift++;
+namespace {
+// Launch shape of the pooled lookup for pieces of `vec` bytes: lanes per group, bags per tile,
+// and the number of warps the batch fills.
+struct PoolShape {
+  uint32_t lpr_shift, bags_per_tile, warps;
+};
+PoolShape pool_shape(const PoolParams& p, int vec) {
+  PoolShape sh{};
+  const int lpr = lanes_per_row(p.row_bytes, vec);
+  while ((1 << sh.lpr_shift) < lpr) sh.lpr_shift++;
   // bags per lane group: as many as it takes to give every lane of the group a key to probe
   const uint64_t avg_bag = std::max<uint64_t>(1, p.offsets ? (uint64_t)p.n_keys / p.n_bags : p.bag_size);
-  p.bags_per_tile = (uint32_t)std::max<uint64_t>(1, (uint64_t)lpr / avg_bag);
-  const uint32_t n_tiles = (p.n_bags + p.bags_per_tile - 1) / p.bags_per_tile;
-  const uint32_t tiles_per_cta = (uint32_t)kBlock >> p.lpr_shift;
+  sh.bags_per_tile = (uint32_t)std::max<uint64_t>(1, (uint64_t)lpr / avg_bag);
+  const uint64_t n_tiles = ((uint64_t)p.n_bags + sh.bags_per_tile - 1) / sh.bags_per_tile;
+  const uint64_t n_pass = (p.row_bytes / (uint32_t)vec + lpr - 1) / lpr;
+  sh.warps = (uint32_t)std::min<uint64_t>((n_tiles * n_pass * lpr + 31) / 32, 0xffffffffu);
+  return sh;
+}
+}  // namespace
+
+cudaError_t launch_lookup_pool(const void* keys, int key_bytes, const PoolParams& p_in, bool f16,
+                               int max_ctas, int vec_bytes, cudaStream_t stream) {
+  if (p_in.n_bags == 0) return cudaSuccess;
+  PoolParams p = p_in;
+  // 16-byte pieces unless the batch then fills fewer than two warps per SM (few, very long
+  // bags): 4-byte pieces put four times as many lane groups on a bag and keep twice as many
+  // rows in flight per lane, at four times the probes and load instructions (measured on
+  // 212,992 keys of 512-byte rows: bags of 1024 keys 152 against 200 us, bags of 128 keys 51
+  // against 33 us)
+  PoolShape sh = pool_shape(p, 16);
+  int vec = 16;
+  if (vec_bytes == 4 || (vec_bytes != 16 && sh.warps < (uint32_t)max_ctas * (kBlock / 32) / 32)) {
+    vec = 4;
+    sh = pool_shape(p, 4);
+  }
+  p.lpr_shift = sh.lpr_shift;
+  p.bags_per_tile = sh.bags_per_tile;
   const int grid = (int)std::max<uint32_t>(1, std::min<uint32_t>((uint32_t)max_ctas,
-                                                                 (n_tiles + tiles_per_cta - 1) / tiles_per_cta));
+                                                                 (sh.warps + kBlock / 32 - 1) / (kBlock / 32)));
+#define UGC_LAUNCH_POOL(KEYT, F16, VEC) \
+  lookup_pool_kernel<KEYT, F16, VEC><<<grid, kBlock, 0, stream>>>(static_cast<const KEYT*>(keys), p)
   if (key_bytes == 8) {
     if (f16) {
-      lookup_pool_kernel<long long, true><<<grid, kBlock, 0, stream>>>(static_cast<const long long*>(keys), p);
+      if (vec == 16) UGC_LAUNCH_POOL(long long, true, 16); else UGC_LAUNCH_POOL(long long, true, 4);
     } else {
-      lookup_pool_kernel<long long, false><<<grid, kBlock, 0, stream>>>(static_cast<const long long*>(keys), p);
+      if (vec == 16) UGC_LAUNCH_POOL(long long, false, 16); else UGC_LAUNCH_POOL(long long, false, 4);
     }
   } else {
     if (f16) {
-      lookup_pool_kernel<uint32_t, true><<<grid, kBlock, 0, stream>>>(static_cast<const uint32_t*>(keys), p);
+      if (vec == 16) UGC_LAUNCH_POOL(uint32_t, true, 16); else UGC_LAUNCH_POOL(uint32_t, true, 4);
     } else {
-      lookup_pool_kernel<uint32_t, false><<<grid, kBlock, 0, stream>>>(static_cast<const uint32_t*>(keys), p);
+      if (vec == 16) UGC_LAUNCH_POOL(uint32_t, false, 16); else UGC_LAUNCH_POOL(uint32_t, false, 4);
     }
   }
+#undef UGC_LAUNCH_POOL
   return cudaGetLastError();
 }
 

@@ -39,8 +39,10 @@ cudaError_t launch_unique(const void* keys, int key_bytes, uint32_t n, uint64_t 
 
 // Pooled lookup: out[b] = sum (or mean) over the keys of bag b of their rows, fp32, added in key
 // order.  Rows must be a multiple of 16 bytes and every source and `out` 16-byte aligned.
+// vec_bytes: 16 or 4 forces the size of the pieces a lane adds up, anything else lets the
+// launcher choose by how many warps the batch fills.
 cudaError_t launch_lookup_pool(const void* keys, int key_bytes, const PoolParams& p, bool f16,
-                               int max_ctas, cudaStream_t stream);
+                               int max_ctas, int vec_bytes, cudaStream_t stream);
 
 // Orders the host list of the lookup just enqueued by address range (counting sort into 256
 // buckets over `host_rows` rows) into `sorted`; `hist` is host_order_scratch_bytes() of scratch.
