@@ -73,8 +73,9 @@ def parse_args():
     ap.add_argument("--cpu-threads", type=int, default=0,
                     help="threads of the CPU arms; 0 = every core this process may run on")
     ap.add_argument("--tune", default="", help="ugc_tuning fields for the whole run: k=v,k=v")
-    ap.add_argument("--pool-bag", type=int, default=0,
-                    help="also time the pooled lookup with bags of this many consecutive keys")
+    ap.add_argument("--pool-bag", default="",
+                    help="also time the pooled lookup (ugc_lookup_pool: lookup + fp32 sum per bag in one "
+                         "kernel, rows not written) with bags of this many consecutive keys; comma list")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--pdl", type=int, default=-1)
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 30)")
@@ -1039,42 +1040,45 @@ def run_ours(a, job=None):
 
     # ---- optional: the pooled lookup (bags of --pool-bag consecutive keys) on the same batches ----
     pooled = None
-    if a.pool_bag > 0 and a.workload == "dlr":
+    bags = [int(x) for x in str(a.pool_bag).split(",") if x and int(x) > 0]
+    if bags and a.workload == "dlr":
         from oracle import oracle as orc
-        n_bags = a.batch // a.pool_bag
-        pout = torch.empty((n_bags, a.dim), dtype=torch.float32, device=dev)
-        ename = "f32" if elem == 4 else "f16"
-
-        def pstep(i):
-            cache.lookup_pool(rank, keys_dev[i], bag_size=a.pool_bag, elem=ename, out=pout, stream=stream)
-
-        pstep(0)
-        torch.cuda.synchronize()
+        pooled = []
         k0 = keys_np[0]
         if a.empty_feat:
             k0 = k0 & ((1 << a.empty_feat) - 1)
         rows0 = orc.gen_rows_for_keys(a.seed, k0, a.dim, np.float32 if elem == 4 else np.float16)
-        want = orc.pool(rows0, np.arange(a.batch), bag_size=a.pool_bag)
-        p_ok = bool(pout.cpu().numpy().view(np.uint32).tobytes() == want.view(np.uint32).tobytes())
-        p_ranks = int(round(all_sum(1.0 if p_ok else 0.0)))
-        for i in range(a.warmup):
-            pstep(i)
-        barrier()
-        torch.cuda.synchronize()
-        v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        v0.record()
-        for i in range(a.warmup, total):
-            pstep(i)
-        v1.record()
-        torch.cuda.synchronize()
-        barrier()
-        p_us = [m / a.steps * 1e3 for m in all_list(v0.elapsed_time(v1))]
-        pooled = {"bag_size": a.pool_bag, "bags_per_step": n_bags, "step_us_per_rank": p_us,
-                  "rows_read_gbs_per_gpu": a.batch * row_bytes / (max(p_us) * 1e-6) / 1e9,
-                  "bytes_written_per_step": n_bags * a.dim * 4,
-                  "verified_ranks_bit_exact_vs_oracle": p_ranks,
-                  "note": "ugc_lookup_pool: lookup + fp32 sum per bag in one kernel; the rows are not written"}
-        del pout
+        for bag in bags:
+            n_bags = a.batch // bag
+            pout = torch.empty((n_bags, a.dim), dtype=torch.float32, device=dev)
+
+            def pstep(i):
+                cache.lookup_pool_ptr(rank, keys_dev[i].data_ptr(), 8, a.batch, None, n_bags, bag,
+                                      0 if elem == 4 else 1, 0, pout.data_ptr(), stream)
+
+            pstep(0)
+            torch.cuda.synchronize()
+            want = orc.pool(rows0, np.arange(a.batch), bag_size=bag)
+            p_ok = bool(pout.cpu().numpy().view(np.uint32).tobytes() == want.view(np.uint32).tobytes())
+            p_ranks = int(round(all_sum(1.0 if p_ok else 0.0)))
+            for i in range(a.warmup):
+                pstep(i)
+            barrier()
+            torch.cuda.synchronize()
+            v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            v0.record()
+            for i in range(a.warmup, total):
+                pstep(i)
+            v1.record()
+            torch.cuda.synchronize()
+            barrier()
+            p_us = [m / a.steps * 1e3 for m in all_list(v0.elapsed_time(v1))]
+            pooled.append({"bag_size": bag, "bags_per_step": n_bags, "step_us_per_rank": p_us,
+                           "rows_read_gbs_per_gpu": a.batch * row_bytes / (max(p_us) * 1e-6) / 1e9,
+                           "bytes_written_per_step": n_bags * a.dim * 4,
+                           "verified_ranks_bit_exact_vs_oracle": p_ranks})
+            del pout
+        del rows0
 
     # ---- same steps again with per-kernel events (for the roofline of the gather) ------
     cache.profile_begin(rank, a.steps)

@@ -254,6 +254,13 @@ class Cache:
                                          C.c_void_p(out.data_ptr()), C.c_void_p(s)))
         return out
 
+    def lookup_pool_ptr(self, replica_id, keys_ptr, key_bytes, n_keys, offsets_ptr, n_bags, bag_size,
+                        elem_type, mode, out_ptr, stream=0):
+        """ugc_lookup_pool on raw device pointers (elem_type 0 = fp32, 1 = fp16; mode 0 = sum, 1 = mean)."""
+        check(_lib.lib().ugc_lookup_pool(self._h, replica_id, C.c_void_p(keys_ptr), key_bytes, n_keys,
+                                         C.c_void_p(offsets_ptr), n_bags, bag_size, elem_type, mode,
+                                         C.c_void_p(out_ptr), C.c_void_p(stream)))
+
     def reserve_batch(self, replica_id, max_batch):
         check(_lib.lib().ugc_reserve_batch(self._h, replica_id, max_batch))
 
