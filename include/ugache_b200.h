@@ -428,6 +428,11 @@ typedef struct {
                                      16 or 32; 0 = the largest that balances the warps      */
   int32_t direct_deep;            /* direct kernel: 1 = twice the rows in flight per warp at
                                      3 instead of 4 CTAs per SM                             */
+  int32_t direct_early_host;      /* direct kernel: the first host row of every warp's first tile
+                                     is fetched before the kernel waits for the launch ahead of
+                                     it, so that the host link's queue stays filled from one
+                                     lookup to the next: 0 = when the last finished lookup took
+                                     at least 1024 host rows, 1 = always, 2 = never          */
   int32_t host_order_min_rows;    /* grouped extraction: order the host list by address (two
                                      small kernels between lookup and gather) when the last
                                      finished lookup took at least this many rows from the

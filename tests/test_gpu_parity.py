@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
-@pytest.fixture(autouse=True, params=["grouped", "grouped_static", "direct", "auto"])
+@pytest.fixture(autouse=True, params=["grouped", "grouped_static", "direct", "direct_early", "auto"])
 def extract_mode(request, monkeypatch):
     """Every test of this module runs once per extraction mode (index lists + per-source CTA
     groups / one fused kernel / chosen per lookup from the previous lookup's counts)."""
@@ -30,7 +30,7 @@ def extract_mode(request, monkeypatch):
             "test_duplicates_and_single_source_batches", "test_out_of_range_keys_are_counted_and_skipped",
             "test_unaligned_output_and_host_table", "test_refresh_keeps_results_identical",
             "test_host_list_in_address_order"}
-    if request.param in ("auto", "grouped_static") and request.node.originalname not in wide:
+    if request.param in ("auto", "grouped_static", "direct_early") and request.node.originalname not in wide:
         pytest.skip("covered by the grouped and direct runs")
     monkeypatch.setenv("UGC_EXTRACT_MODE", request.param)
     return request.param

@@ -105,6 +105,7 @@ class Tuning(C.Structure):
         ("direct_block_threads", C.c_int32),
         ("direct_tile_keys", C.c_int32),
         ("direct_deep", C.c_int32),
+        ("direct_early_host", C.c_int32),
         ("host_order_min_rows", C.c_int32),
         ("refresh_fill_ctas", C.c_int32),
         ("refresh_fill_batch_rows", C.c_int32),

@@ -569,6 +569,7 @@ struct Replica {
   int direct_max_host_rows = 8192;
   int direct_tile_shift = 0;               // 0: chosen per launch
   int direct_deep = 0;
+  int direct_early_host = 0;               // 0 auto, 1 always, 2 never
   uint64_t n_local = 0;                    // rows stored here
   uint64_t n_remote = 0;                   // keys read from peers
   // Device-resident placement view of this reader and the key lists of the last
@@ -1015,8 +1016,16 @@ int do_lookup(ugc_ctx* c, Replica* r, const void* keys, int key_bytes, size_t n,
     d.prev_seq = r->last_seq;
     r->direct_slot ^= 1u;
     r->last_slot = d.slot;
+    d.host_base = r->src_base[c->cfg.num_device];
+    // host rows fetched ahead of the dependency wait: worth its prologue when a lookup takes
+    // enough rows from the host for the link's queue to matter
+    bool early = r->direct_early_host == 1;
+    if (r->direct_early_host == 0 && r->feedback) {
+      const volatile Feedback* f = r->feedback;
+      early = f->seq != 0 && f->count[kGroupHost] >= 1024u;
+    }
     UGC_CUDA(launch_extract_direct(keys, key_bytes, d, r->direct_grid, r->direct_block, r->vec_bytes, r->direct_deep != 0,
-                                   (r->pdl & 1) != 0 && n_dev == nullptr, s));
+                                   early && d.host_base != nullptr, (r->pdl & 1) != 0 && n_dev == nullptr, s));
     if (prof) {
       UGC_CUDA(cudaEventRecord(r->prof_events[r->prof_used + 2], s));
       r->prof_used += 3;
@@ -1346,6 +1355,10 @@ int ugc_build(ugc_ctx* c, int replica_id, int device_id, const void* host_table,
     if (!strcmp(m, "grouped_static")) {  // grouped with fixed striding instead of chunk hand-out
       r->extract_mode = UGC_EXTRACT_GROUPED;
       r->gather_dynamic = 0;
+    }
+    if (!strcmp(m, "direct_early")) {  // direct, host rows always fetched ahead of the wait
+      r->extract_mode = UGC_EXTRACT_DIRECT;
+      r->direct_early_host = 1;
     }
   }
   // Far-source CTA budgets and the per-group time-per-byte come from the link description:
@@ -2162,6 +2175,7 @@ int ugc_get_tuning(ugc_ctx* c, int replica_id, ugc_tuning* out) {
   out->split_fixed = r->split_fixed;
   out->direct_tile_keys = r->direct_tile_shift ? (1 << r->direct_tile_shift) : 0;
   out->direct_deep = r->direct_deep;
+  out->direct_early_host = r->direct_early_host;
   out->host_order_min_rows = r->host_order_min_rows;
   out->refresh_fill_ctas = r->refresh_fill_ctas;
   out->refresh_fill_batch_rows = r->refresh_fill_batch_rows;
@@ -2200,6 +2214,7 @@ int ugc_set_tuning(ugc_ctx* c, int replica_id, const ugc_tuning* t) {
   r->split_fixed = t->split_fixed ? 1 : 0;
   r->direct_tile_shift = t->direct_tile_keys == 8 ? 3 : t->direct_tile_keys == 16 ? 4 : t->direct_tile_keys == 32 ? 5 : 0;
   r->direct_deep = t->direct_deep ? 1 : 0;
+  r->direct_early_host = (t->direct_early_host >= 0 && t->direct_early_host <= 2) ? t->direct_early_host : 0;
   r->host_order_min_rows = t->host_order_min_rows < 0 ? 0 : t->host_order_min_rows;
   if (t->refresh_fill_ctas > 0) r->refresh_fill_ctas = t->refresh_fill_ctas;
   if (t->refresh_fill_batch_rows > 0) r->refresh_fill_batch_rows = t->refresh_fill_batch_rows;

@@ -139,6 +139,7 @@ struct DirectParams {
   Counters* counters;
   Feedback* feedback;   // pinned host mirror of the last lookup's counts, or nullptr
   const uint32_t* n_dev;  // if set: the number of keys, in device memory (never above n_keys)
+  const void* host_base;  // src_base[host_loc], for the kernel's prologue
   uint32_t n_keys;
   uint32_t row_bytes;
   uint32_t local_loc;

@@ -839,7 +839,7 @@ __device__ __forceinline__ void fetch_key(const KeyT* __restrict__ keys, uint32_
   key = (uint32_t)k;
 }
 
-template <typename KeyT, int VEC, bool DEEP>
+template <typename KeyT, int VEC, bool DEEP, bool EARLY>
 __global__ void __launch_bounds__(kBlock, DEEP ? 3 : 4)
     extract_direct_kernel(const KeyT* __restrict__ keys, DirectParams p) {
   // rows in flight per lane group: 4 (2 with 32-byte vectors) at 4 CTAs per SM, or twice that
@@ -876,7 +876,30 @@ __global__ void __launch_bounds__(kBlock, DEEP ? 3 : 4)
   probe_issue(p.table, key_cur, ok_cur, pr);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   uint32_t word = probe_resolve(p.table, pr, key_cur, ok_cur);
+  // EARLY: the first host row of this warp's first tile is fetched before the dependency wait
+  // (the host table is never written by a lookup) and held in registers, one piece per lane.
+  // CTAs of this launch become resident while the launch ahead is still waiting for ITS last
+  // host rows; their requests keep the host link's queue filled across the boundary between
+  // two launches, where it would otherwise run empty and fill up again.
+  Vec<VEC> early;
+  uint32_t early_lane = 32;  // lane whose key the held row belongs to; 32 = none
+  if (EARLY) {
+    const bool is_host = ok_cur && word == kEmptyWord;
+    const unsigned hmask = __ballot_sync(kFull, is_host);
+    if (hmask && p.row_bytes / VEC <= 32) {
+      early_lane = __ffs(hmask) - 1;
+      const uint32_t k = __shfl_sync(kFull, key_cur, early_lane);
+      if (lane < p.row_bytes / VEC)
+        ld_row(early, static_cast<const char*>(p.host_base) + (size_t)(k & p.host_mask) * p.row_bytes +
+                          (size_t)lane * VEC);
+    }
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (EARLY && early_lane < 32) {
+    if (lane < p.row_bytes / VEC)
+      st_row(static_cast<char*>(p.out) + (((size_t)tile << tshift) + early_lane) * p.row_bytes + (size_t)lane * VEC,
+             early);
+  }
   // The extraction ahead of this one is complete now.  One thread hands ITS counts on (they
   // sit in the other slot, final) -- to the pinned host mirror the library reads to choose
   // the mode of later lookups -- and clears that slot for the launch after this one.
@@ -926,6 +949,8 @@ __global__ void __launch_bounds__(kBlock, DEEP ? 3 : 4)
       }
       src = s_src[loc] + (size_t)off * p.row_bytes;
     }
+    if (EARLY && lane == early_lane) src = nullptr;  // copied already (still counted below)
+    early_lane = 32;
     n_local += __popc(__ballot_sync(kFull, group == (uint32_t)kGroupLocal));
     n_remote += __popc(__ballot_sync(kFull, group == (uint32_t)kGroupRemote));
     n_host += __popc(__ballot_sync(kFull, group == (uint32_t)kGroupHost));
@@ -1632,7 +1657,8 @@ int usable_vec_bytes(uint32_t row_bytes, int want, const void* out, const void* 
 }
 
 cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectParams& p_in, int grid,
-                                  int block, int vec_bytes, bool deep, bool pdl, cudaStream_t stream) {
+                                  int block, int vec_bytes, bool deep, bool early_host, bool pdl,
+                                  cudaStream_t stream) {
   if (block != 128 && block != 256) block = kBlock;
   const int warps_per_block = block / 32;
   if (p_in.n_keys == 0) return cudaSuccess;
@@ -1663,9 +1689,12 @@ cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectP
 #define UGC_LAUNCH_DIRECT(KEYT, VEC)                                                              \
   do {                                                                                            \
     if (deep)                                                                                     \
-      return launch_pdl(extract_direct_kernel<KEYT, VEC, true>, grid, block, 0, stream, pdl,       \
+      return launch_pdl(extract_direct_kernel<KEYT, VEC, true, false>, grid, block, 0, stream, pdl, \
                         static_cast<const KEYT*>(keys), p);                                       \
-    return launch_pdl(extract_direct_kernel<KEYT, VEC, false>, grid, block, 0, stream, pdl,        \
+    if (early_host)                                                                               \
+      return launch_pdl(extract_direct_kernel<KEYT, VEC, false, true>, grid, block, 0, stream, pdl, \
+                        static_cast<const KEYT*>(keys), p);                                       \
+    return launch_pdl(extract_direct_kernel<KEYT, VEC, false, false>, grid, block, 0, stream, pdl, \
                       static_cast<const KEYT*>(keys), p);                                         \
   } while (0)
   if (key_bytes == 8) {

@@ -55,8 +55,11 @@ cudaError_t launch_host_order(const uint64_t* list_host, uint64_t* sorted, const
 // the most CTAs to use (a multiple of the SM count); fewer are launched for small batches.
 // `deep`: twice the rows in flight per warp at 3 instead of 4 CTAs per SM.  p.tile_shift 3..5
 // forces tiles of 8 / 16 / 32 keys; anything else lets the launcher choose.
+// `early_host` (ignored with `deep`): the first host row of every warp's first tile is fetched
+// before the kernel waits for the launch ahead of it.
 cudaError_t launch_extract_direct(const void* keys, int key_bytes, const DirectParams& p, int grid,
-                                  int block, int vec_bytes, bool deep, bool pdl, cudaStream_t stream);
+                                  int block, int vec_bytes, bool deep, bool early_host, bool pdl,
+                                  cudaStream_t stream);
 
 // Widest of 32 / 16 / 4 bytes, not above `want`, that divides row_bytes and the address of
 // `out` and of every non-null source base: rows then start on a multiple of it on both sides.
