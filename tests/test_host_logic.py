@@ -271,3 +271,29 @@ def test_ctypes_structs_follow_the_header(built_lib):
     sizes = (C.c_uint32 * 5)()
     assert _lib.lib().ugc_abi_sizes(C.byref(sizes)) == 0
     assert list(sizes) == [C.sizeof(cls) for _, cls in pairs]
+
+
+def test_oracle_pool_is_a_sequential_fp32_sum():
+    """The pooled-lookup restatement: per bag, rows added in key order in fp32 from +0; fp16 rows
+    widened first; the mean divides once; ids outside the table add nothing; empty bags are zero."""
+    from oracle import oracle as orc
+    rng = np.random.default_rng(5)
+    for dtype in (np.float32, np.float16):
+        table = (rng.standard_normal((500, 12)) * 100).astype(dtype)
+        keys = rng.integers(0, 500, 300)
+        keys[5], keys[77] = -3, 500
+        offsets = np.array([0, 0, 7, 7, 40, 41, 300])
+        for mean in (False, True):
+            got = orc.pool(table, keys, offsets=offsets, mean=mean)
+            want = np.zeros((6, 12), np.float32)
+            for b in range(6):
+                acc = np.zeros(12, np.float32)
+                for i in range(offsets[b], offsets[b + 1]):
+                    if 0 <= keys[i] < 500:
+                        acc = (acc + table[keys[i]].astype(np.float32)).astype(np.float32)
+                n = offsets[b + 1] - offsets[b]
+                want[b] = acc / np.float32(n) if (mean and n) else acc
+            assert got.dtype == np.float32 and got.view(np.uint32).tobytes() == want.view(np.uint32).tobytes()
+        fixed = orc.pool(table, keys, bag_size=7)
+        assert fixed.shape == (300 // 7, 12)
+        assert np.array_equal(fixed[3], orc.pool(table, keys[21:28], bag_size=7)[0])
