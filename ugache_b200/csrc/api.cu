@@ -1758,7 +1758,7 @@ int ugc_lookup_pool(ugc_ctx* c, int replica_id, const void* keys, int key_bytes,
   if (n_bags == 0) return UGC_OK;
   if (!out || (n_keys && !keys)) return fail(UGC_ERR_INVALID, "keys and out must be non-null");
   if (!offsets && bag_size == 0) return fail(UGC_ERR_INVALID, "give offsets or a bag size");
-  if (!offsets && n_bags * bag_size > n_keys)
+  if (!offsets && bag_size > n_keys / n_bags)  // n_bags * bag_size > n_keys, without overflow
     return fail(UGC_ERR_INVALID, "%zu bags of %zu keys need more than the %zu keys given", n_bags, bag_size, n_keys);
   if (n_keys > kMaxBatch || n_bags > kMaxBatch) return fail(UGC_ERR_INVALID, "at most 2^28 keys and bags per call");
   const uint32_t row_bytes = c->cfg.row_bytes;
