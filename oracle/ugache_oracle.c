@@ -18,9 +18,10 @@
  *     the refresh scatter: the reference's LookupHelper, radix-sort dispatcher, find_boundary
  *     and extract_data device code run on a B200 (ref_extract_pin.cu,
  *     tests/golden/ref_extract.json, tests/test_gpu_refpin.py).
- * Still pinned only by reading ("parity unpinned"): the placement heuristics (the reference's
- * solver file does not compile without the commercial solver's headers) and the host-side
- * slot bookkeeping of a refresh.
+ *   - the placement heuristics (Intuitive, Rep, CliquePart): the four placement arrays the
+ *     reference's solver classes produce on 13 seeded rankings, run on the CPU
+ *     (ref_solver_pin.cc, tests/golden/ref_solver.json, tests/test_oracle_golden.py).
+ * Still pinned only by reading ("parity unpinned"): the host-side slot bookkeeping of a refresh.
  *
  * Every function cites the reference file:line it follows (paths relative to the
  * reference project root).

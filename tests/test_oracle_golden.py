@@ -190,3 +190,32 @@ def test_oracle_extraction_matches_reference_gpu_kernels():
         assert [int(x) for x in want["groups"]] == g["groups"], case["name"]
         assert digest(want["records"]) == g["records"], case["name"]
         assert digest(want["out"]) == g["out"], case["name"]
+
+
+def test_placement_heuristics_match_the_reference_solver_classes(built_lib):
+    """The oracle's Intuitive / Rep / CliquePart solvers AND the library's own produce, array for
+    array (nid_to_block, block_placement, block_access_from, block_density), what the reference's
+    solver classes (coll_cache_lib/coll_cache/optimal_solver_class.cc:1251-1404, :1869-2058,
+    compiled in place into oracle/_ref/ref_solver_pin) produced for the same seeded rankings;
+    their digests are kept in tests/golden/ref_solver.json (made by tests/golden/make_solver_pin.py)."""
+    import json
+    import os
+    import sys
+    from ugache_b200 import runtime as rt
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, here)
+    try:
+        import make_solver_pin as pin
+    finally:
+        sys.path.remove(here)
+    with open(os.path.join(here, "ref_solver.json")) as f:
+        want = {c["name"]: c for c in json.load(f)["cases"]}
+    assert len(want) == len(pin.CASES) >= 13
+    for case in pin.CASES:
+        name, policy, G, N, pct, alpha, tl, tr, tc = case
+        assert pin.digest_placement(*pin.oracle_placement(case)) == want[name]["digest"], name
+        ids, freqs = pin.ranking(name, N, alpha)
+        p = rt.solve_placement(policy, G, ids, freqs, pct, t_local=tl, t_remote=tr, t_cpu=tc)
+        ours = (p.nid_to_block, p.block_placement, np.asarray(p.block_access_from).reshape(G, -1), p.block_density)
+        assert pin.digest_placement(*ours) == want[name]["digest"], ("library", name)
+
